@@ -89,7 +89,9 @@ static void build_selection(xccl_team *team)
             team->coll_team_id[c][m] = -1;
             for (size_t i = 0; i < team->tl_teams.size(); i++) {
                 const TlCaps &caps = team->tl_teams[i]->ctx->tl->caps;
-                if ((caps.coll_types & XCCL_BIT(c)) && (caps.mem_types & XCCL_BIT(m))) {
+                const bool    sync = (c == XCCL_BARRIER || c == XCCL_FANIN || c == XCCL_FANOUT);
+                const uint64_t mems = (sync && caps.sync_mem_types != ~0ull) ? caps.sync_mem_types : caps.mem_types;
+                if ((caps.coll_types & XCCL_BIT(c)) && (mems & XCCL_BIT(m))) {
                     team->coll_team_id[c][m] = (int)i;
                     break;
                 }

@@ -67,6 +67,9 @@ public:
 struct TlCaps {
     uint64_t                   coll_types   = 0;
     uint64_t                   mem_types    = 0;  // bit per xccl_memory_type_t
+    // barrier / fanin / fanout carry no buffer and are dispatched as host memory; a device TL that
+    // wants to serve them (as stream-ordered kernels) sets the host bit here only
+    uint64_t                   sync_mem_types = ~0ull;  // ~0 = same as mem_types
     unsigned                   reproducible = XCCL_REPRODUCIBILITY_MODE_NON_REPRODUCIBLE;
     unsigned                   thread_mode  = XCCL_THREAD_MODE_SINGLE | XCCL_THREAD_MODE_MULTIPLE;
     uint64_t                   team_usage   = XCCL_LIB_PARAMS_TEAM_USAGE_SW_COLLECTIVES;

@@ -1,0 +1,590 @@
+// Tensor-parallel GEMM kernels for sm_100a (see tp_gemm.cuh for the operations).
+//
+// CTA anatomy (192 threads, one CTA per SM, persistent over output tiles of 128 x 256):
+//   warp 0   one elected thread issues TMA tiled loads (A: 128 x 64, B: 256 x 64 bf16, 128B swizzle)
+//            into a 4-stage shared-memory ring guarded by full/empty mbarriers
+//   warp 1   one elected thread issues tcgen05.mma (M128 N256 K16, 4 per stage) accumulating fp32 in
+//            tensor memory; tcgen05.commit releases the stage and, after the last K block, hands the
+//            accumulator to the epilogue. Two accumulators (2 x 256 TMEM columns) alternate so the
+//            epilogue of tile i overlaps the MMAs of tile i+1
+//   warps 2-5  read their 32 TMEM lanes with tcgen05.ld, apply the epilogue (bf16 cast or
+//            silu(gate)*up), transpose through shared memory and write 128-byte row segments to
+//            local or peer memory
+// No TMA load uses cluster multicast and no TMA load reads another GPU's memory: remote operands
+// are first copied into local memory by the copy CTAs of this same kernel.
+#include <algorithm>
+#include <cstdio>
+#include <cuda_bf16.h>
+
+#include "../cuda/cuda_common.h"
+#include "sm100_ptx.cuh"
+#include "tp_gemm.cuh"
+
+namespace xccl {
+namespace tp {
+
+using namespace sm100;
+
+namespace {
+
+constexpr uint32_t kABytes     = kBM * kBK * 2;          // 16 KB
+constexpr uint32_t kBBytes     = kBN * kBK * 2;          // 32 KB
+constexpr uint32_t kStageBytes = kABytes + kBBytes;
+constexpr uint32_t kStageRowBytes = 144;                 // 128 B of payload + 16 B pad: conflict-free transposes
+constexpr uint32_t kEpiBytes   = 4 * 32 * kStageRowBytes;
+constexpr uint32_t kTmemCols   = 512;
+constexpr uint32_t kSmemBytes  = kStages * kStageBytes + kEpiBytes + 256 + 1024;  // + barriers + alignment slack
+
+struct Tile {
+    int mb, nb, shard;
+};
+
+// Order in which a rank walks its output tiles.
+//  COMM_NONE            groups of 16 row blocks x all column blocks (L2 reuse of A and B)
+//  COMM_ALLGATHER_A     row shard by row shard, starting with the local one (its A is already here)
+//  COMM_REDUCE_SCATTER  row shard by row shard, starting with the next rank's and ending with the
+//                       local one, so remote partial tiles leave early and local ones need no wire
+__device__ __forceinline__ Tile tile_of(const GemmParams &p, int rank, int t, int tiles_m, int tiles_n)
+{
+    Tile tl;
+    if (p.comm == COMM_NONE) {
+        const int group = 16 * tiles_n;
+        const int g = t / group, within = t % group;
+        const int gm = min(16, tiles_m - g * 16);
+        tl.mb    = g * 16 + within % gm;
+        tl.nb    = within / gm;
+        tl.shard = 0;
+        return tl;
+    }
+    const int mbs   = tiles_m / p.tp_size;
+    const int per   = mbs * tiles_n;
+    const int idx   = t / per, within = t % per;
+    const int first = (p.comm == COMM_ALLGATHER_A) ? 0 : 1;
+    tl.shard = (rank + first + idx) % p.tp_size;
+    tl.mb    = tl.shard * mbs + within % mbs;
+    tl.nb    = within / mbs;
+    return tl;
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void red_release_gpu_add(uint32_t *p, uint32_t v)
+{
+    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Bounded wait for a counter to reach `target` (wrap-safe); sys = counter written by another GPU.
+__device__ __forceinline__ bool wait_counter(const uint32_t *ctr, uint32_t target, bool sys, const AbortFlag &ab,
+                                             uint32_t where)
+{
+    const unsigned long long t0 = now_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; i++) {
+            uint32_t v = sys ? nvl::ld_acquire_sys(ctr) : ld_acquire_gpu(ctr);
+            if ((int32_t)(v - target) >= 0) return true;
+        }
+        if (*ab.smem != 0) return false;
+        if (now_ns() - t0 > ab.budget_ns) {
+            *ab.smem = 1;
+            atomicCAS(ab.global, 0u, 0x200u | where);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
+{
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+
+// Copy CTAs of the allgather mode: pull the remote row shards into the local gathered buffer,
+// one 128-row block at a time, and count each finished slice into ready[block].
+__device__ void copy_cta_loop(const GemmParams &p, int rank, int local, int copy_idx, int n_copy, const AbortFlag &ab)
+{
+    const int    tiles_m = (p.M + kBM - 1) / kBM;
+    const int    mbs     = tiles_m / p.tp_size;
+    const size_t blk_packs = (size_t)kBM * p.K * 2 / 16;  // 16-byte packs in one row block
+    const size_t per   = (blk_packs + n_copy - 1) / n_copy;
+    const size_t lo    = min((size_t)copy_idx * per, blk_packs), hi = min(lo + per, blk_packs);
+    // peers must have published their shards before we read them: barrier among the copy CTAs
+    uint32_t *epoch_slot = p.pad[rank] + nvl::kPadEpochOff + copy_idx;
+    uint32_t  epoch      = *epoch_slot + 1;
+    __syncthreads();
+    int bad = 0;
+    if ((int)threadIdx.x < p.tp_size) {
+        const int q = threadIdx.x;
+        nvl::st_release_sys(p.pad[q] + (size_t)copy_idx * nvl::kMaxRanks + rank, epoch);
+        if (!nvl::wait_flag(p.pad[rank] + (size_t)copy_idx * nvl::kMaxRanks + q, epoch, ab.budget_ns)) bad = 1;
+    }
+    if (__syncthreads_or(bad)) {
+        if (threadIdx.x == 0) {
+            *ab.smem = 1;
+            atomicCAS(ab.global, 0u, 0x300u);
+        }
+        return;
+    }
+    for (int i = 1; i < p.tp_size; i++) {
+        const int shard = (rank + i) % p.tp_size;
+        for (int mb_in = 0; mb_in < mbs; mb_in++) {
+            const int    mb   = shard * mbs + mb_in;
+            const size_t base = (size_t)mb * blk_packs;
+            const uint4 *from = reinterpret_cast<const uint4 *>(p.xg[shard]) + base;
+            uint4       *to   = reinterpret_cast<uint4 *>(p.xg[rank]) + base;
+            size_t       k    = lo + threadIdx.x;
+            for (; k + 3 * blockDim.x < hi; k += 4 * blockDim.x) {
+                uint4 v0 = nvl::ld_nc16(from + k), v1 = nvl::ld_nc16(from + k + blockDim.x);
+                uint4 v2 = nvl::ld_nc16(from + k + 2 * blockDim.x), v3 = nvl::ld_nc16(from + k + 3 * blockDim.x);
+                to[k] = v0;
+                to[k + blockDim.x] = v1;
+                to[k + 2 * blockDim.x] = v2;
+                to[k + 3 * blockDim.x] = v3;
+            }
+            for (; k < hi; k += blockDim.x) to[k] = nvl::ld_nc16(from + k);
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                __threadfence();
+                red_release_gpu_add(p.ready[local] + mb, 1u);
+            }
+        }
+    }
+    // closing barrier: nobody overwrites a shard that a peer may still be reading
+    epoch++;
+    __syncthreads();
+    bad = 0;
+    if ((int)threadIdx.x < p.tp_size) {
+        const int q = threadIdx.x;
+        nvl::st_release_sys(p.pad[q] + (size_t)copy_idx * nvl::kMaxRanks + rank, epoch);
+        if (!nvl::wait_flag(p.pad[rank] + (size_t)copy_idx * nvl::kMaxRanks + q, epoch, ab.budget_ns)) bad = 1;
+    }
+    if (__syncthreads_or(bad) && threadIdx.x == 0) {
+        *ab.smem = 1;
+        atomicCAS(ab.global, 0u, 0x301u);
+    }
+    if (threadIdx.x == 0) *epoch_slot = epoch;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t       *smem_gen  = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t sA        = smem_base;
+    const uint32_t sB        = smem_base + kStages * kABytes;
+    uint8_t       *epi_gen   = smem_gen + kStages * kStageBytes;
+    const uint32_t bars      = smem_base + kStages * kStageBytes + kEpiBytes;
+    auto full_bar       = [&](int s) { return bars + 8u * s; };
+    auto empty_bar      = [&](int s) { return bars + 8u * (kStages + s); };
+    auto tmem_full_bar  = [&](int a) { return bars + 8u * (2 * kStages + a); };
+    auto tmem_empty_bar = [&](int a) { return bars + 8u * (2 * kStages + 2 + a); };
+    volatile uint32_t *tmem_slot  = reinterpret_cast<volatile uint32_t *>(epi_gen + kEpiBytes + 8 * (2 * kStages + 4));
+    volatile uint32_t *abort_slot = tmem_slot + 1;
+
+    const int warp  = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int local = blockIdx.y;
+    const int rank  = p.rank_base + local;
+    AbortFlag ab{abort_slot, p.error, p.budget_ns};
+
+    if (threadIdx.x == 0) *abort_slot = 0;
+    __syncthreads();
+
+    // ---- copy CTAs (allgather mode) never touch the tensor cores
+    if ((int)blockIdx.x >= p.n_gemm_ctas) {
+        copy_cta_loop(p, rank, local, blockIdx.x - p.n_gemm_ctas, gridDim.x - p.n_gemm_ctas, ab);
+        return;
+    }
+
+    const CUtensorMap *tmA = &lp.tmA[local], *tmB0 = &lp.tmB0[local], *tmB1 = &lp.tmB1[local];
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; s++) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(tmem_full_bar(a), 1);
+            mbar_init(tmem_empty_bar(a), 4);
+        }
+        mbar_fence_init();
+        tma_prefetch_desc(tmA);
+        tma_prefetch_desc(tmB0);
+        if (p.epilogue == EPI_SWIGLU) tma_prefetch_desc(tmB1);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32((const void *)tmem_slot), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int tiles_m = (p.M + kBM - 1) / kBM;
+    const int tiles_n = (p.N + kBN - 1) / kBN;
+    const int total   = tiles_m * tiles_n;
+    const int kblocks = (p.K + kBK - 1) / kBK;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (elect_one()) {
+            int      s = 0;
+            uint32_t phase = 0;
+            int      armed[kStages];
+            for (int i = 0; i < kStages; i++) armed[i] = -1;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total && ok; t += p.n_gemm_ctas) {
+                const Tile tl = tile_of(p, rank, t, tiles_m, tiles_n);
+                if (p.comm == COMM_ALLGATHER_A && tl.shard != rank) {
+                    // rows of this block are being copied in by the copy CTAs of this kernel
+                    const uint32_t n_copy = gridDim.x - p.n_gemm_ctas;
+                    ok = wait_counter(p.ready[local] + tl.mb, p.seq * n_copy, false, ab, 1);
+                    asm volatile("fence.proxy.async.global;" ::: "memory");
+                    if (!ok) break;
+                }
+                for (int kb = 0; kb < kblocks; kb++) {
+                    if (!mbar_wait(empty_bar(s), phase ^ 1, ab, 2)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(full_bar(s), kStageBytes);
+                    armed[s] = (int)phase;
+                    tma_load_2d(sA + s * kABytes, tmA, kb * kBK, tl.mb * kBM, full_bar(s));
+                    if (p.epilogue == EPI_SWIGLU) {
+                        tma_load_2d(sB + s * kBBytes, tmB0, kb * kBK, tl.nb * (kBN / 2), full_bar(s));
+                        tma_load_2d(sB + s * kBBytes + kBBytes / 2, tmB1, kb * kBK, tl.nb * (kBN / 2), full_bar(s));
+                    } else {
+                        tma_load_2d(sB + s * kBBytes, tmB0, kb * kBK, tl.nb * kBN, full_bar(s));
+                    }
+                    if (++s == kStages) {
+                        s = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+            if (!ok) {
+                // let the copies that are still in flight land before the CTA goes away
+                for (int i = 0; i < kStages; i++) {
+                    if (armed[i] < 0) continue;
+                    for (int spin = 0; spin < (1 << 16); spin++) {
+                        if (mbar_try_wait(full_bar(i), (uint32_t)armed[i])) break;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (elect_one()) {
+            const uint32_t idesc = make_idesc(1, 1, kBM, kBN);
+            int            s = 0;
+            uint32_t       phase = 0, acc_phase = 0;
+            int            a = 0;
+            bool           ok = true;
+            for (int t = blockIdx.x; t < total && ok; t += p.n_gemm_ctas) {
+                if (!mbar_wait(tmem_empty_bar(a), acc_phase ^ 1, ab, 3)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)a * kBN;
+                for (int kb = 0; kb < kblocks; kb++) {
+                    if (!mbar_wait(full_bar(s), phase, ab, 4)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint64_t da = make_desc_sw128(sA + s * kABytes);
+                    const uint64_t db = make_desc_sw128(sB + s * kBBytes);
+#pragma unroll
+                    for (int k = 0; k < kBK / 16; k++) {
+                        // 16 bf16 = 32 bytes further along K inside the 128-byte swizzle row
+                        mma_f16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+                    }
+                    mma_commit(empty_bar(s));
+                    if (++s == kStages) {
+                        s = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (!ok) break;
+                mma_commit(tmem_full_bar(a));
+                a ^= 1;
+                if (a == 0) acc_phase ^= 1;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue warps
+        const int      quarter = warp % 4;  // TMEM lanes this warp may read: 32*quarter ..
+        uint8_t       *stage   = epi_gen + (warp - 2) * 32 * kStageRowBytes;
+        uint32_t       acc_phase = 0;
+        int            a = 0;
+        const int      mbs  = (p.comm == COMM_NONE) ? tiles_m : tiles_m / p.tp_size;
+        const int      out_cols_per_tile = (p.epilogue == EPI_SWIGLU) ? kBN / 2 : kBN;
+        const int      n_out = (p.epilogue == EPI_SWIGLU) ? p.N / 2 : p.N;
+        for (int t = blockIdx.x; t < total; t += p.n_gemm_ctas) {
+            const Tile tl = tile_of(p, rank, t, tiles_m, tiles_n);
+            if (!mbar_wait(tmem_full_bar(a), acc_phase, ab, 5)) break;
+            tc_fence_after();
+            const uint32_t t_acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)a * kBN;
+            // destination of this tile
+            __nv_bfloat16 *out;
+            size_t         ld;
+            int            row0;
+            if (p.comm == COMM_REDUCE_SCATTER_C) {
+                // slot `rank` of the owner's partial buffer, parity by launch sequence
+                const size_t shard_rows = (size_t)mbs * kBM;
+                out  = p.part[tl.shard] + ((size_t)(p.seq & 1) * p.tp_size + rank) * shard_rows * (size_t)p.N;
+                ld   = (size_t)p.N;
+                row0 = (tl.mb - tl.shard * mbs) * kBM;
+            } else {
+                out  = p.C[local];
+                ld   = (size_t)p.ldc;
+                row0 = tl.mb * kBM;
+            }
+            const int rows_valid = ((p.comm == COMM_REDUCE_SCATTER_C) ? mbs * kBM : p.M) - row0;
+            for (int oc = 0; oc < out_cols_per_tile; oc += 64) {
+                // 64 output columns -> one 128-byte staging row per TMEM lane
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    uint32_t g[32];
+                    uint32_t packed[16];
+                    tmem_ld_32x32(t_acc + (uint32_t)(oc + h * 32), g);
+                    if (p.epilogue == EPI_SWIGLU) {
+                        uint32_t u[32];
+                        tmem_ld_32x32(t_acc + (uint32_t)(kBN / 2 + oc + h * 32), u);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
+                            float u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
+                            packed[j] = pack_bf16x2(silu(g0) * u0, silu(g1) * u1);
+                        }
+                    } else {
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            packed[j] = pack_bf16x2(__uint_as_float(g[2 * j]), __uint_as_float(g[2 * j + 1]));
+                        }
+                    }
+                    uint4 *row = reinterpret_cast<uint4 *>(stage + lane * kStageRowBytes + h * 64);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        row[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+                    }
+                }
+                __syncwarp();
+                const int col0 = tl.nb * out_cols_per_tile + oc;
+#pragma unroll
+                for (int it = 0; it < 8; it++) {
+                    const int r = it * 4 + lane / 8, chunk = lane % 8;
+                    const int grow = quarter * 32 + r, gcol = col0 + chunk * 8;
+                    if (grow < rows_valid && gcol < n_out) {
+                        uint4 v = *reinterpret_cast<const uint4 *>(stage + r * kStageRowBytes + chunk * 16);
+                        *reinterpret_cast<uint4 *>(out + (size_t)(row0 + grow) * ld + gcol) = v;
+                    }
+                }
+                __syncwarp();
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tmem_empty_bar(a));
+            if (p.comm == COMM_REDUCE_SCATTER_C) {
+                // all four epilogue warps have stored their rows: tell the owner one more tile arrived
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (warp == 2 && lane == 0) {
+                    __threadfence_system();
+                    uint32_t *ctr = p.pad[tl.shard] + nvl::kPadCounterOff +
+                                    ((p.seq & 1) * p.tp_size + rank) * 64 + (tl.mb - tl.shard * mbs);
+                    nvl::red_release_sys_add(ctr, 1u);
+                }
+            }
+            a ^= 1;
+            if (a == 0) acc_phase ^= 1;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+
+    // ---- reduce-scatter: add up the partial tiles that every rank stored for my rows
+    if (p.comm == COMM_REDUCE_SCATTER_C && *abort_slot == 0) {
+        const int    mbs        = tiles_m / p.tp_size;
+        const size_t shard_rows = (size_t)mbs * kBM;
+        const size_t slot_elems = shard_rows * (size_t)p.N;
+        const __nv_bfloat16 *mine = p.part[rank] + (size_t)(p.seq & 1) * p.tp_size * slot_elems;
+        const uint32_t *ctr_base  = p.pad[rank] + nvl::kPadCounterOff + (p.seq & 1) * p.tp_size * 64;
+        const int items = mbs * tiles_n;
+        __shared__ int item_ok;
+        for (int it = blockIdx.x; it < items; it += p.n_gemm_ctas) {
+            const int mb_in = it % mbs, nb = it / mbs;
+            if (threadIdx.x == 0) {
+                int good = 1;
+                for (int src = 0; src < p.tp_size && good; src++) {
+                    // rs_target = tiles that rank `src` has sent for this row block over all launches
+                    // of this parity, this one included (the host keeps the running total)
+                    good = wait_counter(ctr_base + src * 64 + mb_in, p.rs_target, true, ab, 6) ? 1 : 0;
+                }
+                item_ok = good;
+            }
+            __syncthreads();
+            if (!item_ok) break;
+            // 128 rows x 256 columns: 32 packs of 8 bf16 per row
+            for (int k = threadIdx.x; k < kBM * (kBN / 8); k += blockDim.x) {
+                const int    r = k / (kBN / 8), cpk = k % (kBN / 8);
+                const size_t row = (size_t)mb_in * kBM + r;
+                const int    col = nb * kBN + cpk * 8;
+                if (col >= p.N) continue;
+                float acc[8];
+#pragma unroll
+                for (int e = 0; e < 8; e++) acc[e] = 0.0f;
+                for (int src = 0; src < p.tp_size; src++) {
+                    uint4 v = nvl::ld_nc16(mine + (size_t)src * slot_elems + row * (size_t)p.N + col);
+                    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&v);
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        float2 f = __bfloat1622float2(h[e]);
+                        acc[2 * e] += f.x;
+                        acc[2 * e + 1] += f.y;
+                    }
+                }
+                uint4 o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                                     pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+                *reinterpret_cast<uint4 *>(p.C[local] + row * (size_t)p.ldc + col) = o;
+            }
+            __syncthreads();
+        }
+    }
+}
+
+}  // namespace
+
+uint32_t *error_word()
+{
+    static uint32_t *word[64] = {nullptr};
+    int              dev = 0;
+    cudaGetDevice(&dev);
+    if (word[dev] == nullptr) {
+        if (cudaMalloc((void **)&word[dev], 4) != cudaSuccess) return nullptr;
+        cudaMemset(word[dev], 0, 4);
+    }
+    return word[dev];
+}
+
+size_t gemm_smem_bytes() { return kSmemBytes; }
+
+xccl_status_t make_tensor_map_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint64_t ld,
+                                 uint32_t box_rows)
+{
+    XCCL_DRIVER_FN(cuTensorMapEncodeTiled);
+    if (((uintptr_t)base & 15) != 0 || (ld * 2) % 16 != 0) return XCCL_ERR_INVALID_PARAM;
+    cuuint64_t dims[2]    = {cols, rows};
+    cuuint64_t strides[1] = {ld * 2};
+    cuuint32_t box[2]     = {(cuuint32_t)kBK, box_rows};
+    cuuint32_t estr[2]    = {1, 1};
+    XCCL_CU_CHECK(cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims,
+                                         strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+    return XCCL_OK;
+}
+
+xccl_status_t launch_gemm(const GemmParams &p_in, const GemmLaunch &l, cudaStream_t stream)
+{
+    GemmParams p = p_in;
+    if (p.K % 8 != 0 || p.N % 8 != 0 || p.M <= 0 || p.N <= 0 || p.K <= 0) return XCCL_ERR_INVALID_PARAM;
+    if (p.epilogue == EPI_SWIGLU && p.N % kBN != 0) return XCCL_ERR_INVALID_PARAM;  // gate/up halves of a tile
+    if (p.comm != COMM_NONE) {
+        int tiles_m = (p.M + kBM - 1) / kBM;
+        if (p.M % kBM != 0 || tiles_m % p.tp_size != 0 || tiles_m / p.tp_size > 64) return XCCL_ERR_INVALID_PARAM;
+    }
+    static bool attr_set[64] = {false};
+    int         dev = 0, sms = 0;
+    XCCL_CUDA_CHECK(cudaGetDevice(&dev));
+    XCCL_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    if (!attr_set[dev]) {
+        XCCL_CUDA_CHECK(cudaFuncSetAttribute(tp_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        attr_set[dev] = true;
+    }
+    int ctas = l.ctas > 0 ? l.ctas : sms / std::max(l.n_local, 1);
+    if (p.n_gemm_ctas <= 0 || p.n_gemm_ctas > ctas) p.n_gemm_ctas = ctas;
+    if (p.comm == COMM_ALLGATHER_A && p.tp_size > 1 && p.n_gemm_ctas == ctas) return XCCL_ERR_INVALID_PARAM;
+    if (p.error == nullptr) p.error = error_word();
+    if (p.budget_ns == 0) p.budget_ns = 4000000000ull;
+
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim          = dim3((unsigned)ctas, (unsigned)l.n_local);
+    cfg.blockDim         = dim3(kThreads);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.stream           = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id              = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = l.cooperative ? 1 : 0;
+    cfg.attrs               = attr;
+    cfg.numAttrs            = 1;
+    XCCL_CUDA_CHECK(cudaLaunchKernelEx(&cfg, tp_gemm_kernel, p, l));
+    return XCCL_OK;
+}
+
+}  // namespace tp
+}  // namespace xccl
+
+using namespace xccl;
+using namespace xccl::tp;
+
+extern "C" {
+
+xccl_status_t xccl_gemm_bf16(const void *A, const void *B, void *C, int M, int N, int K, void *stream)
+{
+    GemmParams p{};
+    GemmLaunch l{};
+    p.M = M; p.N = N; p.K = K;
+    p.epilogue = EPI_STORE;
+    p.comm     = COMM_NONE;
+    p.tp_size  = 1;
+    p.ldc      = N;
+    p.C[0]     = (__nv_bfloat16 *)C;
+    xccl_status_t st = make_tensor_map_2d(&l.tmA[0], A, (uint64_t)M, (uint64_t)K, (uint64_t)K, kBM);
+    if (st != XCCL_OK) return st;
+    st = make_tensor_map_2d(&l.tmB0[0], B, (uint64_t)N, (uint64_t)K, (uint64_t)K, kBN);
+    if (st != XCCL_OK) return st;
+    l.tmB1[0] = l.tmB0[0];
+    return launch_gemm(p, l, (cudaStream_t)stream);
+}
+
+xccl_status_t xccl_gemm_swiglu_bf16(const void *A, const void *Wg, const void *Wu, void *H, int M, int F, int K,
+                                    void *stream)
+{
+    GemmParams p{};
+    GemmLaunch l{};
+    p.M = M; p.N = 2 * F; p.K = K;
+    p.epilogue = EPI_SWIGLU;
+    p.comm     = COMM_NONE;
+    p.tp_size  = 1;
+    p.ldc      = F;
+    p.C[0]     = (__nv_bfloat16 *)H;
+    if (F % (kBN / 2) != 0) return XCCL_ERR_INVALID_PARAM;
+    xccl_status_t st = make_tensor_map_2d(&l.tmA[0], A, (uint64_t)M, (uint64_t)K, (uint64_t)K, kBM);
+    if (st != XCCL_OK) return st;
+    st = make_tensor_map_2d(&l.tmB0[0], Wg, (uint64_t)F, (uint64_t)K, (uint64_t)K, kBN / 2);
+    if (st != XCCL_OK) return st;
+    st = make_tensor_map_2d(&l.tmB1[0], Wu, (uint64_t)F, (uint64_t)K, (uint64_t)K, kBN / 2);
+    if (st != XCCL_OK) return st;
+    return launch_gemm(p, l, (cudaStream_t)stream);
+}
+
+uint32_t xccl_gemm_last_error(void)
+{
+    uint32_t *w = xccl::tp::error_word();
+    uint32_t  v = 0;
+    if (w == nullptr) return 0xffffffffu;
+    cudaMemcpy(&v, w, 4, cudaMemcpyDeviceToHost);
+    if (v != 0) cudaMemset(w, 0, 4);
+    return v;
+}
+
+}  // extern "C"

@@ -1,0 +1,85 @@
+// Interface of the tensor-parallel GEMM kernels (implemented in tp_gemm.cu).
+//
+// One persistent, warp-specialised tcgen05 kernel serves four operations:
+//   GEMM             C[M,N]   = A[M,K] * B[N,K]^T                         (bf16 in, fp32 accumulate in TMEM)
+//   GEMM + SwiGLU    H[M,F]   = silu(A * Wg^T) .* (A * Wu^T)              (gate and up tiles share one accumulator)
+//   allgather->GEMM  the A operand is the concatenation of every rank's row shard; CTAs of the
+//                    same kernel pull the remote shards over NVLink into local memory and
+//                    release them to the MMA pipeline block of rows by block of rows
+//   GEMM->reduce-scatter  each output tile is stored straight into the memory of the rank that
+//                    owns those rows; when a row block has arrived from every rank its owner adds
+//                    the partial tiles up - still inside the same kernel
+// Ranks can be real (one process per GPU, peer pointers) or emulated (all ranks in one
+// cooperative launch on one GPU, gridDim.y = ranks), exactly like the NVLink collectives.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "../tl/nvlink/nvl_device.cuh"
+#include "xccl/xccl.h"
+
+namespace xccl {
+namespace tp {
+
+constexpr int kBM = 128, kBN = 256, kBK = 64, kStages = 4;
+constexpr int kThreads = 192;           // warp 0: TMA, warp 1: MMA, warps 2-5: epilogue
+constexpr int kMaxTpRanks = 8;
+
+enum Epilogue { EPI_STORE = 0, EPI_SWIGLU = 1 };
+enum CommMode { COMM_NONE = 0, COMM_ALLGATHER_A = 1, COMM_REDUCE_SCATTER_C = 2 };
+
+struct GemmParams {
+    int M, N, K;          // N counts accumulator columns (gate + up for SwiGLU)
+    int epilogue;
+    int comm;
+    int tp_size;          // ranks taking part (1 without communication)
+    int rank_base;        // team rank of blockIdx.y == 0
+    int n_gemm_ctas;      // CTAs (per rank) that run MMA tiles; the rest copy (allgather mode)
+    uint32_t seq;         // launch sequence number (starts at 1): readiness counters and buffer parity follow it
+    uint32_t rs_target;   // reduce-scatter: running total of tiles per (source, row block) for this parity
+    unsigned long long budget_ns;
+    uint32_t *error;      // device word, 0 = fine
+    int ldc;              // leading dimension of the output in elements
+
+    // per LOCAL rank (blockIdx.y)
+    __nv_bfloat16 *C[kMaxTpRanks];        // EPI output (COMM_NONE / ALLGATHER) or the reduced shard (REDUCE_SCATTER)
+    // allgather mode: xg[r] is rank r's gathered A buffer [M,K] as mapped here; shard s of rank s is valid on entry
+    __nv_bfloat16 *xg[kMaxTpRanks];       // indexed by TEAM rank
+    uint32_t      *ready[kMaxTpRanks];    // per LOCAL rank: one flag per 128-row block of A, local memory
+    // reduce-scatter mode: part[r] = rank r's partial buffer [tp_size][M/tp_size][N] as mapped here
+    __nv_bfloat16 *part[kMaxTpRanks];     // indexed by TEAM rank
+    uint32_t      *pad[kMaxTpRanks];      // signal pads (TEAM rank) for barriers and arrival counters
+};
+
+// Host launcher. tmA / tmB0 / tmB1 are built by make_tensor_map_2d for each local rank.
+struct GemmLaunch {
+    CUtensorMap tmA[kMaxTpRanks];
+    CUtensorMap tmB0[kMaxTpRanks];
+    CUtensorMap tmB1[kMaxTpRanks];  // SwiGLU: the "up" weights; otherwise unused
+    int         n_local = 1;        // gridDim.y
+    int         ctas    = 0;        // gridDim.x; 0 = one per SM (divided among local ranks)
+    bool        cooperative = false;
+};
+
+// rows x cols bf16 matrix with `ld` elements between rows, tiles of box_rows x 64, 128B swizzle
+xccl_status_t make_tensor_map_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint64_t ld,
+                                 uint32_t box_rows);
+
+xccl_status_t launch_gemm(const GemmParams &p, const GemmLaunch &l, cudaStream_t stream);
+
+size_t gemm_smem_bytes();
+uint32_t *error_word();  // per-device error word shared by the GEMM kernels
+
+}  // namespace tp
+}  // namespace xccl
+
+extern "C" {
+// Plain C hooks (ctypes). All pointers are device pointers to bf16 row-major matrices.
+// C[M,N] = A[M,K] * B[N,K]^T
+xccl_status_t xccl_gemm_bf16(const void *A, const void *B, void *C, int M, int N, int K, void *stream);
+// H[M,F] = silu(A Wg^T) .* (A Wu^T), Wg and Wu are [F,K]
+xccl_status_t xccl_gemm_swiglu_bf16(const void *A, const void *Wg, const void *Wu, void *H, int M, int F, int K,
+                                    void *stream);
+// Last error word written by a GEMM kernel on the current device (0 = none); clears it.
+uint32_t      xccl_gemm_last_error(void);
+}

@@ -1,0 +1,663 @@
+// NVLink-team collectives for sm_100a: kernels that move and reduce data by loading and
+// storing peer GPUs' memory directly (and, for NVLS, through NVSwitch multimem instructions).
+//
+// Shared structure. Every rank owns a workspace split into two halves that alternate between
+// consecutive uses, so a rank may start the next collective while a slower peer still reads the
+// previous one. Data is cut into 16-byte packs; block b of every rank works on the same range of
+// packs ("piece"), which makes a barrier among the b-th blocks of all ranks sufficient.
+//
+//   one-shot allreduce   push my vector into slot[my rank] of every peer's workspace, barrier,
+//                        reduce the N slots locally                    (latency-bound sizes)
+//   two-shot allreduce   copy in, barrier, reduce my 1/N of each piece from all peers' workspaces
+//                        in place, barrier, gather the reduced parts   (bandwidth-bound sizes)
+//   NVLS allreduce       as two-shot, but the reduction is one multimem.ld_reduce (done in the
+//                        switch) and the result is broadcast with multimem.st
+//   reduce / reduce-scatter / bcast / allgather / alltoall / alltoallv: copy in, barrier, pull.
+//   barrier / fanin / fanout: flag traffic only.
+//
+// The post-scale and the output cast of xccl_coll_epilogue_t are applied where the reduced value
+// is produced, so gradient averaging and fp32->bf16 casting cost no extra pass over memory.
+// Baseline these replace: the reference's NCCL team, src/team_lib/nccl/xccl_nccl_collective.c:40-231.
+#include <algorithm>
+
+#include "../../cuda/cuda_common.h"
+#include "../../cuda/dev_types.cuh"
+#include "nvl_kernels.cuh"
+
+namespace xccl {
+namespace nvl {
+
+namespace {
+
+using dev::Pack;
+using dev::Traits;
+
+template <typename T> struct Epp {
+    static constexpr int value = 16 / (int)sizeof(T);
+};
+
+struct Range {
+    size_t lo, hi;
+};
+
+__device__ __forceinline__ Range block_range(size_t npacks)
+{
+    size_t per = (npacks + gridDim.x - 1) / gridDim.x;
+    size_t lo  = min((size_t)blockIdx.x * per, npacks);
+    return Range{lo, min(lo + per, npacks)};
+}
+
+__device__ __forceinline__ Range sub_range(Range r, int n, int k)
+{
+    size_t len = r.hi - r.lo;
+    size_t per = (len + n - 1) / n;
+    size_t lo  = min(r.lo + (size_t)k * per, r.hi);
+    return Range{lo, min(lo + per, r.hi)};
+}
+
+template <typename T> __device__ __forceinline__ uint4 as_raw(const Pack<T, Epp<T>::value> &p)
+{
+    return *reinterpret_cast<const uint4 *>(&p);
+}
+template <typename T> __device__ __forceinline__ Pack<T, Epp<T>::value> from_raw(uint4 v)
+{
+    return *reinterpret_cast<Pack<T, Epp<T>::value> *>(&v);
+}
+
+// Pack i of an array of `count` elements that may be unaligned or end inside the pack.
+template <typename T>
+__device__ __forceinline__ uint4 load_pack(const T *p, size_t i, size_t count, bool aligned)
+{
+    constexpr int E  = Epp<T>::value;
+    const size_t  e0 = i * E;
+    if (aligned && e0 + E <= count) {
+        return *reinterpret_cast<const uint4 *>(p + e0);
+    }
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    T    *v   = reinterpret_cast<T *>(&raw);
+#pragma unroll
+    for (int e = 0; e < E; e++) {
+        if (e0 + e < count) v[e] = p[e0 + e];
+    }
+    return raw;
+}
+
+// Stores E output elements (converted from accumulators) as pack i of `dst`.
+template <typename O, int E, typename A>
+__device__ __forceinline__ void store_out(O *dst, size_t i, size_t count, bool aligned, const A (&acc)[E])
+{
+    const size_t e0 = i * E;
+    if (aligned && e0 + E <= count) {
+        Pack<O, E> out;
+#pragma unroll
+        for (int e = 0; e < E; e++) out.v[e] = dev::to_out<O>(acc[e]);
+        *reinterpret_cast<Pack<O, E> *>(dst + e0) = out;
+        return;
+    }
+#pragma unroll
+    for (int e = 0; e < E; e++) {
+        if (e0 + e < count) dst[e0 + e] = dev::to_out<O>(acc[e]);
+    }
+}
+
+template <typename O, int E> __device__ __forceinline__ bool out_aligned(const O *dst)
+{
+    constexpr size_t a = sizeof(Pack<O, E>) >= 16 ? 16 : sizeof(Pack<O, E>);
+    return ((uintptr_t)dst % a) == 0;
+}
+
+// ------------------------------------------------------------------ allreduce: one-shot
+
+template <typename T, typename O, bool kSum>
+__global__ void __launch_bounds__(512) allreduce_one_shot_kernel(World w, Call c)
+{
+    using A          = typename Traits<T>::acc;
+    constexpr int E  = Epp<T>::value;
+    Self          s  = self_begin(w);
+    const T      *src = (const T *)c.src[s.local];
+    O            *dst = (O *)c.dst[s.local];
+    const size_t  npacks = (c.count + E - 1) / E;
+    const size_t  slot   = npacks * 16;
+    const size_t  hoff   = (size_t)c.parity * (w.ws_bytes / 2);
+    const bool    src_al = ((uintptr_t)src & 15) == 0;
+    const bool    dst_al = out_aligned<O, E>(dst);
+    const Range   r      = block_range(npacks);
+
+    for (size_t i = r.lo + threadIdx.x; i < r.hi; i += blockDim.x) {
+        uint4 v = load_pack<T>(src, i, c.count, src_al);
+        for (int p = 0; p < w.size; p++) {
+            st_16(w.ws[p] + hoff + (size_t)s.rank * slot + i * 16, v);
+        }
+    }
+    block_barrier(w, s);
+    if (!s.failed) {
+        const char *mine = w.ws[s.rank] + hoff;
+        for (size_t i = r.lo + threadIdx.x; i < r.hi; i += blockDim.x) {
+            A acc[E];
+            {
+                auto x = from_raw<T>(ld_nc16(mine + i * 16));
+#pragma unroll
+                for (int e = 0; e < E; e++) acc[e] = Traits<T>::up(x.v[e]);
+            }
+            for (int q = 1; q < w.size; q++) {
+                auto y = from_raw<T>(ld_nc16(mine + (size_t)q * slot + i * 16));
+#pragma unroll
+                for (int e = 0; e < E; e++) acc[e] = dev::combine<T, kSum>(c.op, acc[e], Traits<T>::up(y.v[e]));
+            }
+#pragma unroll
+            for (int e = 0; e < E; e++) acc[e] = dev::scaled(acc[e], c.scale, c.do_scale != 0);
+            store_out<O, E>(dst, i, c.count, dst_al, acc);
+        }
+    }
+    self_end(w, s);
+}
+
+// ------------------------------------------------------------------ allreduce: two-shot and NVLS
+
+template <typename T> __device__ __forceinline__ uint4 nvls_reduce(const void *mc);
+template <> __device__ __forceinline__ uint4 nvls_reduce<float>(const void *mc) { return mm_ld_reduce_add_f32x4(mc); }
+template <> __device__ __forceinline__ uint4 nvls_reduce<__nv_bfloat16>(const void *mc) { return mm_ld_reduce_add_bf16x8(mc); }
+template <> __device__ __forceinline__ uint4 nvls_reduce<__half>(const void *mc) { return mm_ld_reduce_add_f16x8(mc); }
+template <typename T> __device__ __forceinline__ uint4 nvls_reduce(const void *) { return make_uint4(0, 0, 0, 0); }
+
+template <typename T, typename O, bool kSum, bool kNvls>
+__global__ void __launch_bounds__(512) allreduce_two_shot_kernel(World w, Call c)
+{
+    using A           = typename Traits<T>::acc;
+    constexpr int E   = Epp<T>::value;
+    Self          s   = self_begin(w);
+    const T      *src = (const T *)c.src[s.local];
+    O            *dst = (O *)c.dst[s.local];
+    const size_t  npacks = (c.count + E - 1) / E;
+    const size_t  half   = w.ws_bytes / 2;
+    const size_t  cap    = half / 16;  // packs per chunk
+    const bool    src_al = ((uintptr_t)src & 15) == 0;
+    const bool    dst_al = out_aligned<O, E>(dst);
+    int           parity = c.parity;
+
+    for (size_t c0 = 0; c0 < npacks; c0 += cap, parity ^= 1) {
+        const size_t n     = min(cap, npacks - c0);
+        const size_t hoff  = (size_t)parity * half;
+        const size_t e_off = c0 * E;
+        const size_t cnt   = c.count - e_off;  // elements from this chunk's start to the end
+        const Range  r     = block_range(n);
+        char        *mine  = w.ws[s.rank] + hoff;
+
+        // 1. my input piece -> my workspace
+        for (size_t i = r.lo + threadIdx.x; i < r.hi; i += blockDim.x) {
+            st_16(mine + i * 16, load_pack<T>(src + e_off, i, cnt, src_al));
+        }
+        block_barrier(w, s);
+        if (s.failed) break;
+
+        // 2. reduce my share of the piece across all ranks, result in place
+        const Range m = sub_range(r, w.size, s.rank);
+        if (kNvls) {
+            char *mc = w.mc_ws + hoff;
+            for (size_t i = m.lo + threadIdx.x; i < m.hi; i += blockDim.x) {
+                uint4 v = nvls_reduce<T>(mc + i * 16);
+                if (c.do_scale) {
+                    auto x = from_raw<T>(v);
+#pragma unroll
+                    for (int e = 0; e < E; e++) x.v[e] = Traits<T>::down(dev::scaled(Traits<T>::up(x.v[e]), c.scale, true));
+                    v = as_raw<T>(x);
+                }
+                mm_st_16(mc + i * 16, v);
+            }
+        } else {
+            for (size_t i = m.lo + threadIdx.x; i < m.hi; i += blockDim.x) {
+                uint4 raw[kMaxRanks];
+#pragma unroll
+                for (int p = 0; p < kMaxRanks; p++) {
+                    if (p < w.size) raw[p] = ld_nc16(w.ws[p] + hoff + i * 16);
+                }
+                A acc[E];
+                {
+                    auto x = from_raw<T>(raw[0]);
+#pragma unroll
+                    for (int e = 0; e < E; e++) acc[e] = Traits<T>::up(x.v[e]);
+                }
+#pragma unroll
+                for (int p = 1; p < kMaxRanks; p++) {
+                    if (p < w.size) {
+                        auto y = from_raw<T>(raw[p]);
+#pragma unroll
+                        for (int e = 0; e < E; e++) acc[e] = dev::combine<T, kSum>(c.op, acc[e], Traits<T>::up(y.v[e]));
+                    }
+                }
+                Pack<T, E> out;
+#pragma unroll
+                for (int e = 0; e < E; e++) out.v[e] = Traits<T>::down(dev::scaled(acc[e], c.scale, c.do_scale != 0));
+                st_16(mine + i * 16, as_raw<T>(out));
+            }
+        }
+        block_barrier(w, s);
+        if (s.failed) break;
+
+        // 3. gather the reduced shares. NVLS already broadcast them into my workspace.
+        for (int q = 0; q < w.size; q++) {
+            const int   p    = (s.rank + q) % w.size;  // start with my own share, spread the peers
+            const Range g    = sub_range(r, w.size, p);
+            const char *from = (kNvls ? mine : w.ws[p] + hoff);
+            for (size_t i = g.lo + threadIdx.x; i < g.hi; i += blockDim.x) {
+                auto x = from_raw<T>(ld_nc16(from + i * 16));
+                A    acc[E];
+#pragma unroll
+                for (int e = 0; e < E; e++) acc[e] = Traits<T>::up(x.v[e]);
+                store_out<O, E>(dst + e_off, i, cnt, dst_al, acc);
+            }
+        }
+    }
+    self_end(w, s);
+}
+
+// ------------------------------------------------------------------ reduce (to root), reduce-scatter
+
+template <typename T, typename O, bool kSum, bool kScatter>
+__global__ void __launch_bounds__(512) reduce_kernel(World w, Call c)
+{
+    using A           = typename Traits<T>::acc;
+    constexpr int E   = Epp<T>::value;
+    Self          s   = self_begin(w);
+    const T      *src = (const T *)c.src[s.local];
+    O            *dst = (O *)c.dst[s.local];
+    const int     nseg   = kScatter ? w.size : 1;  // segments each rank contributes
+    const size_t  npacks = (c.count + E - 1) / E;  // packs per segment
+    const size_t  half   = w.ws_bytes / 2;
+    const size_t  cap    = half / 16 / nseg;
+    const bool    dst_al = out_aligned<O, E>(dst);
+    const int     my_seg = kScatter ? s.rank : 0;
+    const bool    i_reduce = kScatter || s.rank == c.root;
+    int           parity = c.parity;
+
+    for (size_t c0 = 0; c0 < npacks; c0 += cap, parity ^= 1) {
+        const size_t n     = min(cap, npacks - c0);
+        const size_t hoff  = (size_t)parity * half;
+        const size_t e_off = c0 * E;
+        const size_t cnt   = c.count - e_off;
+        const Range  r     = block_range(n);
+        char        *mine  = w.ws[s.rank] + hoff;
+        for (int q = 0; q < nseg; q++) {
+            const T   *seg = src + (size_t)q * c.count + e_off;
+            const bool al  = ((uintptr_t)seg & 15) == 0;
+            for (size_t i = r.lo + threadIdx.x; i < r.hi; i += blockDim.x) {
+                st_16(mine + ((size_t)q * n + i) * 16, load_pack<T>(seg, i, cnt, al));
+            }
+        }
+        block_barrier(w, s);
+        if (s.failed) break;
+        if (i_reduce) {
+            for (size_t i = r.lo + threadIdx.x; i < r.hi; i += blockDim.x) {
+                uint4 raw[kMaxRanks];
+#pragma unroll
+                for (int p = 0; p < kMaxRanks; p++) {
+                    if (p < w.size) raw[p] = ld_nc16(w.ws[p] + hoff + ((size_t)my_seg * n + i) * 16);
+                }
+                A acc[E];
+                {
+                    auto x = from_raw<T>(raw[0]);
+#pragma unroll
+                    for (int e = 0; e < E; e++) acc[e] = Traits<T>::up(x.v[e]);
+                }
+#pragma unroll
+                for (int p = 1; p < kMaxRanks; p++) {
+                    if (p < w.size) {
+                        auto y = from_raw<T>(raw[p]);
+#pragma unroll
+                        for (int e = 0; e < E; e++) acc[e] = dev::combine<T, kSum>(c.op, acc[e], Traits<T>::up(y.v[e]));
+                    }
+                }
+#pragma unroll
+                for (int e = 0; e < E; e++) acc[e] = dev::scaled(acc[e], c.scale, c.do_scale != 0);
+                store_out<O, E>(dst + e_off, i, cnt, dst_al, acc);
+            }
+        }
+    }
+    self_end(w, s);
+}
+
+// ------------------------------------------------------------------ byte movers
+
+enum MoveKind { MV_BCAST = 0, MV_ALLGATHER = 1, MV_ALLTOALL = 2 };
+
+using Byte = unsigned char;
+
+__device__ __forceinline__ void store_bytes(Byte *dst, size_t i, size_t bytes, bool aligned, uint4 v)
+{
+    const size_t b0 = i * 16;
+    if (aligned && b0 + 16 <= bytes) {
+        *reinterpret_cast<uint4 *>(dst + b0) = v;
+        return;
+    }
+    const Byte *s = reinterpret_cast<const Byte *>(&v);
+    for (int e = 0; e < 16; e++) {
+        if (b0 + e < bytes) dst[b0 + e] = s[e];
+    }
+}
+
+template <int KIND> __global__ void __launch_bounds__(512) mover_kernel(World w, Call c)
+{
+    Self          s   = self_begin(w);
+    const Byte   *src = (const Byte *)c.src[s.local];
+    Byte         *dst = (Byte *)c.dst[s.local];
+    const size_t  seg_bytes = (KIND == MV_ALLGATHER) ? c.len / w.size : c.len;
+    const int     nseg_ws   = (KIND == MV_ALLTOALL) ? w.size : 1;
+    const size_t  npacks    = (seg_bytes + 15) / 16;
+    const size_t  half      = w.ws_bytes / 2;
+    const size_t  cap       = half / 16 / nseg_ws;
+    int           parity    = c.parity;
+
+    for (size_t c0 = 0; c0 < npacks; c0 += cap, parity ^= 1) {
+        const size_t n     = min(cap, npacks - c0);
+        const size_t hoff  = (size_t)parity * half;
+        const size_t b_off = c0 * 16;
+        const size_t left  = seg_bytes - b_off;
+        const Range  r     = block_range(n);
+        char        *mine  = w.ws[s.rank] + hoff;
+
+        if (KIND != MV_BCAST || s.rank == c.root) {
+            for (int q = 0; q < nseg_ws; q++) {
+                const Byte *seg = src + (size_t)q * seg_bytes + b_off;
+                const bool  al  = ((uintptr_t)seg & 15) == 0;
+                Byte       *own = nullptr;  // bcast root with a separate dst keeps a local copy too
+                if (KIND == MV_BCAST && dst != src) own = dst + b_off;
+                const bool own_al = ((uintptr_t)own & 15) == 0;
+                for (size_t i = r.lo + threadIdx.x; i < r.hi; i += blockDim.x) {
+                    uint4 v = load_pack<Byte>(seg, i, left, al);
+                    st_16(mine + ((size_t)q * n + i) * 16, v);
+                    if (own != nullptr) store_bytes(own, i, left, own_al, v);
+                }
+            }
+        }
+        block_barrier(w, s);
+        if (s.failed) break;
+
+        if (KIND == MV_BCAST) {
+            if (s.rank != c.root) {
+                Byte      *out = dst + b_off;
+                const bool al  = ((uintptr_t)out & 15) == 0;
+                for (size_t i = r.lo + threadIdx.x; i < r.hi; i += blockDim.x) {
+                    store_bytes(out, i, left, al, ld_nc16(w.ws[c.root] + hoff + i * 16));
+                }
+            }
+        } else {
+            for (int q = 0; q < w.size; q++) {
+                const int   p    = (s.rank + q) % w.size;
+                const int   seg  = (KIND == MV_ALLTOALL) ? s.rank : 0;
+                const char *from = w.ws[p] + hoff + (size_t)seg * n * 16;
+                Byte       *out  = dst + (size_t)p * seg_bytes + b_off;
+                const bool  al   = ((uintptr_t)out & 15) == 0;
+                for (size_t i = r.lo + threadIdx.x; i < r.hi; i += blockDim.x) {
+                    store_bytes(out, i, left, al, ld_nc16(from + i * 16));
+                }
+            }
+        }
+    }
+    self_end(w, s);
+}
+
+// alltoallv: one chunk; a header per block index publishes the sender's per-destination bytes.
+constexpr size_t kVHeaderBytes = (size_t)kMaxBlocks * kMaxRanks * 4;
+
+__global__ void __launch_bounds__(512) alltoallv_kernel(World w, Call c)
+{
+    Self            s    = self_begin(w);
+    const Byte     *src  = (const Byte *)c.src[s.local];
+    Byte           *dst  = (Byte *)c.dst[s.local];
+    const uint32_t *meta = c.vmeta[s.local];
+    const uint32_t *sc = meta, *sd = meta + w.size, *dc = meta + 2 * w.size, *dd = meta + 3 * w.size;
+    const size_t    hoff = (size_t)c.parity * (w.ws_bytes / 2);
+    char           *mine = w.ws[s.rank] + hoff;
+    uint32_t       *hdr  = reinterpret_cast<uint32_t *>(mine) + (size_t)blockIdx.x * kMaxRanks;
+
+    if ((int)threadIdx.x < w.size) hdr[threadIdx.x] = sc[threadIdx.x] * (uint32_t)c.src_es;
+    size_t off = kVHeaderBytes;
+    for (int q = 0; q < w.size; q++) {
+        const size_t bytes = (size_t)sc[q] * c.src_es;
+        const size_t n     = (bytes + 15) / 16;
+        const Byte  *seg   = src + (size_t)sd[q] * c.src_es;
+        const bool   al    = ((uintptr_t)seg & 15) == 0;
+        const Range  r     = block_range(n);
+        for (size_t i = r.lo + threadIdx.x; i < r.hi; i += blockDim.x) {
+            st_16(mine + off + i * 16, load_pack<Byte>(seg, i, bytes, al));
+        }
+        off += n * 16;
+    }
+    block_barrier(w, s);
+    if (!s.failed) {
+        for (int q = 0; q < w.size; q++) {
+            const int       p    = (s.rank + q) % w.size;
+            const char     *peer = w.ws[p] + hoff;
+            const uint32_t *ph   = reinterpret_cast<const uint32_t *>(peer) + (size_t)blockIdx.x * kMaxRanks;
+            size_t          poff = kVHeaderBytes;
+            for (int j = 0; j < s.rank; j++) poff += (((size_t)ld_relaxed_sys(ph + j) + 15) / 16) * 16;
+            const size_t sent  = ld_relaxed_sys(ph + s.rank);
+            const size_t want  = (size_t)dc[p] * c.dst_es;
+            const size_t bytes = min(sent, want);
+            const size_t n     = (sent + 15) / 16;  // the sender's partition
+            Byte        *out   = dst + (size_t)dd[p] * c.dst_es;
+            const bool   al    = ((uintptr_t)out & 15) == 0;
+            const Range  r     = block_range(n);
+            for (size_t i = r.lo + threadIdx.x; i < r.hi; i += blockDim.x) {
+                store_bytes(out, i, bytes, al, ld_nc16(peer + poff + i * 16));
+            }
+        }
+    }
+    self_end(w, s);
+}
+
+// ------------------------------------------------------------------ synchronisation only
+
+__global__ void sync_kernel(World w, Call c, int kind)
+{
+    Self s = self_begin(w);
+    if (kind == XCCL_BARRIER) {
+        block_barrier(w, s);
+    } else {
+        s.epoch++;
+        int bad = 0;
+        const bool to_root = (kind == XCCL_FANIN);
+        if (s.rank == c.root) {
+            if ((int)threadIdx.x < w.size && (int)threadIdx.x != c.root) {
+                if (to_root) {
+                    if (!wait_rank(w, s, threadIdx.x, s.epoch)) {
+                        record_failure(w, s, NVL_TIMEOUT, threadIdx.x, s.epoch);
+                        bad = 1;
+                    }
+                } else {
+                    signal_rank(w, s, threadIdx.x, s.epoch);
+                }
+            }
+        } else if (threadIdx.x == 0) {
+            if (to_root) {
+                signal_rank(w, s, c.root, s.epoch);
+            } else if (!wait_rank(w, s, c.root, s.epoch)) {
+                record_failure(w, s, NVL_TIMEOUT, c.root, s.epoch);
+                bad = 1;
+            }
+        }
+        s.failed = __syncthreads_or(bad) != 0;
+    }
+    self_end(w, s);
+}
+
+__global__ void timeout_probe_kernel(World w, unsigned long long budget_ns)
+{
+    Self s = self_begin(w);
+    if (threadIdx.x == 0) {
+        // the last general counter is reserved for this probe and is never written
+        const uint32_t *never = w.pad[s.rank] + kPadCounterOff + kPadCounterWords - 1;
+        if (!wait_flag(never, 1u, budget_ns)) record_failure(w, s, NVL_TIMEOUT, s.rank, 1u);
+    }
+    self_end(w, s);
+}
+
+// ------------------------------------------------------------------ launch helpers
+
+template <typename... Args>
+xccl_status_t launch(void (*kernel)(Args...), dim3 grid, dim3 block, bool cooperative, cudaStream_t stream, Args... args)
+{
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim          = grid;
+    cfg.blockDim         = block;
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream           = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id              = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = cooperative ? 1 : 0;
+    cfg.attrs               = attr;
+    cfg.numAttrs            = 1;
+    XCCL_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, args...));
+    return XCCL_OK;
+}
+
+// How many blocks (per rank) may run: bounded by the pad layout, the work, and - when all ranks
+// share one cooperative launch - by what fits on the device at once.
+template <typename K>
+int pick_blocks(K kernel, const World &w, const LaunchCfg &cfg, size_t packs, int packs_per_thread)
+{
+    int blocks = cfg.blocks;
+    if (blocks <= 0) {
+        size_t per_block = (size_t)cfg.threads * (size_t)packs_per_thread;
+        blocks           = (int)std::min<size_t>((packs + per_block - 1) / per_block, (size_t)cfg.max_blocks);
+    }
+    blocks = std::max(1, std::min(blocks, std::min(cfg.max_blocks, kMaxBlocks)));
+    if (cfg.cooperative) {
+        int dev = 0, sms = 0, per_sm = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, cfg.threads, 0);
+        int fit = std::max(1, (sms * std::max(per_sm, 1)) / std::max(w.n_local, 1));
+        blocks  = std::min(blocks, fit);
+    }
+    return blocks;
+}
+
+bool reduce_op_ok(xccl_dt_t dt, xccl_op_t op)
+{
+    bool arith = (op == XCCL_OP_MAX || op == XCCL_OP_MIN || op == XCCL_OP_SUM || op == XCCL_OP_PROD);
+    bool logic = (op >= XCCL_OP_AND && op <= XCCL_OP_BXOR);
+    bool is_f  = (dt == XCCL_DT_FLOAT16 || dt == XCCL_DT_FLOAT32 || dt == XCCL_DT_FLOAT64 || dt == XCCL_DT_BFLOAT16);
+    return is_f ? arith : (arith || logic);
+}
+
+template <typename T, typename O>
+xccl_status_t allreduce_typed(const World &w, const Call &c, Alg alg, const LaunchCfg &cfg, cudaStream_t stream)
+{
+    constexpr int E      = Epp<T>::value;
+    const size_t  npacks = (c.count + E - 1) / E;
+    const bool    sum    = (c.op == XCCL_OP_SUM);
+    dim3          block((unsigned)cfg.threads);
+    if (alg == ALG_ONE_SHOT) {
+        if (npacks * 16 * (size_t)w.size > w.ws_bytes / 2) return XCCL_ERR_BUFFER_TOO_SMALL;
+        auto k      = sum ? allreduce_one_shot_kernel<T, O, true> : allreduce_one_shot_kernel<T, O, false>;
+        int  blocks = pick_blocks(k, w, cfg, npacks, 2);
+        return launch(k, dim3((unsigned)blocks, (unsigned)w.n_local), block, cfg.cooperative, stream, w, c);
+    }
+    if (alg == ALG_NVLS) {
+        constexpr bool can = std::is_same<T, float>::value || std::is_same<T, __half>::value ||
+                             std::is_same<T, __nv_bfloat16>::value;
+        if (!can || !sum || w.mc_ws == nullptr) return XCCL_ERR_UNSUPPORTED;
+        auto k      = allreduce_two_shot_kernel<T, O, true, true>;
+        int  blocks = pick_blocks(k, w, cfg, npacks, 8);
+        return launch(k, dim3((unsigned)blocks, (unsigned)w.n_local), block, cfg.cooperative, stream, w, c);
+    }
+    auto k      = sum ? allreduce_two_shot_kernel<T, O, true, false> : allreduce_two_shot_kernel<T, O, false, false>;
+    int  blocks = pick_blocks(k, w, cfg, npacks, 8);
+    return launch(k, dim3((unsigned)blocks, (unsigned)w.n_local), block, cfg.cooperative, stream, w, c);
+}
+
+template <typename T, typename O, bool kScatter>
+xccl_status_t reduce_typed(const World &w, const Call &c, const LaunchCfg &cfg, cudaStream_t stream)
+{
+    constexpr int E      = Epp<T>::value;
+    const size_t  npacks = (c.count + E - 1) / E;
+    const bool    sum    = (c.op == XCCL_OP_SUM);
+    auto          k      = sum ? reduce_kernel<T, O, true, kScatter> : reduce_kernel<T, O, false, kScatter>;
+    int           blocks = pick_blocks(k, w, cfg, npacks * (kScatter ? w.size : 1), 8);
+    return launch(k, dim3((unsigned)blocks, (unsigned)w.n_local), dim3((unsigned)cfg.threads), cfg.cooperative, stream,
+                  w, c);
+}
+
+}  // namespace
+
+bool nvls_supported(xccl_dt_t dt, xccl_op_t op)
+{
+    return op == XCCL_OP_SUM && (dt == XCCL_DT_FLOAT32 || dt == XCCL_DT_FLOAT16 || dt == XCCL_DT_BFLOAT16);
+}
+
+size_t one_shot_limit(const World &w) { return w.ws_bytes / 2 / (size_t)std::max(w.size, 1); }
+
+xccl_status_t launch_allreduce(const World &w, const Call &c, xccl_dt_t dt, xccl_dt_t out_dt, Alg alg,
+                               const LaunchCfg &cfg, cudaStream_t stream)
+{
+    if (!reduce_op_ok(dt, (xccl_op_t)c.op)) return XCCL_ERR_UNSUPPORTED;
+    if (c.count == 0) return XCCL_OK;
+    return XCCL_DISPATCH_IO(dt, out_dt, return (allreduce_typed<T, O>(w, c, alg, cfg, stream)););
+}
+
+xccl_status_t launch_reduce(const World &w, const Call &c, xccl_dt_t dt, xccl_dt_t out_dt, const LaunchCfg &cfg,
+                            cudaStream_t stream)
+{
+    if (!reduce_op_ok(dt, (xccl_op_t)c.op)) return XCCL_ERR_UNSUPPORTED;
+    if (c.count == 0) return XCCL_OK;
+    return XCCL_DISPATCH_IO(dt, out_dt, return (reduce_typed<T, O, false>(w, c, cfg, stream)););
+}
+
+xccl_status_t launch_reduce_scatter(const World &w, const Call &c, xccl_dt_t dt, xccl_dt_t out_dt,
+                                    const LaunchCfg &cfg, cudaStream_t stream)
+{
+    if (!reduce_op_ok(dt, (xccl_op_t)c.op)) return XCCL_ERR_UNSUPPORTED;
+    if (c.count == 0) return XCCL_OK;
+    return XCCL_DISPATCH_IO(dt, out_dt, return (reduce_typed<T, O, true>(w, c, cfg, stream)););
+}
+
+template <int KIND>
+static xccl_status_t mover(const World &w, const Call &c, const LaunchCfg &cfg, cudaStream_t stream)
+{
+    size_t seg    = (KIND == MV_ALLGATHER) ? c.len / (size_t)w.size : c.len;
+    size_t npacks = (seg + 15) / 16;
+    if (npacks == 0) return XCCL_OK;
+    auto k      = mover_kernel<KIND>;
+    int  blocks = pick_blocks(k, w, cfg, npacks * (KIND == MV_BCAST ? 1 : (size_t)w.size), 8);
+    return launch(k, dim3((unsigned)blocks, (unsigned)w.n_local), dim3((unsigned)cfg.threads), cfg.cooperative, stream,
+                  w, c);
+}
+
+xccl_status_t launch_bcast(const World &w, const Call &c, const LaunchCfg &cfg, cudaStream_t stream)
+{
+    return mover<MV_BCAST>(w, c, cfg, stream);
+}
+xccl_status_t launch_allgather(const World &w, const Call &c, const LaunchCfg &cfg, cudaStream_t stream)
+{
+    return mover<MV_ALLGATHER>(w, c, cfg, stream);
+}
+xccl_status_t launch_alltoall(const World &w, const Call &c, const LaunchCfg &cfg, cudaStream_t stream)
+{
+    return mover<MV_ALLTOALL>(w, c, cfg, stream);
+}
+
+xccl_status_t launch_alltoallv(const World &w, const Call &c, size_t max_src_bytes, const LaunchCfg &cfg,
+                               cudaStream_t stream)
+{
+    // every segment is rounded up to a pack; the whole exchange must fit one workspace half
+    size_t need = kVHeaderBytes + max_src_bytes + (size_t)w.size * 16;
+    if (need > w.ws_bytes / 2) return XCCL_ERR_BUFFER_TOO_SMALL;
+    auto k      = alltoallv_kernel;
+    int  blocks = pick_blocks(k, w, cfg, (max_src_bytes + 15) / 16, 8);
+    return launch(k, dim3((unsigned)blocks, (unsigned)w.n_local), dim3((unsigned)cfg.threads), cfg.cooperative, stream,
+                  w, c);
+}
+
+xccl_status_t launch_sync(const World &w, const Call &c, int kind, const LaunchCfg &cfg, cudaStream_t stream)
+{
+    return launch(sync_kernel, dim3(1, (unsigned)w.n_local), dim3(32), cfg.cooperative, stream, w, c, kind);
+}
+
+xccl_status_t launch_timeout_probe(const World &w, unsigned long long budget_ns, cudaStream_t stream)
+{
+    return launch(timeout_probe_kernel, dim3(1, (unsigned)w.n_local), dim3(32), false, stream, w, budget_ns);
+}
+
+}  // namespace nvl
+}  // namespace xccl

@@ -1,0 +1,273 @@
+"""GPU tests of the hand-written kernels against plain PyTorch fp32 references.
+
+The multi-rank NVLink kernels run here through the single-GPU emulation (one cooperative launch
+whose blockIdx.y is the rank); the real multi-process path has its own test module.
+"""
+import ctypes as C
+
+import pytest
+import torch
+
+from xccl_b200 import _capi as K
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    torch.cuda.set_device(0)
+    return torch.device("cuda:0")
+
+
+def _loaded_native():
+    # fail loudly if the native library is not the thing that runs
+    with open("/proc/self/maps") as f:
+        assert "libxccl.so" in f.read(), "libxccl.so is not loaded"
+
+
+# ----------------------------------------------------------------------------- local reduce kernels
+@pytest.mark.parametrize("dtype,dt", [(torch.float32, K.DT_FLOAT32), (torch.bfloat16, K.DT_BFLOAT16),
+                                      (torch.float16, K.DT_FLOAT16), (torch.int32, K.DT_INT32),
+                                      (torch.int64, K.DT_INT64), (torch.uint8, K.DT_UINT8)])
+@pytest.mark.parametrize("count", [1, 7, 4099, 1 << 20])
+def test_reduce_multi_kernel(dev, dtype, dt, count):
+    from xccl_b200.ops import emu  # noqa: F401  (declares optional prototypes)
+    L = K.load()
+    L.xccl_cuda_reduce_multi.restype = C.c_int
+    L.xccl_cuda_reduce_multi.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t,
+                                         C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p]
+    g = torch.Generator(device="cpu").manual_seed(0)
+    nvec = 5
+    hi = 4 if dtype == torch.uint8 else 9
+    a = torch.randint(0, hi, (count,), generator=g).to(dtype).to(dev)
+    v = torch.randint(0, hi, (nvec, count), generator=g).to(dtype).to(dev)
+    out = torch.empty_like(a)
+    for op, ref in ((K.OP_SUM, lambda x: x.sum(0)), (K.OP_MAX, lambda x: x.max(0).values)):
+        st = L.xccl_cuda_reduce_multi(a.data_ptr(), v.data_ptr(), out.data_ptr(), nvec, count,
+                                      count * a.element_size(), dt, op, 1.0, K.DT_UNSUPPORTED,
+                                      torch.cuda.current_stream().cuda_stream)
+        assert st == K.OK
+        allv = torch.cat([a[None], v]).to(torch.float64 if dtype.is_floating_point else torch.int64)
+        want = ref(allv).to(dtype)
+        torch.cuda.synchronize()
+        assert torch.equal(out, want), (dtype, op, count)
+    _loaded_native()
+
+
+def test_reduce_scale_and_cast(dev):
+    L = K.load()
+    L.xccl_cuda_reduce_multi.restype = C.c_int
+    L.xccl_cuda_reduce_multi.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t,
+                                         C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p]
+    n = 100003
+    a = torch.randn(n, device=dev)
+    v = torch.randn(3, n, device=dev)
+    out = torch.empty(n, device=dev, dtype=torch.bfloat16)
+    st = L.xccl_cuda_reduce_multi(a.data_ptr(), v.data_ptr(), out.data_ptr(), 3, n, n * 4, K.DT_FLOAT32, K.OP_SUM,
+                                  0.25, K.DT_BFLOAT16, torch.cuda.current_stream().cuda_stream)
+    assert st == K.OK
+    want = ((a + v.sum(0)) * 0.25).to(torch.bfloat16)
+    torch.cuda.synchronize()
+    torch.testing.assert_close(out.float(), want.float(), rtol=1e-2, atol=1e-2)
+
+
+def test_stream_hold_times_out_without_hanging(dev):
+    L = K.load()
+    L.xccl_cuda_hold_timeout_probe.restype = C.c_int
+    L.xccl_cuda_hold_timeout_probe.argtypes = [C.c_int, C.POINTER(C.c_float)]
+    ms = C.c_float()
+    st = L.xccl_cuda_hold_timeout_probe(50, C.byref(ms))
+    assert st == K.ERR_TIMED_OUT
+    assert 40.0 <= ms.value < 2000.0
+    # the context is still usable
+    assert float(torch.ones(4, device=dev).sum()) == 4.0
+
+
+# ----------------------------------------------------------------------------- emulated NVLink team
+@pytest.fixture(scope="module")
+def world4(dev):
+    from xccl_b200.ops.emu import EmuWorld
+    w = EmuWorld(4, 8 << 20)
+    yield w
+    w.close()
+
+
+def _ints(n, count, dtype, dev, seed):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return [torch.randint(-8, 9, (count,), generator=g).to(dtype).to(dev) for _ in range(n)]
+
+
+@pytest.mark.parametrize("alg", [K.NVLINK_ALG_ONE_SHOT, K.NVLINK_ALG_TWO_SHOT])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.int32])
+@pytest.mark.parametrize("count", [1, 33, 4096, 262147])
+def test_emu_allreduce(world4, dev, alg, dtype, count):
+    if alg == K.NVLINK_ALG_ONE_SHOT and count * 4 * 4 > (4 << 20):
+        pytest.skip("one-shot needs size x message bytes in one workspace half")
+    srcs = _ints(4, count, dtype, dev, seed=count)
+    dsts = [torch.full_like(s, 99) for s in srcs]
+    world4.allreduce(srcs, dsts, alg=alg)
+    want = torch.stack([s.double() for s in srcs]).sum(0).to(dtype)
+    for d in dsts:
+        assert torch.equal(d, want)
+    # max
+    world4.allreduce(srcs, dsts, op=K.OP_MAX, alg=alg)
+    want = torch.stack(srcs).max(0).values
+    for d in dsts:
+        assert torch.equal(d, want)
+
+
+def test_emu_allreduce_chunks_through_small_workspace(world4, dev):
+    # 12 MB per rank through a workspace half of 4 MB: three chunks, alternating halves
+    count = 3 << 20
+    srcs = [torch.randn(count, device=dev) for _ in range(4)]
+    dsts = [torch.empty_like(s) for s in srcs]
+    world4.allreduce(srcs, dsts, alg=K.NVLINK_ALG_TWO_SHOT)
+    want = torch.stack(srcs).double().sum(0).float()
+    for d in dsts:
+        torch.testing.assert_close(d, want, rtol=1e-5, atol=1e-5)
+    assert torch.equal(dsts[0], dsts[3])  # every rank adds in the same order
+
+
+def test_emu_allreduce_fused_scale_cast_and_unaligned(world4, dev):
+    count = 10007
+    base = [torch.randn(count + 3, device=dev) for _ in range(4)]
+    srcs = [b[3:] for b in base]  # 12-byte offset: not 16-byte aligned
+    dsts = [torch.empty(count + 1, device=dev, dtype=torch.bfloat16)[1:] for _ in range(4)]
+    for alg in (K.NVLINK_ALG_ONE_SHOT, K.NVLINK_ALG_TWO_SHOT):
+        world4.allreduce(srcs, dsts, alg=alg, scale=0.25)
+        want = (torch.stack(srcs).double().sum(0) * 0.25).float()
+        for d in dsts:
+            torch.testing.assert_close(d.float(), want, rtol=1e-2, atol=2e-2)
+
+
+def test_emu_reduce_and_reduce_scatter(world4, dev):
+    count = 5000
+    srcs = _ints(4, count, torch.float32, dev, seed=3)
+    for root in range(4):
+        dsts = [torch.full((count,), -1.0, device=dev) for _ in range(4)]
+        world4.reduce(srcs, dsts, root)
+        assert torch.equal(dsts[root], torch.stack(srcs).sum(0))
+        for r in range(4):
+            if r != root:
+                assert torch.all(dsts[r] == -1.0)
+    per = 1237
+    srcs = _ints(4, per * 4, torch.int32, dev, seed=4)
+    dsts = [torch.zeros(per, dtype=torch.int32, device=dev) for _ in range(4)]
+    world4.reduce_scatter(srcs, dsts)
+    full = torch.stack(srcs).sum(0)
+    for r in range(4):
+        assert torch.equal(dsts[r], full[r * per:(r + 1) * per].to(torch.int32))
+
+
+def test_emu_bcast_allgather_alltoall(world4, dev):
+    n = 4
+    for nbytes in (1, 13, 4096, 3 << 20):
+        bufs = [torch.randint(0, 255, (nbytes,), dtype=torch.uint8, device=dev) for _ in range(n)]
+        root = 2
+        want = bufs[root].clone()
+        world4.bcast(bufs, bufs, root)
+        for b in bufs:
+            assert torch.equal(b, want)
+    for per in (3, 1000, 1 << 20):
+        srcs = [torch.randint(0, 255, (per,), dtype=torch.uint8, device=dev) for _ in range(n)]
+        dsts = [torch.zeros(per * n, dtype=torch.uint8, device=dev) for _ in range(n)]
+        world4.allgather(srcs, dsts)
+        for d in dsts:
+            assert torch.equal(d, torch.cat(srcs))
+    for per in (1, 1024, 100003):
+        srcs = [torch.randn(per * n, device=dev) for _ in range(n)]
+        dsts = [torch.zeros(per * n, device=dev) for _ in range(n)]
+        world4.alltoall(srcs, dsts)
+        for r in range(n):
+            want = torch.cat([srcs[s][r * per:(r + 1) * per] for s in range(n)])
+            assert torch.equal(dsts[r], want)
+
+
+def test_emu_alltoallv(world4, dev):
+    n = 4
+    sc = [[(s * 3 + d * 5 + 1) for d in range(n)] for s in range(n)]  # elements rank s sends to rank d
+    srcs, dsts, metas, keep = [], [], [], []
+    for r in range(n):
+        scounts = sc[r]
+        sdispl = [sum(scounts[:d]) for d in range(n)]
+        rcounts = [sc[s][r] for s in range(n)]
+        rdispl = [sum(rcounts[:s]) for s in range(n)]
+        srcs.append(torch.cat([torch.full((scounts[d],), float(r * 10 + d), device=dev) for d in range(n)]))
+        dsts.append(torch.zeros(sum(rcounts), device=dev))
+        metas.append(torch.tensor(scounts + sdispl + rcounts + rdispl, dtype=torch.int32, device=dev))
+        keep.append((rcounts,))
+    world4.alltoallv(srcs, dsts, metas, max(s.numel() for s in srcs) * 4)
+    for r in range(n):
+        want = torch.cat([torch.full((sc[s][r],), float(s * 10 + r), device=dev) for s in range(n)])
+        assert torch.equal(dsts[r], want)
+
+
+def test_emu_sync_collectives_and_bounded_wait(world4, dev):
+    for _ in range(3):
+        world4.barrier()
+    for root in range(4):
+        world4.fanin(root)
+        world4.fanout(root)
+    st, ms, st4 = world4.timeout_probe(30)
+    assert st == K.ERR_TIMED_OUT and st4[0] == 1
+    assert 20.0 <= ms < 2000.0
+    # the team still works after the probe
+    srcs = _ints(4, 100, torch.float32, dev, seed=9)
+    dsts = [torch.empty_like(s) for s in srcs]
+    world4.allreduce(srcs, dsts)
+    assert torch.equal(dsts[1], torch.stack(srcs).sum(0))
+
+
+def test_emu_allreduce_eight_ranks(dev):
+    from xccl_b200.ops.emu import EmuWorld
+    w = EmuWorld(8, 8 << 20)
+    try:
+        for count, alg in ((1000, K.NVLINK_ALG_ONE_SHOT), (300000, K.NVLINK_ALG_TWO_SHOT)):
+            srcs = _ints(8, count, torch.bfloat16, dev, seed=count)
+            dsts = [torch.empty_like(s) for s in srcs]
+            w.allreduce(srcs, dsts, alg=alg)
+            want = torch.stack([s.float() for s in srcs]).sum(0).to(torch.bfloat16)
+            for d in dsts:
+                assert torch.equal(d, want)
+    finally:
+        w.close()
+
+
+# ----------------------------------------------------------------------------- tcgen05 GEMM
+@pytest.mark.parametrize("M,N,K_", [(128, 256, 64), (256, 512, 256), (384, 768, 1024), (1000, 264, 520)])
+def test_gemm_bf16_matches_fp32_reference(dev, M, N, K_):
+    from xccl_b200.ops import gemm
+    a = (torch.randn(M, K_, device=dev) * 0.5).to(torch.bfloat16)
+    b = (torch.randn(N, K_, device=dev) * 0.5).to(torch.bfloat16)
+    out = gemm.gemm_bf16(a, b)
+    assert gemm.last_error() == 0
+    want = a.float() @ b.float().t()
+    torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2 * K_ ** 0.5)
+    _loaded_native()
+
+
+def test_gemm_swiglu_matches_fp32_reference(dev):
+    from xccl_b200.ops import gemm
+    M, F, K_ = 512, 384, 512
+    a = (torch.randn(M, K_, device=dev) * 0.5).to(torch.bfloat16)
+    wg = (torch.randn(F, K_, device=dev) * 0.05).to(torch.bfloat16)
+    wu = (torch.randn(F, K_, device=dev) * 0.05).to(torch.bfloat16)
+    out = gemm.gemm_swiglu(a, wg, wu)
+    assert gemm.last_error() == 0
+    g = a.float() @ wg.float().t()
+    u = a.float() @ wu.float().t()
+    want = torch.nn.functional.silu(g) * u
+    torch.testing.assert_close(out.float(), want, rtol=3e-2, atol=3e-2)
+
+
+def test_gemm_many_tiles_persistent_schedule(dev):
+    from xccl_b200.ops import gemm
+    M, N, K_ = 4096, 4096, 512   # 512 tiles over 148 CTAs: several tiles per CTA, both accumulators in use
+    a = (torch.randn(M, K_, device=dev) * 0.3).to(torch.bfloat16)
+    b = (torch.randn(N, K_, device=dev) * 0.3).to(torch.bfloat16)
+    out = gemm.gemm_bf16(a, b)
+    assert gemm.last_error() == 0
+    want = a.float() @ b.float().t()
+    torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=0.5)
