@@ -13,6 +13,7 @@
 // cooperative launch on one GPU, gridDim.y = ranks), exactly like the NVLink collectives.
 #pragma once
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
 #include "../tl/nvlink/nvl_device.cuh"

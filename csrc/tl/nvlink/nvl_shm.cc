@@ -217,14 +217,14 @@ xccl_status_t SymmetricRegion::setup(const OobGroup &g, size_t want_bytes, bool 
     bytes     = round_up(want_bytes, gran);
     mcp.size  = bytes;
     mc_bytes_ = bytes;
-    CUaccessDesc access{};
-    access.location = prop.location;
-    access.flags    = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+    CUmemAccessDesc acc_desc{};
+    acc_desc.location = prop.location;
+    acc_desc.flags    = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
     XCCL_CU_CHECK(cuMemCreate(&handles_[(size_t)rank], bytes, &prop, 0));
     CUdeviceptr va = 0;
     XCCL_CU_CHECK(cuMemAddressReserve(&va, bytes, gran, 0, 0));
     XCCL_CU_CHECK(cuMemMap(va, bytes, 0, handles_[(size_t)rank], 0));
-    XCCL_CU_CHECK(cuMemSetAccess(va, bytes, &access, 1));
+    XCCL_CU_CHECK(cuMemSetAccess(va, bytes, &acc_desc, 1));
     base[(size_t)rank]    = (char *)va;
     mapped_[(size_t)rank] = true;
     XCCL_CUDA_CHECK(cudaMemset((void *)va, 0, bytes));
@@ -308,7 +308,7 @@ xccl_status_t SymmetricRegion::setup(const OobGroup &g, size_t want_bytes, bool 
         }
         CUdeviceptr pva = 0;
         if (cuMemAddressReserve(&pva, bytes, gran, 0, 0) != CUDA_SUCCESS || cuMemMap(pva, bytes, 0, h, 0) != CUDA_SUCCESS ||
-            cuMemSetAccess(pva, bytes, &access, 1) != CUDA_SUCCESS) {
+            cuMemSetAccess(pva, bytes, &acc_desc, 1) != CUDA_SUCCESS) {
             xccl_debug("nvlink: cannot map the memory of rank %d (no peer access?)", p);
             ok = 0;
             break;
@@ -350,7 +350,7 @@ xccl_status_t SymmetricRegion::setup(const OobGroup &g, size_t want_bytes, bool 
             CUdeviceptr mcva = 0;
             if (cuMemAddressReserve(&mcva, bytes, gran, 0, 0) == CUDA_SUCCESS) {
                 if (cuMemMap(mcva, bytes, 0, mc_handle_, 0) == CUDA_SUCCESS &&
-                    cuMemSetAccess(mcva, bytes, &access, 1) == CUDA_SUCCESS) {
+                    cuMemSetAccess(mcva, bytes, &acc_desc, 1) == CUDA_SUCCESS) {
                     mc_base    = (char *)mcva;
                     mc_va_     = (char *)mcva;
                     mc_mapped_ = true;

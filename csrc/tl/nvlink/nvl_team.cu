@@ -1,0 +1,401 @@
+// NVLink team library: the product path for CUDA buffers on one NVSwitch box.
+//
+// A team owns one symmetric region per rank (signal pad + workspace, optionally bound to an
+// NVSwitch multicast object) and serves every collective with the kernels of nvl_kernels.cu,
+// launched on the caller's stream (or on an internal one). A request completes when its CUDA
+// event does; the kernels' status words, kept in mapped host memory, turn an expired device
+// wait into XCCL_ERR_TIMED_OUT and poison the team.
+// Allreduce picks one-shot / two-shot / NVLS per message size; the thresholds are options so that
+// a measured table can be applied without rebuilding.
+#include <cstdlib>
+#include <cstring>
+
+#include "../../core/core.h"
+#include "../../cuda/cuda_common.h"
+#include "nvl_kernels.cuh"
+#include "nvl_shm.h"
+#include "nvl_world.h"
+
+namespace xccl {
+namespace nvl {
+
+namespace {
+
+struct NvlCfg {
+    size_t ws_bytes      = 128u << 20;
+    bool   nvls          = true;
+    size_t one_shot_max  = 128u << 10;
+    size_t nvls_min      = 256u << 10;
+    int    max_blocks    = 64;
+    int    threads       = 512;
+    double wait_timeout_ms = 5000.0;
+    bool   timing        = false;
+};
+
+class NvlTeam;
+
+class NvlReq final : public xccl_coll_req {
+public:
+    NvlReq(NvlTeam *t, const xccl_coll_op_args_t &a) : team_(t), args_(a) {}
+    ~NvlReq() override;
+    xccl_status_t prepare();
+    xccl_status_t post() override;
+    xccl_status_t test() override;
+    xccl_status_t wait() override;
+    xccl_status_t finalize() override { return in_flight_ ? XCCL_INPROGRESS : XCCL_OK; }
+    double        elapsed_us() override { return elapsed_us_; }
+
+private:
+    xccl_status_t complete();
+    NvlTeam            *team_;
+    xccl_coll_op_args_t args_;
+    cudaEvent_t         done_ = nullptr, start_ = nullptr;
+    bool                in_flight_ = false;
+    xccl_status_t       last_ = XCCL_OK;
+    double              elapsed_us_ = -1.0;
+    uint32_t           *vmeta_ = nullptr;
+    size_t              max_src_bytes_ = 0;
+};
+
+class NvlTeam final : public TlTeam {
+public:
+    NvlTeam(TeamLib *tl, const NvlCfg &cfg) : tl_(tl), cfg(cfg) {}
+    ~NvlTeam() override
+    {
+        if (stream != nullptr) {
+            cudaStreamSynchronize(stream);
+            cudaStreamDestroy(stream);
+        }
+        delete region;
+        if (status_host != nullptr) cudaFreeHost(status_host);
+    }
+
+    xccl_status_t init(const OobGroup &g)
+    {
+        rank = g.rank;
+        size = g.size;
+        if (size > kMaxRanks) return XCCL_ERR_UNSUPPORTED;
+        size_t        total = kPadBytes + cfg.ws_bytes;
+        xccl_status_t st    = SymmetricRegion::create(g, total, cfg.nvls, &region);
+        if (st != XCCL_OK) return st;
+        XCCL_CUDA_CHECK(cudaHostAlloc((void **)&status_host, sizeof(HostStatus), cudaHostAllocMapped));
+        std::memset(status_host, 0, sizeof(HostStatus));
+        uint32_t *sdev = nullptr;
+        XCCL_CUDA_CHECK(cudaHostGetDevicePointer((void **)&sdev, status_host, 0));
+        int lo = 0, hi = 0;
+        cudaDeviceGetStreamPriorityRange(&lo, &hi);
+        XCCL_CUDA_CHECK(cudaStreamCreateWithPriority(&stream, cudaStreamNonBlocking, hi));
+        world.size      = size;
+        world.rank_base = rank;
+        world.n_local   = 1;
+        world.ws_bytes  = cfg.ws_bytes;
+        world.wait_budget_ns = (unsigned long long)(cfg.wait_timeout_ms * 1e6);
+        for (int p = 0; p < size; p++) {
+            world.pad[p] = (uint32_t *)region->base[(size_t)p];
+            world.ws[p]  = region->base[(size_t)p] + kPadBytes;
+        }
+        world.status[0] = sdev;
+        world.mc_ws     = region->mc_base != nullptr ? region->mc_base + kPadBytes : nullptr;
+        tl_info(tl_, "nvlink team: rank %d/%d, workspace %zu MiB, NVLS %s", rank, size, cfg.ws_bytes >> 20,
+                world.mc_ws != nullptr ? "on" : "off");
+        return XCCL_OK;
+    }
+
+    xccl_status_t create_test() override { return XCCL_OK; }
+
+    xccl_status_t collective_init(const xccl_coll_op_args_t &args, xccl_memory_type_t, xccl_coll_req **req) override
+    {
+        auto         *r  = new NvlReq(this, args);
+        xccl_status_t st = r->prepare();
+        if (st != XCCL_OK) {
+            delete r;
+            return st;
+        }
+        *req = r;
+        return XCCL_OK;
+    }
+
+    TeamLib         *tl_;
+    NvlCfg           cfg;
+    SymmetricRegion *region = nullptr;
+    World            world{};
+    HostStatus      *status_host = nullptr;
+    cudaStream_t     stream = nullptr;
+    int              phase  = 0;  // workspace halves consumed so far
+};
+
+NvlReq::~NvlReq()
+{
+    if (done_ != nullptr) cudaEventDestroy(done_);
+    if (start_ != nullptr) cudaEventDestroy(start_);
+    if (vmeta_ != nullptr) cudaFree(vmeta_);
+}
+
+xccl_status_t NvlReq::prepare()
+{
+    const auto &bi = args_.buffer_info;
+    const int   n  = team_->size;
+    switch (args_.coll_type) {
+    case XCCL_ALLREDUCE:
+    case XCCL_REDUCE:
+    case XCCL_REDUCE_SCATTER:
+        if (xccl_dt_size(args_.reduce_info.dt) == 0) return XCCL_ERR_UNSUPPORTED;
+        break;
+    case XCCL_ALLTOALLV: {
+        if (bi.src_counts == nullptr || bi.dst_counts == nullptr || bi.src_displacements == nullptr ||
+            bi.dst_displacements == nullptr) {
+            return XCCL_ERR_INVALID_PARAM;
+        }
+        if (bi.src_buffer == XCCL_IN_PLACE || bi.src_buffer == bi.dst_buffer) return XCCL_ERR_UNSUPPORTED;
+        if (xccl_dt_size(bi.src_datatype) == 0 || xccl_dt_size(bi.dst_datatype) == 0) return XCCL_ERR_INVALID_PARAM;
+        std::vector<uint32_t> meta((size_t)4 * n);
+        size_t                total = 0;
+        for (int p = 0; p < n; p++) {
+            meta[(size_t)p]         = bi.src_counts[p];
+            meta[(size_t)n + p]     = bi.src_displacements[p];
+            meta[(size_t)2 * n + p] = bi.dst_counts[p];
+            meta[(size_t)3 * n + p] = bi.dst_displacements[p];
+            total += ((size_t)bi.src_counts[p] * xccl_dt_size(bi.src_datatype) + 15) / 16 * 16;
+        }
+        max_src_bytes_ = total;
+        XCCL_CUDA_CHECK(cudaMalloc((void **)&vmeta_, meta.size() * 4));
+        XCCL_CUDA_CHECK(cudaMemcpy(vmeta_, meta.data(), meta.size() * 4, cudaMemcpyHostToDevice));
+        break;
+    }
+    case XCCL_BCAST:
+    case XCCL_ALLGATHER:
+    case XCCL_ALLTOALL:
+    case XCCL_BARRIER:
+    case XCCL_FANIN:
+    case XCCL_FANOUT: break;
+    default: return XCCL_ERR_UNSUPPORTED;
+    }
+    XCCL_CUDA_CHECK(cudaEventCreateWithFlags(&done_, team_->cfg.timing ? cudaEventDefault : cudaEventDisableTiming));
+    if (team_->cfg.timing) XCCL_CUDA_CHECK(cudaEventCreate(&start_));
+    return XCCL_OK;
+}
+
+xccl_status_t NvlReq::post()
+{
+    if (in_flight_) return XCCL_ERR_NO_RESOURCE;
+    if (team_->poisoned) return XCCL_ERR_NO_PROGRESS;
+    const auto  &bi = args_.buffer_info;
+    cudaStream_t s  = team_->stream;
+    if ((args_.field_mask & XCCL_COLL_OP_ARGS_FIELD_STREAM) && args_.stream.stream != nullptr) {
+        s = *(cudaStream_t *)args_.stream.stream;
+    }
+    const World &w = team_->world;
+    Call         c{};
+    void        *src = bi.src_buffer, *dst = bi.dst_buffer;
+    bool         sync_only = (args_.coll_type == XCCL_BARRIER || args_.coll_type == XCCL_FANIN || args_.coll_type == XCCL_FANOUT);
+    if (!sync_only && (src == XCCL_IN_PLACE || src == nullptr)) {
+        src = dst;
+        if (args_.coll_type == XCCL_ALLGATHER) src = (char *)dst + (size_t)team_->rank * (bi.len / (size_t)team_->size);
+    }
+    c.src[0]   = src;
+    c.dst[0]   = dst;
+    c.vmeta[0] = vmeta_;
+    c.count    = args_.reduce_info.count;
+    c.len      = bi.len;
+    c.op       = (int)args_.reduce_info.op;
+    c.root     = args_.root;
+    c.scale    = 1.0f;
+    xccl_dt_t out_dt = XCCL_DT_UNSUPPORTED;
+    if (args_.field_mask & XCCL_COLL_OP_ARGS_FIELD_EPILOGUE) {
+        c.scale = args_.epilogue.scale;
+        out_dt  = args_.epilogue.out_dt;
+    }
+    c.do_scale = (c.scale != 1.0f);
+    c.parity   = team_->phase & 1;
+    LaunchCfg cfg;
+    cfg.threads    = team_->cfg.threads;
+    cfg.max_blocks = team_->cfg.max_blocks;
+    const xccl_dt_t dt = args_.reduce_info.dt;
+    if (start_ != nullptr) XCCL_CUDA_CHECK(cudaEventRecord(start_, s));
+    xccl_status_t st;
+    switch (args_.coll_type) {
+    case XCCL_ALLREDUCE: {
+        const size_t bytes = c.count * xccl_dt_size(dt);
+        Alg          alg   = ALG_AUTO;
+        if (args_.alg.set_by_user) alg = (Alg)args_.alg.id;
+        if (alg == ALG_AUTO) {
+            if (bytes <= team_->cfg.one_shot_max && bytes + 16 <= one_shot_limit(w)) {
+                alg = ALG_ONE_SHOT;
+            } else if (w.mc_ws != nullptr && nvls_supported(dt, (xccl_op_t)c.op) && bytes >= team_->cfg.nvls_min) {
+                alg = ALG_NVLS;
+            } else {
+                alg = ALG_TWO_SHOT;
+            }
+        }
+        st = launch_allreduce(w, c, dt, out_dt, alg, cfg, s);
+        team_->phase += (alg == ALG_ONE_SHOT) ? 1 : chunks_used(w, XCCL_ALLREDUCE, c.count, c.len, dt);
+        break;
+    }
+    case XCCL_REDUCE:
+        st = launch_reduce(w, c, dt, out_dt, cfg, s);
+        team_->phase += chunks_used(w, XCCL_REDUCE, c.count, c.len, dt);
+        break;
+    case XCCL_REDUCE_SCATTER:
+        if (c.count == 0 && c.len != 0) c.count = c.len / xccl_dt_size(dt) / (size_t)team_->size;
+        st = launch_reduce_scatter(w, c, dt, out_dt, cfg, s);
+        team_->phase += chunks_used(w, XCCL_REDUCE_SCATTER, c.count, c.len, dt);
+        break;
+    case XCCL_BCAST:
+        st = launch_bcast(w, c, cfg, s);
+        team_->phase += chunks_used(w, XCCL_BCAST, c.count, c.len, dt);
+        break;
+    case XCCL_ALLGATHER:
+        st = launch_allgather(w, c, cfg, s);
+        team_->phase += chunks_used(w, XCCL_ALLGATHER, c.count, c.len, dt);
+        break;
+    case XCCL_ALLTOALL:
+        st = launch_alltoall(w, c, cfg, s);
+        team_->phase += chunks_used(w, XCCL_ALLTOALL, c.count, c.len, dt);
+        break;
+    case XCCL_ALLTOALLV:
+        c.src_es = (int)xccl_dt_size(bi.src_datatype);
+        c.dst_es = (int)xccl_dt_size(bi.dst_datatype);
+        st       = launch_alltoallv(w, c, max_src_bytes_, cfg, s);
+        team_->phase += 1;
+        break;
+    default: st = launch_sync(w, c, (int)args_.coll_type, cfg, s); break;
+    }
+    if (st != XCCL_OK) return st;
+    XCCL_CUDA_CHECK(cudaEventRecord(done_, s));
+    in_flight_ = true;
+    return XCCL_OK;
+}
+
+xccl_status_t NvlReq::complete()
+{
+    in_flight_ = false;
+    last_      = XCCL_OK;
+    if (team_->status_host->code != NVL_OK) {
+        tl_error(team_->tl_, "nvlink: device wait expired (code %u, rank %u waiting for rank %u, epoch %u)",
+                 team_->status_host->code, team_->status_host->rank, team_->status_host->peer,
+                 team_->status_host->epoch);
+        team_->poisoned = true;
+        last_           = XCCL_ERR_TIMED_OUT;
+    }
+    if (start_ != nullptr) {
+        float ms = 0;
+        if (cudaEventElapsedTime(&ms, start_, done_) == cudaSuccess) elapsed_us_ = (double)ms * 1000.0;
+    }
+    return last_;
+}
+
+xccl_status_t NvlReq::test()
+{
+    if (!in_flight_) return last_;
+    cudaError_t e = cudaEventQuery(done_);
+    if (e == cudaErrorNotReady) return XCCL_INPROGRESS;
+    if (e != cudaSuccess) {
+        in_flight_ = false;
+        last_      = cuda_status(e);
+        return last_;
+    }
+    return complete();
+}
+
+xccl_status_t NvlReq::wait()
+{
+    if (!in_flight_) return last_;
+    cudaError_t e = cudaEventSynchronize(done_);
+    if (e != cudaSuccess) {
+        in_flight_ = false;
+        last_      = cuda_status(e);
+        return last_;
+    }
+    return complete();
+}
+
+class NvlContext final : public TlContext {
+public:
+    NvlContext(const xccl_context_params_t &p, const NvlCfg &c) : params_(p), cfg_(c) {}
+    xccl_status_t team_create_post(const xccl_team_params_t &tp, TlTeam **team) override
+    {
+        OobGroup g = make_oob_group(tp, params_.oob);
+        if (g.rank < 0 || g.size < 1) return XCCL_ERR_INVALID_PARAM;
+        auto         *t  = new NvlTeam(tl, cfg_);
+        xccl_status_t st = t->init(g);
+        if (st != XCCL_OK) {
+            delete t;
+            return st;
+        }
+        *team = t;
+        return XCCL_OK;
+    }
+
+private:
+    xccl_context_params_t params_;
+    NvlCfg                cfg_;
+};
+
+class NvlLib final : public TeamLib {
+public:
+    NvlLib() : TeamLib(XCCL_TL_NVLINK, 120)
+    {
+        caps.coll_types = XCCL_COLL_CAP_BARRIER | XCCL_COLL_CAP_BCAST | XCCL_COLL_CAP_ALLREDUCE | XCCL_COLL_CAP_REDUCE |
+                          XCCL_COLL_CAP_ALLTOALL | XCCL_COLL_CAP_ALLTOALLV | XCCL_COLL_CAP_ALLGATHER |
+                          XCCL_COLL_CAP_FANIN | XCCL_COLL_CAP_FANOUT | XCCL_COLL_CAP_REDUCE_SCATTER;
+        caps.mem_types      = XCCL_BIT(XCCL_MEMORY_TYPE_CUDA);
+        caps.sync_mem_types = XCCL_BIT(XCCL_MEMORY_TYPE_HOST);
+        caps.team_usage     = XCCL_LIB_PARAMS_TEAM_USAGE_HW_COLLECTIVES | XCCL_LIB_PARAMS_TEAM_USAGE_SW_COLLECTIVES;
+        caps.reproducible   = XCCL_REPRODUCIBILITY_MODE_REPRODUCIBLE | XCCL_REPRODUCIBILITY_MODE_NON_REPRODUCIBLE;
+    }
+
+    xccl_status_t open() override { return cuda_available() ? XCCL_OK : XCCL_ERR_NO_RESOURCE; }
+
+    std::vector<OptField> context_options() const override
+    {
+        return {
+            {"WORKSPACE_SIZE", "128m", "Bytes of symmetric workspace per rank (two alternating halves)", OptType::MEMUNITS},
+            {"NVLS", "try", "Bind the workspace to an NVSwitch multicast object and use multimem kernels", OptType::TERNARY},
+            {"ONE_SHOT_MAX", "128k", "Allreduce messages up to this size use the one-shot kernel", OptType::MEMUNITS},
+            {"NVLS_MIN", "256k", "Allreduce messages from this size use NVLS when available", OptType::MEMUNITS},
+            {"MAX_BLOCKS", "64", "Upper bound of thread blocks per collective kernel (at most 128)", OptType::UINT},
+            {"THREADS", "512", "Threads per block of the collective kernels", OptType::UINT},
+            {"WAIT_TIMEOUT_MS", "5000", "Budget of every device-side wait for a peer", OptType::DOUBLE},
+            {"TIMING", "no", "Record CUDA events around each collective (xccl_collective_elapsed_us)", OptType::BOOL},
+        };
+    }
+
+    xccl_status_t query(xccl_tl_attr_t *attr) override
+    {
+        TeamLib::query(attr);
+        if (attr->field_mask & XCCL_TL_ATTR_FIELD_DEVICES_COUNT) {
+            int n = 0;
+            if (cudaGetDeviceCount(&n) != cudaSuccess) n = 0;
+            attr->devices_count = n;
+        }
+        return XCCL_OK;
+    }
+
+    xccl_status_t context_create(xccl_lib *, const xccl_context_params_t &params, const OptTable &cfg,
+                                 TlContext **ctx) override
+    {
+        if (!cuda_available()) return XCCL_ERR_NO_RESOURCE;
+        if (!(params.field_mask & XCCL_CONTEXT_PARAM_FIELD_OOB)) {
+            // teams may still bring their own OOB; nothing to check here
+        }
+        NvlCfg c;
+        c.ws_bytes        = ((size_t)cfg.num("WORKSPACE_SIZE") + 4095) & ~(size_t)4095;
+        c.nvls            = cfg.flag("NVLS");
+        c.one_shot_max    = (size_t)cfg.num("ONE_SHOT_MAX");
+        c.nvls_min        = (size_t)cfg.num("NVLS_MIN");
+        c.max_blocks      = std::max(1, std::min((int)cfg.num("MAX_BLOCKS"), kMaxBlocks));
+        c.threads         = std::max(32, std::min((int)cfg.num("THREADS"), 512)) / 32 * 32;
+        c.wait_timeout_ms = cfg.real("WAIT_TIMEOUT_MS");
+        c.timing          = cfg.flag("TIMING");
+        *ctx              = new NvlContext(params, c);
+        return XCCL_OK;
+    }
+};
+
+NvlLib           g_nvl_lib;
+TeamLibRegistrar g_nvl_reg(&g_nvl_lib);
+
+}  // namespace
+
+}  // namespace nvl
+}  // namespace xccl

@@ -1,0 +1,139 @@
+"""NVLink team with one process per GPU (needs at least 2 GPUs; skipped otherwise).
+
+Every rank checks its results against values it can compute alone from the seeds, so a wrong
+answer fails on the rank that sees it. NVLS is exercised when the team reports it.
+"""
+import os
+
+import pytest
+import torch
+
+from xccl_b200 import _capi as K
+from xccl_b200.utils.launch import run_ranks
+
+pytestmark = pytest.mark.gpu
+
+
+def _ngpus():
+    try:
+        return torch.cuda.device_count() if torch.cuda.is_available() else 0
+    except Exception:
+        return 0
+
+
+def _vals(rank, count, dtype, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed * 100 + rank)
+    return torch.randint(-8, 9, (count,), generator=g).to(dtype)
+
+
+def _rank_main(rank, size, job, tls, nvls):
+    from xccl_b200.api import Context, Lib, ShmOob, Team
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    oob = ShmOob(job, rank, size)
+    lib = Lib()
+    cfg = {K.TL_NVLINK: {"WORKSPACE_SIZE": "32m", "NVLS": "try" if nvls else "no", "TIMING": "y"}}
+    ctx = Context(lib, oob, tls=tls, config=cfg)
+    team = Team(ctx)
+    want_tl = K.TL_NVLINK if (tls & K.TL_NVLINK) else K.TL_NCCL
+    assert team.coll_tl(K.ALLREDUCE, K.MEM_CUDA) == want_tl, team.coll_tl(K.ALLREDUCE, K.MEM_CUDA)
+    stream = torch.cuda.current_stream().cuda_stream
+    out = {}
+
+    algs = [None]
+    if tls & K.TL_NVLINK:
+        algs = [K.NVLINK_ALG_ONE_SHOT, K.NVLINK_ALG_TWO_SHOT] + ([K.NVLINK_ALG_NVLS] if nvls else [])
+    for dtype in (torch.float32, torch.bfloat16):
+        for count in (1, 1000, 65536, 1 << 20, (3 << 20) + 5):
+            for alg in algs:
+                if alg == K.NVLINK_ALG_ONE_SHOT and count * 4 * size > (16 << 20):
+                    continue
+                src = _vals(rank, count, dtype).to(dev)
+                dst = torch.zeros_like(src)
+                req = team.allreduce(src, dst, alg=alg, stream=stream)
+                try:
+                    req.post().wait()
+                except Exception as e:  # NVLS may be unavailable on this box: fall back loudly
+                    if alg == K.NVLINK_ALG_NVLS:
+                        out["nvls"] = f"unavailable: {e}"
+                        req.finalize()
+                        continue
+                    raise
+                want = torch.stack([_vals(r, count, dtype).double() for r in range(size)]).sum(0).to(dtype)
+                assert torch.equal(dst.cpu(), want), (dtype, count, alg)
+                if alg == K.NVLINK_ALG_NVLS:
+                    out["nvls"] = "ok"
+                req.finalize()
+    # fused scale + cast (gradient averaging), persistent request posted 3 times
+    src = torch.randn(100000, device=dev, generator=torch.Generator(device=dev).manual_seed(rank))
+    dst = torch.empty(100000, device=dev, dtype=torch.bfloat16)
+    if tls & K.TL_NVLINK:
+        req = team.allreduce(src, dst, scale=1.0 / size, out_dt=K.DT_BFLOAT16, stream=stream)
+        for _ in range(3):
+            req.post().wait()
+        allv = [torch.randn(100000, device=dev, generator=torch.Generator(device=dev).manual_seed(r)) for r in range(size)]
+        want = (torch.stack(allv).double().sum(0) / size).float()
+        torch.testing.assert_close(dst.float(), want, rtol=1e-2, atol=2e-2)
+        out["elapsed_us"] = req.elapsed_us
+        req.finalize()
+    # the other collectives
+    per = 4099
+    src = _vals(rank, per, torch.int32, seed=3).to(dev)
+    dst = torch.zeros(per * size, dtype=torch.int32, device=dev)
+    team.allgather(src, dst, stream=stream).run().finalize()
+    assert torch.equal(dst.cpu(), torch.cat([_vals(r, per, torch.int32, seed=3) for r in range(size)]))
+    src = (torch.arange(per * size, dtype=torch.float32) + rank * 1e5).to(dev)
+    dst = torch.zeros_like(src)
+    team.alltoall(src, dst, stream=stream).run().finalize()
+    want = torch.cat([(torch.arange(per * size, dtype=torch.float32) + r * 1e5)[rank * per:(rank + 1) * per]
+                      for r in range(size)])
+    assert torch.equal(dst.cpu(), want)
+    for root in range(size):
+        buf = _vals(root, 70001, torch.float32, seed=9).to(dev) if rank == root else torch.zeros(70001, device=dev)
+        team.bcast(buf, root, stream=stream).run().finalize()
+        assert torch.equal(buf.cpu(), _vals(root, 70001, torch.float32, seed=9))
+    if tls & K.TL_NVLINK:
+        src = _vals(rank, 5000, torch.float32, seed=4).to(dev)
+        dst = torch.zeros_like(src)
+        team.reduce(src, dst, root=size - 1, stream=stream).run().finalize()
+        if rank == size - 1:
+            assert torch.equal(dst.cpu(), torch.stack([_vals(r, 5000, torch.float32, seed=4) for r in range(size)]).sum(0))
+        src = _vals(rank, 1237 * size, torch.float32, seed=5).to(dev)
+        dst = torch.zeros(1237, device=dev)
+        team.reduce_scatter(src, dst, stream=stream).run().finalize()
+        full = torch.stack([_vals(r, 1237 * size, torch.float32, seed=5) for r in range(size)]).sum(0)
+        assert torch.equal(dst.cpu(), full[rank * 1237:(rank + 1) * 1237])
+        # variable counts
+        sc = [rank + d + 1 for d in range(size)]
+        sd = [sum(sc[:d]) for d in range(size)]
+        rc = [s + rank + 1 for s in range(size)]
+        rd = [sum(rc[:s]) for s in range(size)]
+        src = torch.cat([torch.full((sc[d],), float(rank * 100 + d)) for d in range(size)]).to(dev)
+        dst = torch.zeros(sum(rc), device=dev)
+        team.alltoallv(src, sc, sd, dst, rc, rd, stream=stream).run().finalize()
+        assert torch.equal(dst.cpu(), torch.cat([torch.full((rc[s],), float(s * 100 + rank)) for s in range(size)]))
+        # stream-ordered barrier served by the nvlink team
+        assert team.coll_tl(K.BARRIER, K.MEM_HOST) == K.TL_NVLINK
+        for _ in range(3):
+            team.barrier().run().finalize()
+    torch.cuda.synchronize()
+    team.close()
+    ctx.close()
+    lib.close()
+    oob.close()
+    return out
+
+
+@pytest.mark.parametrize("size", [2, 4, 8])
+def test_nvlink_team_collectives(size):
+    if _ngpus() < size:
+        pytest.skip(f"needs {size} GPUs")
+    res = run_ranks(_rank_main, size, K.TL_NVLINK | K.TL_UCX, True, timeout=300, start_method="spawn",
+                    env={"NCCL_NVLS_ENABLE": "0"})
+    print("nvlink team:", res[0])
+
+
+def test_nccl_team_collectives():
+    if _ngpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    run_ranks(_rank_main, 2, K.TL_NCCL | K.TL_UCX, False, timeout=300, start_method="spawn")
