@@ -1,0 +1,120 @@
+"""Tensor-parallel Llama-style MLP block on the fused kernels.
+
+``y = W_down (silu(W_gate x) * W_up x)`` with the FFN dimension split over ``tp`` ranks and the
+activations sharded by tokens (sequence parallel): the up/gate projection is allgather->GEMM with
+the SwiGLU fused into the epilogue, the down projection is GEMM->reduce-scatter. Each is ONE
+kernel of ``csrc/fused/tp_gemm.cu``; with ``tp == 1`` the same kernels run without communication.
+
+``TorchTpMlp`` is the same block written with torch collectives and matmuls (NCCL + cuBLAS); it
+is the comparison point, not a fallback.
+"""
+from __future__ import annotations
+
+from typing import Any, Optional
+
+import torch
+
+from ..ops.tp import TpWorkspace
+
+
+def _init_weights(tokens: int, hidden: int, ffn: int, tp: int, rank: int, device, seed: int = 0):
+    """Random-init shards ~N(0, 0.02) of the named architecture; the same seed gives every
+    implementation the same full weights."""
+    f_local = ffn // tp
+    g = torch.Generator(device=device).manual_seed(seed * 1000 + rank)
+    mk = lambda *s: (torch.randn(*s, device=device, generator=g) * 0.02).to(torch.bfloat16)  # noqa: E731
+    return mk(f_local, hidden), mk(f_local, hidden), mk(hidden, f_local)
+
+
+class TpMlp:
+    """One rank of the block (or, with ``oob=None`` and ``tp > 1``, all ranks emulated on one GPU)."""
+
+    def __init__(self, tokens: int, hidden: int, ffn: int, tp: int = 1, rank: int = 0, oob: Any = None,
+                 seed: int = 0, emulate: bool = False):
+        if ffn % tp or tokens % tp:
+            raise ValueError("tokens and ffn must divide by tp")
+        self.tokens, self.hidden, self.ffn, self.tp, self.rank = tokens, hidden, ffn, tp, rank
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self.emulate = emulate or (oob is None and tp > 1)
+        self.ws = TpWorkspace(tokens, hidden, oob=None if self.emulate else oob, emu_ranks=tp if self.emulate else 1)
+        self.n_local = self.ws.n_local
+        ranks = range(tp) if self.emulate else [rank]
+        ws_ = [_init_weights(tokens, hidden, ffn, tp, r, self.device, seed) for r in ranks]
+        self.w_gate = [w[0] for w in ws_]
+        self.w_up = [w[1] for w in ws_]
+        self.w_down = [w[2] for w in ws_]
+        f_local = ffn // tp
+        self.h = [torch.empty(tokens, f_local, dtype=torch.bfloat16, device=self.device) for _ in ranks]
+        self.y = [torch.empty(tokens // tp, hidden, dtype=torch.bfloat16, device=self.device) for _ in ranks]
+        self.x_shards = [self.ws.x_shard(i) for i in range(self.n_local)]
+        self.launches = 0
+
+    def forward(self, x_shards: Optional[list] = None) -> list:
+        """x_shards: one [tokens/tp, hidden] bf16 tensor per local rank, or None when the input was
+        already written into ``self.x_shards``. Returns the [tokens/tp, hidden] output shards."""
+        if x_shards is not None:
+            for dst, src in zip(self.x_shards, x_shards):
+                dst.copy_(src, non_blocking=True)
+        self.ws.ag_gemm_swiglu(self.w_gate, self.w_up, self.h)
+        self.ws.gemm_rs(self.h, self.w_down, self.y)
+        self.launches += 2
+        return self.y
+
+    def forward_from_host(self, x_pinned: list) -> torch.Tensor:
+        """End-to-end step: host->device copy of this step's input shards from pinned memory,
+        the block, and a device->host read of a scalar metric of the result."""
+        for dst, src in zip(self.x_shards, x_pinned):
+            dst.copy_(src, non_blocking=True)
+        y = self.forward()
+        metric = y[0].float().square().mean()
+        return metric.cpu()
+
+    def check_error(self) -> None:
+        e = self.ws.error()
+        if e:
+            raise RuntimeError(f"a bounded wait expired inside a fused TP kernel (code {e:#x})")
+
+    def close(self) -> None:
+        self.ws.close()
+
+
+class TorchTpMlp:
+    """The same block with torch.distributed collectives and torch matmuls."""
+
+    def __init__(self, tokens: int, hidden: int, ffn: int, tp: int = 1, rank: int = 0, group=None, seed: int = 0):
+        import torch.distributed as dist
+        self.dist = dist
+        self.tokens, self.hidden, self.ffn, self.tp, self.rank, self.group = tokens, hidden, ffn, tp, rank, group
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self.w_gate, self.w_up, self.w_down = _init_weights(tokens, hidden, ffn, tp, rank, self.device, seed)
+        self.xg = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=self.device)
+        self.y = torch.empty(tokens // tp, hidden, dtype=torch.bfloat16, device=self.device)
+        self.x_shard = torch.empty(tokens // tp, hidden, dtype=torch.bfloat16, device=self.device)
+
+    def forward(self, x_shard: Optional[torch.Tensor] = None) -> torch.Tensor:
+        x_shard = self.x_shard if x_shard is None else x_shard
+        if self.tp > 1:
+            self.dist.all_gather_into_tensor(self.xg, x_shard, group=self.group)
+            x = self.xg
+        else:
+            x = x_shard
+        h = torch.nn.functional.silu(x @ self.w_gate.t()) * (x @ self.w_up.t())
+        part = h @ self.w_down.t()
+        if self.tp > 1:
+            self.dist.reduce_scatter_tensor(self.y, part, group=self.group)
+            return self.y
+        return part
+
+    def forward_from_host(self, x_pinned: torch.Tensor) -> torch.Tensor:
+        self.x_shard.copy_(x_pinned, non_blocking=True)
+        y = self.forward()
+        return y.float().square().mean().cpu()
+
+
+def reference_forward_fp32(x_full: torch.Tensor, w_gate_full: torch.Tensor, w_up_full: torch.Tensor,
+                           w_down_full: torch.Tensor) -> torch.Tensor:
+    """Plain fp32 statement of the block on full (unsharded) tensors: the numerics oracle."""
+    x = x_full.float()
+    h = torch.nn.functional.silu(x @ w_gate_full.float().t()) * (x @ w_up_full.float().t())
+    h = h.to(torch.bfloat16).float()  # the fused kernels round h to bf16 between the two GEMMs
+    return h @ w_down_full.float().t()

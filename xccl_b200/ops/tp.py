@@ -1,0 +1,93 @@
+"""Fused tensor-parallel MLP operations (``csrc/fused/tp_mlp.cu``) on torch tensors.
+
+``TpWorkspace`` owns the symmetric buffers. With ``oob=None`` it emulates ``emu_ranks`` ranks on
+the current device (every call takes one tensor per rank and is one cooperative launch); with an
+out-of-band provider it is one rank of a real group (lists have one entry).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Any, Optional, Sequence
+
+import torch
+
+from .. import _capi as K
+from ..api import XcclError
+
+_pp = C.POINTER(C.c_void_p)
+K.optional("xccl_tp_ws_create", C.c_int, C.POINTER(K.Oob), C.c_int, C.c_int, C.c_int, C.c_int, _pp)
+K.optional("xccl_tp_ws_destroy", None, C.c_void_p)
+K.optional("xccl_tp_ws_x_shard", C.c_void_p, C.c_void_p, C.c_int)
+K.optional("xccl_tp_ws_x_full", C.c_void_p, C.c_void_p, C.c_int)
+K.optional("xccl_tp_ws_error", C.c_uint32, C.c_void_p)
+K.optional("xccl_tp_ag_gemm_swiglu", C.c_int, C.c_void_p, _pp, _pp, _pp, C.c_int, C.c_void_p)
+K.optional("xccl_tp_gemm_rs", C.c_int, C.c_void_p, _pp, _pp, _pp, C.c_int, C.c_void_p)
+
+
+def _ptrs(ts: Sequence[torch.Tensor]):
+    arr = (C.c_void_p * len(ts))()
+    for i, t in enumerate(ts):
+        if t.dtype != torch.bfloat16 or not t.is_contiguous() or not t.is_cuda:
+            raise ValueError("expected contiguous CUDA bf16 tensors")
+        arr[i] = t.data_ptr()
+    return arr
+
+
+def _as_tensor(ptr: int, shape: tuple, device: torch.device) -> torch.Tensor:
+    """A bf16 tensor view of library-owned device memory (no copy, not owned by torch)."""
+    n = 1
+    for s in shape:
+        n *= s
+
+    class _Mem:
+        __cuda_array_interface__ = {"shape": (n,), "typestr": "<i2", "data": (ptr, False), "version": 3}
+
+    return torch.as_tensor(_Mem(), device=device).view(torch.bfloat16).view(shape)
+
+
+class TpWorkspace:
+    def __init__(self, M: int, hidden: int, oob: Any = None, emu_ranks: int = 1, n_out: Optional[int] = None):
+        self.M, self.K, self.N = M, hidden, hidden if n_out is None else n_out
+        self.h = C.c_void_p()
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        L = K.load()
+        st = L.xccl_tp_ws_create(C.byref(oob.c) if oob is not None else None, emu_ranks, M, self.K, self.N,
+                                 C.byref(self.h))
+        if st != K.OK:
+            raise XcclError(st, "xccl_tp_ws_create")
+        self.tp = oob.size if oob is not None else emu_ranks
+        self.n_local = 1 if oob is not None else emu_ranks
+        self.rank = oob.rank if oob is not None else 0
+
+    def x_shard(self, local_rank: int = 0) -> torch.Tensor:
+        """This rank's rows of the gathered activation buffer: write the layer input here."""
+        p = K.load().xccl_tp_ws_x_shard(self.h, local_rank)
+        return _as_tensor(p, (self.M // self.tp, self.K), self.device)
+
+    def x_full(self, local_rank: int = 0) -> torch.Tensor:
+        p = K.load().xccl_tp_ws_x_full(self.h, local_rank)
+        return _as_tensor(p, (self.M, self.K), self.device)
+
+    def ag_gemm_swiglu(self, w_gate: Sequence[torch.Tensor], w_up: Sequence[torch.Tensor],
+                       out: Sequence[torch.Tensor]) -> None:
+        f_local = w_gate[0].shape[0]
+        st = K.load().xccl_tp_ag_gemm_swiglu(self.h, _ptrs(w_gate), _ptrs(w_up), _ptrs(out), f_local,
+                                             torch.cuda.current_stream().cuda_stream)
+        if st != K.OK:
+            raise XcclError(st, "xccl_tp_ag_gemm_swiglu")
+
+    def gemm_rs(self, h: Sequence[torch.Tensor], w_down: Sequence[torch.Tensor], out: Sequence[torch.Tensor]) -> None:
+        f_local = h[0].shape[1]
+        st = K.load().xccl_tp_gemm_rs(self.h, _ptrs(h), _ptrs(w_down), _ptrs(out), f_local,
+                                      torch.cuda.current_stream().cuda_stream)
+        if st != K.OK:
+            raise XcclError(st, "xccl_tp_gemm_rs")
+
+    def error(self) -> int:
+        torch.cuda.synchronize()
+        return int(K.load().xccl_tp_ws_error(self.h))
+
+    def close(self) -> None:
+        if self.h:
+            K.load().xccl_tp_ws_destroy(self.h)
+            self.h = C.c_void_p()
