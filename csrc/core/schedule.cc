@@ -43,9 +43,9 @@ void Schedule::add(Task *t)
 void Schedule::rearm()
 {
     n_completed_.store(0);
-    reset();
+    Task::reset();
     for (Task *t : tasks_) {
-        t->reset();
+        t->reset();  // nested schedules re-arm their own tasks
     }
 }
 

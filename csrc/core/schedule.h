@@ -38,7 +38,7 @@ public:
     void fire(TaskEvent ev);
     // marks completion, notifies the owning schedule and fires EVENT_COMPLETED
     void complete(xccl_status_t st = XCCL_OK);
-    void reset();
+    virtual void reset();
 
     // Called by a progress queue until state leaves TASK_INPROGRESS.
     std::function<xccl_status_t(Task *)> progress;
@@ -59,6 +59,7 @@ public:
     void start();
     void child_done(Task *t);
     void rearm();
+    void reset() override { rearm(); }
     int  n_tasks() const { return (int)tasks_.size(); }
     const std::vector<Task *> &tasks() const { return tasks_; }
 

@@ -81,6 +81,8 @@ public:
     HierContext *hctx;
     OobGroup     oob;
     Layout       layout;
+    std::vector<ProcInfo> procs;       // placement of every team rank
+    xccl_ep_range_t       place_range{};  // team rank -> context rank when the team has its own OOB
     std::array<Pair, PAIR_LAST> pairs;
     bool pair_ok(PairId p) const { return pairs[p].team != nullptr; }
 
