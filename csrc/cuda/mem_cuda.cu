@@ -92,6 +92,12 @@ xccl_status_t cuda_copy(void *dst, const void *src, size_t bytes, void *stream)
     return XCCL_OK;
 }
 
+xccl_status_t cuda_stream_sync(void *stream)
+{
+    XCCL_CUDA_CHECK(cudaStreamSynchronize((cudaStream_t)stream));
+    return XCCL_OK;
+}
+
 xccl_status_t cuda_event_record(void *stream, void **event)
 {
     cudaEvent_t ev;

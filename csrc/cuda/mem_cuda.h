@@ -22,6 +22,9 @@ xccl_status_t cuda_reduce_multi_sync(const void *a, const void *vecs, void *dst,
                                      size_t stride_bytes, xccl_dt_t dt, xccl_op_t op);
 
 xccl_status_t cuda_copy(void *dst, const void *src, size_t bytes, void *stream_or_null);
+// dst block (j, i) = src block (i, j) for rows x cols blocks of block_bytes (out of place)
+xccl_status_t cuda_block_transpose(void *dst, const void *src, int rows, int cols, size_t block_bytes, void *stream);
+xccl_status_t cuda_stream_sync(void *stream);
 
 // Events: a collective that the host progresses starts only after work already queued on the
 // caller's stream has finished.
