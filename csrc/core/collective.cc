@@ -52,6 +52,22 @@ struct FanoutMemHandle final : xccl_mem_handle {
 
 }  // namespace
 
+namespace xccl {
+// A region handle returned by xccl_global_mem_map_start bundles one handle per team library;
+// a team library finds its own part with this.
+xccl_mem_handle *find_mem_part(xccl_mem_handle *h, bool (*match)(xccl_mem_handle *))
+{
+    if (h == nullptr) return nullptr;
+    if (auto *f = dynamic_cast<FanoutMemHandle *>(h)) {
+        for (auto *p : f->parts) {
+            if (match(p)) return p;
+        }
+        return nullptr;
+    }
+    return match(h) ? h : nullptr;
+}
+}  // namespace xccl
+
 extern "C" {
 
 xccl_status_t xccl_collective_init(xccl_coll_op_args_t *args, xccl_coll_req_h *request, xccl_team_h team)

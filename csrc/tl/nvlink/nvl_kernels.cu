@@ -335,7 +335,9 @@ __device__ __forceinline__ void store_bytes(Byte *dst, size_t i, size_t bytes, b
     }
 }
 
-template <int KIND> __global__ void __launch_bounds__(512) mover_kernel(World w, Call c)
+// kMc (bcast only): the root stores through the multicast mapping, so one store lands in every
+// rank's workspace (the switch replicates it) and the others copy out of their OWN workspace.
+template <int KIND, bool kMc> __global__ void __launch_bounds__(512) mover_kernel(World w, Call c)
 {
     Self          s   = self_begin(w);
     const Byte   *src = (const Byte *)c.src[s.local];
@@ -364,7 +366,11 @@ template <int KIND> __global__ void __launch_bounds__(512) mover_kernel(World w,
                 const bool own_al = ((uintptr_t)own & 15) == 0;
                 for (size_t i = r.lo + threadIdx.x; i < r.hi; i += blockDim.x) {
                     uint4 v = load_pack<Byte>(seg, i, left, al);
-                    st_16(mine + ((size_t)q * n + i) * 16, v);
+                    if (kMc) {
+                        mm_st_16(w.mc_ws + hoff + i * 16, v);
+                    } else {
+                        st_16(mine + ((size_t)q * n + i) * 16, v);
+                    }
                     if (own != nullptr) store_bytes(own, i, left, own_al, v);
                 }
             }
@@ -377,7 +383,7 @@ template <int KIND> __global__ void __launch_bounds__(512) mover_kernel(World w,
                 Byte      *out = dst + b_off;
                 const bool al  = ((uintptr_t)out & 15) == 0;
                 for (size_t i = r.lo + threadIdx.x; i < r.hi; i += blockDim.x) {
-                    store_bytes(out, i, left, al, ld_nc16(w.ws[c.root] + hoff + i * 16));
+                    store_bytes(out, i, left, al, ld_nc16((kMc ? mine : w.ws[c.root] + hoff) + i * 16));
                 }
             }
         } else {
@@ -612,20 +618,24 @@ xccl_status_t launch_reduce_scatter(const World &w, const Call &c, xccl_dt_t dt,
     return XCCL_DISPATCH_IO(dt, out_dt, return (reduce_typed<T, O, true>(w, c, cfg, stream)););
 }
 
-template <int KIND>
+template <int KIND, bool kMc = false>
 static xccl_status_t mover(const World &w, const Call &c, const LaunchCfg &cfg, cudaStream_t stream)
 {
     size_t seg    = (KIND == MV_ALLGATHER) ? c.len / (size_t)w.size : c.len;
     size_t npacks = (seg + 15) / 16;
     if (npacks == 0) return XCCL_OK;
-    auto k      = mover_kernel<KIND>;
+    auto k      = mover_kernel<KIND, kMc>;
     int  blocks = pick_blocks(k, w, cfg, npacks * (KIND == MV_BCAST ? 1 : (size_t)w.size), 8);
     return launch(k, dim3((unsigned)blocks, (unsigned)w.n_local), dim3((unsigned)cfg.threads), cfg.cooperative, stream,
                   w, c);
 }
 
-xccl_status_t launch_bcast(const World &w, const Call &c, const LaunchCfg &cfg, cudaStream_t stream)
+xccl_status_t launch_bcast(const World &w, const Call &c, const LaunchCfg &cfg, cudaStream_t stream, bool multicast)
 {
+    if (multicast) {
+        if (w.mc_ws == nullptr) return XCCL_ERR_UNSUPPORTED;
+        return mover<MV_BCAST, true>(w, c, cfg, stream);
+    }
     return mover<MV_BCAST>(w, c, cfg, stream);
 }
 xccl_status_t launch_allgather(const World &w, const Call &c, const LaunchCfg &cfg, cudaStream_t stream)

@@ -42,7 +42,9 @@ xccl_status_t launch_reduce(const World &w, const Call &c, xccl_dt_t dt, xccl_dt
                             cudaStream_t stream);
 xccl_status_t launch_reduce_scatter(const World &w, const Call &c, xccl_dt_t dt, xccl_dt_t out_dt,
                                     const LaunchCfg &cfg, cudaStream_t stream);
-xccl_status_t launch_bcast(const World &w, const Call &c, const LaunchCfg &cfg, cudaStream_t stream);
+// multicast = true: root writes once through the NVSwitch multicast mapping (needs w.mc_ws)
+xccl_status_t launch_bcast(const World &w, const Call &c, const LaunchCfg &cfg, cudaStream_t stream,
+                           bool multicast = false);
 xccl_status_t launch_allgather(const World &w, const Call &c, const LaunchCfg &cfg, cudaStream_t stream);
 xccl_status_t launch_alltoall(const World &w, const Call &c, const LaunchCfg &cfg, cudaStream_t stream);
 xccl_status_t launch_alltoallv(const World &w, const Call &c, size_t max_src_bytes, const LaunchCfg &cfg,

@@ -240,10 +240,13 @@ xccl_status_t NvlReq::post()
         st = launch_reduce_scatter(w, c, dt, out_dt, cfg, s);
         team_->phase += chunks_used(w, XCCL_REDUCE_SCATTER, c.count, c.len, dt);
         break;
-    case XCCL_BCAST:
-        st = launch_bcast(w, c, cfg, s);
+    case XCCL_BCAST: {
+        bool mc = w.mc_ws != nullptr && c.len >= team_->cfg.nvls_min;
+        if (args_.alg.set_by_user) mc = (args_.alg.id == ALG_NVLS);
+        st = launch_bcast(w, c, cfg, s, mc);
         team_->phase += chunks_used(w, XCCL_BCAST, c.count, c.len, dt);
         break;
+    }
     case XCCL_ALLGATHER:
         st = launch_allgather(w, c, cfg, s);
         team_->phase += chunks_used(w, XCCL_ALLGATHER, c.count, c.len, dt);

@@ -363,7 +363,48 @@ class Team:
     def fanout(self, root: int = 0) -> Request:
         return self._sync(K.FANOUT, root)
 
+    # ------------------------------------------------------------ global memory
+    def mem_map(self, buf: Any, root: int, nbytes: Optional[int] = None, timeout: float = 60.0) -> "MemHandle":
+        """Maps `nbytes` of the root's `buf` for the whole team (``xccl_global_mem_map_start/test``)."""
+        p = K.MemMapParams()
+        p.field_mask = K.MEM_MAP_ADDRESS | K.MEM_MAP_LENGTH | K.MEM_MAP_ROOT
+        p.address = addr_of(buf)
+        p.length = nbytes_of(buf) if nbytes is None else nbytes
+        p.root = root
+        h = C.c_void_p()
+        _check(K.load().xccl_global_mem_map_start(self.h, p, C.byref(h)), "xccl_global_mem_map_start")
+        t0 = time.monotonic()
+        while True:
+            st = K.load().xccl_global_mem_map_test(h)
+            if st == K.OK:
+                break
+            if st < 0:
+                raise XcclError(st, "xccl_global_mem_map_test")
+            self.ctx.progress()
+            if time.monotonic() - t0 > timeout:
+                raise XcclError(K.ERR_TIMED_OUT, "xccl_global_mem_map_test")
+        return MemHandle(h, buf)
+
+    def fanout_get(self, memh: "MemHandle", offset: int, local: Any, nbytes: int) -> Request:
+        a = K.CollArgs()
+        a.coll_type = K.FANOUT_GET
+        a.get_info.memh = memh.h
+        a.get_info.offset = offset
+        a.get_info.local_buffer = addr_of(local)
+        a.get_info.len = nbytes
+        return Request(self, a, (memh, local))
+
     def close(self) -> None:
         if self.h:
             K.load().xccl_team_destroy(self.h)
+            self.h = C.c_void_p()
+
+
+class MemHandle:
+    def __init__(self, h: C.c_void_p, keep: Any):
+        self.h, self._keep = h, keep
+
+    def unmap(self) -> None:
+        if self.h:
+            _check(K.load().xccl_global_mem_unmap(self.h), "xccl_global_mem_unmap")
             self.h = C.c_void_p()
