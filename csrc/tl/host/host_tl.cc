@@ -218,6 +218,18 @@ xccl_status_t HostReq::prepare()
     default: return XCCL_ERR_UNSUPPORTED;
     }
 
+    const bool reduction = (args.coll_type == XCCL_ALLREDUCE || args.coll_type == XCCL_REDUCE ||
+                            args.coll_type == XCCL_REDUCE_SCATTER);
+    if (reduction && (args.field_mask & XCCL_COLL_OP_ARGS_FIELD_EPILOGUE)) {
+        epi_out_dt_ = args.epilogue.out_dt;
+        if (epi_out_dt_ == XCCL_DT_UNSUPPORTED || epi_out_dt_ == XCCL_DT_LAST_PREDEFINED) epi_out_dt_ = b.dt;
+        epi_scale_  = args.epilogue.scale;
+        epi_        = (epi_scale_ != 1.0f) || (epi_out_dt_ != b.dt);
+        epi_count_  = dst_bytes / xccl_dt_size(b.dt);
+        // probe the conversion once so that an unsupported pair fails at init
+        char probe_in[16] = {0}, probe_out[16] = {0};
+        if (epi_ && host_scale_cast(probe_in, b.dt, probe_out, epi_out_dt_, 1, 1.0f) != XCCL_OK) return XCCL_ERR_UNSUPPORTED;
+    }
     char *src = (char *)bi.src_buffer, *dst = (char *)bi.dst_buffer;
     bool  sync_only = (args.coll_type == XCCL_BARRIER || args.coll_type == XCCL_FANIN || args.coll_type == XCCL_FANOUT);
     if (!sync_only) {
@@ -231,8 +243,8 @@ xccl_status_t HostReq::prepare()
         d_src_       = src;
         d_dst_       = dst;
         h_src_bytes_ = src_bytes;
-        h_dst_bytes_ = dst_bytes;
-        h_dst_       = (char *)std::malloc(std::max<size_t>(dst_bytes, 1));
+        h_dst_bytes_ = epi_ ? epi_count_ * xccl_dt_size(epi_out_dt_) : dst_bytes;
+        h_dst_       = (char *)std::malloc(std::max<size_t>(std::max(dst_bytes, h_dst_bytes_), 1));
         bool aliased = (src == dst);
         h_src_       = aliased ? nullptr : (char *)std::malloc(std::max<size_t>(src_bytes, 1));
         if (h_dst_ == nullptr || (!aliased && h_src_ == nullptr)) return XCCL_ERR_NO_MEMORY;
@@ -244,6 +256,16 @@ xccl_status_t HostReq::prepare()
     } else {
         b.src = src;
         b.dst = dst;
+    }
+    if (epi_) {
+        // reduce in the input datatype into a private buffer, convert into the real destination
+        epi_dst_ = b.dst;
+        epi_buf_.resize(std::max<size_t>(dst_bytes, 1));
+        if (b.src == b.dst) {
+            // in place: the private buffer starts as a copy of the input (made at post time)
+            b.src = nullptr;
+        }
+        b.dst = epi_buf_.data();
     }
     return XCCL_OK;
 }
@@ -268,7 +290,19 @@ Coro HostReq::run()
             if (st != XCCL_OK) co_return st;
         }
     }
-    XCCL_CO_CALL(algo_(*this));
+    if (epi_ && b.src == nullptr) {
+        // in-place call: seed the private buffer with the input that sits in the destination
+        std::memcpy(epi_buf_.data(), epi_dst_, epi_buf_.size());
+        b.src = epi_buf_.data();
+        XCCL_CO_CALL(algo_(*this));
+        b.src = nullptr;
+    } else {
+        XCCL_CO_CALL(algo_(*this));
+    }
+    if (epi_ && !(args.coll_type == XCCL_REDUCE && team->rank != b.root)) {
+        xccl_status_t cst = host_scale_cast(epi_buf_.data(), b.dt, epi_dst_, epi_out_dt_, epi_count_, epi_scale_);
+        if (cst != XCCL_OK) co_return cst;
+    }
     if (staged) {
         bool has_result = true;
         if (args.coll_type == XCCL_REDUCE && team->rank != b.root) has_result = false;

@@ -75,6 +75,13 @@ private:
     void  *event_ = nullptr;
     struct StreamHoldRef;
     void  *hold_ = nullptr;
+    // fused epilogue (scale, cast): the algorithm reduces into epi_buf_, the result is converted into epi_dst_
+    bool              epi_ = false;
+    float             epi_scale_ = 1.0f;
+    xccl_dt_t         epi_out_dt_ = XCCL_DT_UNSUPPORTED;
+    size_t            epi_count_ = 0;
+    char             *epi_dst_ = nullptr;
+    std::vector<char> epi_buf_;
 };
 
 class HostTeam final : public TlTeam {

@@ -30,6 +30,8 @@ xccl_status_t host_reduce(const void *a, const void *b, void *dst, size_t count,
 xccl_status_t host_reduce_multi(const void *a, const void *vecs, void *dst, size_t n_vectors, size_t count,
                                 size_t stride_bytes, xccl_dt_t dt, xccl_op_t op);
 bool          host_reduce_supported(xccl_dt_t dt, xccl_op_t op);
+// dst[i] = out_cast(scale * src[i]); out_dt == XCCL_DT_UNSUPPORTED keeps dt. Same pairs as the GPU epilogue.
+xccl_status_t host_scale_cast(const void *src, xccl_dt_t dt, void *dst, xccl_dt_t out_dt, size_t count, float scale);
 
 // Copies between any two memory types. With a stream the device side is asynchronous on it.
 xccl_status_t mem_copy(void *dst, const void *src, size_t bytes, xccl_memory_type_t dst_mem, xccl_memory_type_t src_mem,

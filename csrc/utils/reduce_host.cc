@@ -156,6 +156,50 @@ xccl_status_t host_reduce_multi(const void *a, const void *v, void *d, size_t n,
     }
 }
 
+namespace {
+template <typename T, typename O> void scale_cast(const void *src_, void *dst_, size_t count, float scale)
+{
+    const T *src = (const T *)src_;
+    O       *dst = (O *)dst_;
+    for (size_t i = 0; i < count; i++) {
+        auto v = load<T>(src[i]);
+        if constexpr (std::is_integral<decltype(v)>::value) {
+            dst[i] = store<O>((typename Acc<O>::type)((float)v * scale));
+        } else {
+            dst[i] = store<O>((typename Acc<O>::type)(v * (decltype(v))scale));
+        }
+    }
+}
+}  // namespace
+
+// dst[i] = out_cast(scale * src[i]): the host form of the fused collective epilogue.
+xccl_status_t host_scale_cast(const void *src, xccl_dt_t dt, void *dst, xccl_dt_t out_dt, size_t count, float scale)
+{
+    if (out_dt == XCCL_DT_UNSUPPORTED || out_dt == XCCL_DT_LAST_PREDEFINED) out_dt = dt;
+    if (out_dt == dt) {
+        switch (dt) {
+        case XCCL_DT_INT8: scale_cast<int8_t, int8_t>(src, dst, count, scale); return XCCL_OK;
+        case XCCL_DT_INT16: scale_cast<int16_t, int16_t>(src, dst, count, scale); return XCCL_OK;
+        case XCCL_DT_INT32: scale_cast<int32_t, int32_t>(src, dst, count, scale); return XCCL_OK;
+        case XCCL_DT_INT64: scale_cast<int64_t, int64_t>(src, dst, count, scale); return XCCL_OK;
+        case XCCL_DT_UINT8: scale_cast<uint8_t, uint8_t>(src, dst, count, scale); return XCCL_OK;
+        case XCCL_DT_UINT16: scale_cast<uint16_t, uint16_t>(src, dst, count, scale); return XCCL_OK;
+        case XCCL_DT_UINT32: scale_cast<uint32_t, uint32_t>(src, dst, count, scale); return XCCL_OK;
+        case XCCL_DT_UINT64: scale_cast<uint64_t, uint64_t>(src, dst, count, scale); return XCCL_OK;
+        case XCCL_DT_FLOAT16: scale_cast<Half, Half>(src, dst, count, scale); return XCCL_OK;
+        case XCCL_DT_BFLOAT16: scale_cast<BFloat, BFloat>(src, dst, count, scale); return XCCL_OK;
+        case XCCL_DT_FLOAT32: scale_cast<float, float>(src, dst, count, scale); return XCCL_OK;
+        case XCCL_DT_FLOAT64: scale_cast<double, double>(src, dst, count, scale); return XCCL_OK;
+        default: return XCCL_ERR_UNSUPPORTED;
+        }
+    }
+    if (dt == XCCL_DT_FLOAT32 && out_dt == XCCL_DT_BFLOAT16) { scale_cast<float, BFloat>(src, dst, count, scale); return XCCL_OK; }
+    if (dt == XCCL_DT_FLOAT32 && out_dt == XCCL_DT_FLOAT16) { scale_cast<float, Half>(src, dst, count, scale); return XCCL_OK; }
+    if (dt == XCCL_DT_BFLOAT16 && out_dt == XCCL_DT_FLOAT32) { scale_cast<BFloat, float>(src, dst, count, scale); return XCCL_OK; }
+    if (dt == XCCL_DT_FLOAT16 && out_dt == XCCL_DT_FLOAT32) { scale_cast<Half, float>(src, dst, count, scale); return XCCL_OK; }
+    return XCCL_ERR_UNSUPPORTED;
+}
+
 xccl_status_t host_reduce(const void *a, const void *b, void *dst, size_t count, xccl_dt_t dt, xccl_op_t op)
 {
     return host_reduce_multi(a, b, dst, 1, count, 0, dt, op);

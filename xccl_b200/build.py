@@ -132,7 +132,7 @@ def build_torch_ext(force: bool = False, verbose: bool = False) -> Path | None:
     cmd = [CXX, "-std=c++17", "-O2", "-fPIC", "-shared", f"-D_GLIBCXX_USE_CXX11_ABI={abi}",
            "-DTORCH_EXTENSION_NAME=xccl_torch", "-DTORCH_API_INCLUDE_EXTENSION_H", *inc, *map(str, srcs),
            "-o", str(target), f"-L{OUT_DIR}", "-lxccl", f"-L{torch_lib}", "-ltorch", "-ltorch_cpu", "-lc10",
-           "-ltorch_python", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{torch_lib}"]
+           "-ltorch_python", "-ltorch_cuda", "-lc10_cuda", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{torch_lib}"]
     if verbose:
         print(" ".join(cmd), flush=True)
     r = subprocess.run(cmd, capture_output=True, text=True)
