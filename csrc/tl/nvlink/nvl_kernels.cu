@@ -106,6 +106,91 @@ template <typename O, int E> __device__ __forceinline__ bool out_aligned(const O
     return ((uintptr_t)dst % a) == 0;
 }
 
+
+// Memory-level parallelism. One 16-byte access per thread per iteration keeps only ~8 KB per SM
+// in flight, far too little to cover NVLink latency, so every streaming loop issues U loads
+// before the first dependent store.
+template <int U, typename LoadFn, typename StoreFn>
+__device__ __forceinline__ void stream_packs(size_t lo, size_t hi, LoadFn ld, StoreFn st)
+{
+    const size_t bd = blockDim.x;
+    size_t       i  = lo + threadIdx.x;
+    for (; i + (U - 1) * bd < hi; i += U * bd) {
+        uint4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) v[u] = ld(i + u * bd);
+#pragma unroll
+        for (int u = 0; u < U; u++) st(i + u * bd, v[u]);
+    }
+    for (; i < hi; i += bd) st(i, ld(i));
+}
+
+// Reduces pack i of n source arrays (src_of(q) + i * 16) and hands the accumulators to out(i, acc).
+// The combination order is q = 0, 1, ... on every rank, so all ranks compute identical bits.
+template <typename T, bool kSum, int U, typename SrcFn, typename OutFn>
+__device__ __forceinline__ void reduce_packs(SrcFn src_of, int n, size_t lo, size_t hi, int op, OutFn out)
+{
+    using A         = typename Traits<T>::acc;
+    constexpr int E = Epp<T>::value;
+    const size_t  bd = blockDim.x;
+    size_t        i  = lo + threadIdx.x;
+    constexpr int kN = 8;  // sources loaded per batch
+    auto one = [&](size_t idx) {
+        A acc[E];
+        for (int q0 = 0; q0 < n; q0 += kN) {
+            uint4 raw[kN];
+#pragma unroll
+            for (int q = 0; q < kN; q++) {
+                if (q0 + q < n) raw[q] = ld_nc16(src_of(q0 + q) + idx * 16);
+            }
+#pragma unroll
+            for (int q = 0; q < kN; q++) {
+                if (q0 + q < n) {
+                    auto y = from_raw<T>(raw[q]);
+                    if (q0 + q == 0) {
+#pragma unroll
+                        for (int e = 0; e < E; e++) acc[e] = Traits<T>::up(y.v[e]);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < E; e++) acc[e] = dev::combine<T, kSum>(op, acc[e], Traits<T>::up(y.v[e]));
+                    }
+                }
+            }
+        }
+        out(idx, acc);
+    };
+    if (U == 2 && E <= 8 && n <= 4) {
+        // few sources: two packs per thread in flight
+        for (; i + bd < hi; i += 2 * bd) {
+            uint4 ra[4], rb[4];
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                if (q < n) {
+                    const char *sq = src_of(q);
+                    ra[q] = ld_nc16(sq + i * 16);
+                    rb[q] = ld_nc16(sq + (i + bd) * 16);
+                }
+            }
+            A acc_a[E], acc_b[E];
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                if (q < n) {
+                    auto ya = from_raw<T>(ra[q]);
+                    auto yb = from_raw<T>(rb[q]);
+#pragma unroll
+                    for (int e = 0; e < E; e++) {
+                        acc_a[e] = (q == 0) ? Traits<T>::up(ya.v[e]) : dev::combine<T, kSum>(op, acc_a[e], Traits<T>::up(ya.v[e]));
+                        acc_b[e] = (q == 0) ? Traits<T>::up(yb.v[e]) : dev::combine<T, kSum>(op, acc_b[e], Traits<T>::up(yb.v[e]));
+                    }
+                }
+            }
+            out(i, acc_a);
+            out(i + bd, acc_b);
+        }
+    }
+    for (; i < hi; i += bd) one(i);
+}
+
 // ------------------------------------------------------------------ allreduce: one-shot
 
 template <typename T, typename O, bool kSum>
@@ -123,31 +208,19 @@ __global__ void __launch_bounds__(512) allreduce_one_shot_kernel(World w, Call c
     const bool    dst_al = out_aligned<O, E>(dst);
     const Range   r      = block_range(npacks);
 
-    for (size_t i = r.lo + threadIdx.x; i < r.hi; i += blockDim.x) {
-        uint4 v = load_pack<T>(src, i, c.count, src_al);
-        for (int p = 0; p < w.size; p++) {
-            st_16(w.ws[p] + hoff + (size_t)s.rank * slot + i * 16, v);
-        }
-    }
+    stream_packs<4>(
+        r.lo, r.hi, [&](size_t i) { return load_pack<T>(src, i, c.count, src_al); },
+        [&](size_t i, uint4 v) {
+            for (int p = 0; p < w.size; p++) st_16(w.ws[p] + hoff + (size_t)s.rank * slot + i * 16, v);
+        });
     block_barrier(w, s);
     if (!s.failed) {
         const char *mine = w.ws[s.rank] + hoff;
-        for (size_t i = r.lo + threadIdx.x; i < r.hi; i += blockDim.x) {
-            A acc[E];
-            {
-                auto x = from_raw<T>(ld_nc16(mine + i * 16));
-#pragma unroll
-                for (int e = 0; e < E; e++) acc[e] = Traits<T>::up(x.v[e]);
-            }
-            for (int q = 1; q < w.size; q++) {
-                auto y = from_raw<T>(ld_nc16(mine + (size_t)q * slot + i * 16));
-#pragma unroll
-                for (int e = 0; e < E; e++) acc[e] = dev::combine<T, kSum>(c.op, acc[e], Traits<T>::up(y.v[e]));
-            }
+        reduce_packs<T, kSum, 2>([&](int q) { return mine + (size_t)q * slot; }, w.size, r.lo, r.hi, c.op, [&](size_t i, A(&acc)[E]) {
 #pragma unroll
             for (int e = 0; e < E; e++) acc[e] = dev::scaled(acc[e], c.scale, c.do_scale != 0);
             store_out<O, E>(dst, i, c.count, dst_al, acc);
-        }
+        });
     }
     self_end(w, s);
 }
@@ -184,9 +257,9 @@ __global__ void __launch_bounds__(512) allreduce_two_shot_kernel(World w, Call c
         char        *mine  = w.ws[s.rank] + hoff;
 
         // 1. my input piece -> my workspace
-        for (size_t i = r.lo + threadIdx.x; i < r.hi; i += blockDim.x) {
-            st_16(mine + i * 16, load_pack<T>(src + e_off, i, cnt, src_al));
-        }
+        stream_packs<4>(
+            r.lo, r.hi, [&](size_t i) { return load_pack<T>(src + e_off, i, cnt, src_al); },
+            [&](size_t i, uint4 v) { st_16(mine + i * 16, v); });
         block_barrier(w, s);
         if (s.failed) break;
 
@@ -194,42 +267,24 @@ __global__ void __launch_bounds__(512) allreduce_two_shot_kernel(World w, Call c
         const Range m = sub_range(r, w.size, s.rank);
         if (kNvls) {
             char *mc = w.mc_ws + hoff;
-            for (size_t i = m.lo + threadIdx.x; i < m.hi; i += blockDim.x) {
-                uint4 v = nvls_reduce<T>(mc + i * 16);
-                if (c.do_scale) {
-                    auto x = from_raw<T>(v);
+            stream_packs<4>(
+                m.lo, m.hi, [&](size_t i) { return nvls_reduce<T>(mc + i * 16); },
+                [&](size_t i, uint4 v) {
+                    if (c.do_scale) {
+                        auto x = from_raw<T>(v);
 #pragma unroll
-                    for (int e = 0; e < E; e++) x.v[e] = Traits<T>::down(dev::scaled(Traits<T>::up(x.v[e]), c.scale, true));
-                    v = as_raw<T>(x);
-                }
-                mm_st_16(mc + i * 16, v);
-            }
-        } else {
-            for (size_t i = m.lo + threadIdx.x; i < m.hi; i += blockDim.x) {
-                uint4 raw[kMaxRanks];
-#pragma unroll
-                for (int p = 0; p < kMaxRanks; p++) {
-                    if (p < w.size) raw[p] = ld_nc16(w.ws[p] + hoff + i * 16);
-                }
-                A acc[E];
-                {
-                    auto x = from_raw<T>(raw[0]);
-#pragma unroll
-                    for (int e = 0; e < E; e++) acc[e] = Traits<T>::up(x.v[e]);
-                }
-#pragma unroll
-                for (int p = 1; p < kMaxRanks; p++) {
-                    if (p < w.size) {
-                        auto y = from_raw<T>(raw[p]);
-#pragma unroll
-                        for (int e = 0; e < E; e++) acc[e] = dev::combine<T, kSum>(c.op, acc[e], Traits<T>::up(y.v[e]));
+                        for (int e = 0; e < E; e++) x.v[e] = Traits<T>::down(dev::scaled(Traits<T>::up(x.v[e]), c.scale, true));
+                        v = as_raw<T>(x);
                     }
-                }
+                    mm_st_16(mc + i * 16, v);
+                });
+        } else {
+            reduce_packs<T, kSum, 2>([&](int q) { return (const char *)w.ws[q] + hoff; }, w.size, m.lo, m.hi, c.op, [&](size_t i, A(&acc)[E]) {
                 Pack<T, E> out;
 #pragma unroll
                 for (int e = 0; e < E; e++) out.v[e] = Traits<T>::down(dev::scaled(acc[e], c.scale, c.do_scale != 0));
                 st_16(mine + i * 16, as_raw<T>(out));
-            }
+            });
         }
         block_barrier(w, s);
         if (s.failed) break;
@@ -239,13 +294,15 @@ __global__ void __launch_bounds__(512) allreduce_two_shot_kernel(World w, Call c
             const int   p    = (s.rank + q) % w.size;  // start with my own share, spread the peers
             const Range g    = sub_range(r, w.size, p);
             const char *from = (kNvls ? mine : w.ws[p] + hoff);
-            for (size_t i = g.lo + threadIdx.x; i < g.hi; i += blockDim.x) {
-                auto x = from_raw<T>(ld_nc16(from + i * 16));
-                A    acc[E];
+            stream_packs<4>(
+                g.lo, g.hi, [&](size_t i) { return ld_nc16(from + i * 16); },
+                [&](size_t i, uint4 v) {
+                    auto x = from_raw<T>(v);
+                    A    acc[E];
 #pragma unroll
-                for (int e = 0; e < E; e++) acc[e] = Traits<T>::up(x.v[e]);
-                store_out<O, E>(dst + e_off, i, cnt, dst_al, acc);
-            }
+                    for (int e = 0; e < E; e++) acc[e] = Traits<T>::up(x.v[e]);
+                    store_out<O, E>(dst + e_off, i, cnt, dst_al, acc);
+                });
         }
     }
     self_end(w, s);
@@ -280,37 +337,19 @@ __global__ void __launch_bounds__(512) reduce_kernel(World w, Call c)
         for (int q = 0; q < nseg; q++) {
             const T   *seg = src + (size_t)q * c.count + e_off;
             const bool al  = ((uintptr_t)seg & 15) == 0;
-            for (size_t i = r.lo + threadIdx.x; i < r.hi; i += blockDim.x) {
-                st_16(mine + ((size_t)q * n + i) * 16, load_pack<T>(seg, i, cnt, al));
-            }
+            stream_packs<4>(
+                r.lo, r.hi, [&](size_t i) { return load_pack<T>(seg, i, cnt, al); },
+                [&](size_t i, uint4 v) { st_16(mine + ((size_t)q * n + i) * 16, v); });
         }
         block_barrier(w, s);
         if (s.failed) break;
         if (i_reduce) {
-            for (size_t i = r.lo + threadIdx.x; i < r.hi; i += blockDim.x) {
-                uint4 raw[kMaxRanks];
-#pragma unroll
-                for (int p = 0; p < kMaxRanks; p++) {
-                    if (p < w.size) raw[p] = ld_nc16(w.ws[p] + hoff + ((size_t)my_seg * n + i) * 16);
-                }
-                A acc[E];
-                {
-                    auto x = from_raw<T>(raw[0]);
-#pragma unroll
-                    for (int e = 0; e < E; e++) acc[e] = Traits<T>::up(x.v[e]);
-                }
-#pragma unroll
-                for (int p = 1; p < kMaxRanks; p++) {
-                    if (p < w.size) {
-                        auto y = from_raw<T>(raw[p]);
-#pragma unroll
-                        for (int e = 0; e < E; e++) acc[e] = dev::combine<T, kSum>(c.op, acc[e], Traits<T>::up(y.v[e]));
-                    }
-                }
+            const size_t seg_off = hoff + (size_t)my_seg * n * 16;
+            reduce_packs<T, kSum, 2>([&](int q) { return (const char *)w.ws[q] + seg_off; }, w.size, r.lo, r.hi, c.op, [&](size_t i, A(&acc)[E]) {
 #pragma unroll
                 for (int e = 0; e < E; e++) acc[e] = dev::scaled(acc[e], c.scale, c.do_scale != 0);
                 store_out<O, E>(dst + e_off, i, cnt, dst_al, acc);
-            }
+            });
         }
     }
     self_end(w, s);
@@ -364,15 +403,16 @@ template <int KIND, bool kMc> __global__ void __launch_bounds__(512) mover_kerne
                 Byte       *own = nullptr;  // bcast root with a separate dst keeps a local copy too
                 if (KIND == MV_BCAST && dst != src) own = dst + b_off;
                 const bool own_al = ((uintptr_t)own & 15) == 0;
-                for (size_t i = r.lo + threadIdx.x; i < r.hi; i += blockDim.x) {
-                    uint4 v = load_pack<Byte>(seg, i, left, al);
-                    if (kMc) {
-                        mm_st_16(w.mc_ws + hoff + i * 16, v);
-                    } else {
-                        st_16(mine + ((size_t)q * n + i) * 16, v);
-                    }
-                    if (own != nullptr) store_bytes(own, i, left, own_al, v);
-                }
+                stream_packs<4>(
+                    r.lo, r.hi, [&](size_t i) { return load_pack<Byte>(seg, i, left, al); },
+                    [&](size_t i, uint4 v) {
+                        if (kMc) {
+                            mm_st_16(w.mc_ws + hoff + i * 16, v);
+                        } else {
+                            st_16(mine + ((size_t)q * n + i) * 16, v);
+                        }
+                        if (own != nullptr) store_bytes(own, i, left, own_al, v);
+                    });
             }
         }
         block_barrier(w, s);
@@ -382,9 +422,10 @@ template <int KIND, bool kMc> __global__ void __launch_bounds__(512) mover_kerne
             if (s.rank != c.root) {
                 Byte      *out = dst + b_off;
                 const bool al  = ((uintptr_t)out & 15) == 0;
-                for (size_t i = r.lo + threadIdx.x; i < r.hi; i += blockDim.x) {
-                    store_bytes(out, i, left, al, ld_nc16((kMc ? mine : w.ws[c.root] + hoff) + i * 16));
-                }
+                const char *from = kMc ? mine : w.ws[c.root] + hoff;
+                stream_packs<4>(
+                    r.lo, r.hi, [&](size_t i) { return ld_nc16(from + i * 16); },
+                    [&](size_t i, uint4 v) { store_bytes(out, i, left, al, v); });
             }
         } else {
             for (int q = 0; q < w.size; q++) {
@@ -393,9 +434,9 @@ template <int KIND, bool kMc> __global__ void __launch_bounds__(512) mover_kerne
                 const char *from = w.ws[p] + hoff + (size_t)seg * n * 16;
                 Byte       *out  = dst + (size_t)p * seg_bytes + b_off;
                 const bool  al   = ((uintptr_t)out & 15) == 0;
-                for (size_t i = r.lo + threadIdx.x; i < r.hi; i += blockDim.x) {
-                    store_bytes(out, i, left, al, ld_nc16(from + i * 16));
-                }
+                stream_packs<4>(
+                    r.lo, r.hi, [&](size_t i) { return ld_nc16(from + i * 16); },
+                    [&](size_t i, uint4 v) { store_bytes(out, i, left, al, v); });
             }
         }
     }
@@ -424,9 +465,9 @@ __global__ void __launch_bounds__(512) alltoallv_kernel(World w, Call c)
         const Byte  *seg   = src + (size_t)sd[q] * c.src_es;
         const bool   al    = ((uintptr_t)seg & 15) == 0;
         const Range  r     = block_range(n);
-        for (size_t i = r.lo + threadIdx.x; i < r.hi; i += blockDim.x) {
-            st_16(mine + off + i * 16, load_pack<Byte>(seg, i, bytes, al));
-        }
+        stream_packs<4>(
+            r.lo, r.hi, [&](size_t i) { return load_pack<Byte>(seg, i, bytes, al); },
+            [&](size_t i, uint4 v) { st_16(mine + off + i * 16, v); });
         off += n * 16;
     }
     block_barrier(w, s);
@@ -444,9 +485,9 @@ __global__ void __launch_bounds__(512) alltoallv_kernel(World w, Call c)
             Byte        *out   = dst + (size_t)dd[p] * c.dst_es;
             const bool   al    = ((uintptr_t)out & 15) == 0;
             const Range  r     = block_range(n);
-            for (size_t i = r.lo + threadIdx.x; i < r.hi; i += blockDim.x) {
-                store_bytes(out, i, bytes, al, ld_nc16(peer + poff + i * 16));
-            }
+            stream_packs<4>(
+                r.lo, r.hi, [&](size_t i) { return ld_nc16(peer + poff + i * 16); },
+                [&](size_t i, uint4 v) { store_bytes(out, i, bytes, al, v); });
         }
     }
     self_end(w, s);
@@ -557,7 +598,7 @@ xccl_status_t allreduce_typed(const World &w, const Call &c, Alg alg, const Laun
     if (alg == ALG_ONE_SHOT) {
         if (npacks * 16 * (size_t)w.size > w.ws_bytes / 2) return XCCL_ERR_BUFFER_TOO_SMALL;
         auto k      = sum ? allreduce_one_shot_kernel<T, O, true> : allreduce_one_shot_kernel<T, O, false>;
-        int  blocks = pick_blocks(k, w, cfg, npacks, 2);
+        int  blocks = pick_blocks(k, w, cfg, npacks, 1);
         return launch(k, dim3((unsigned)blocks, (unsigned)w.n_local), block, cfg.cooperative, stream, w, c);
     }
     if (alg == ALG_NVLS) {
@@ -565,11 +606,11 @@ xccl_status_t allreduce_typed(const World &w, const Call &c, Alg alg, const Laun
                              std::is_same<T, __nv_bfloat16>::value;
         if (!can || !sum || w.mc_ws == nullptr) return XCCL_ERR_UNSUPPORTED;
         auto k      = allreduce_two_shot_kernel<T, O, true, true>;
-        int  blocks = pick_blocks(k, w, cfg, npacks, 8);
+        int  blocks = pick_blocks(k, w, cfg, npacks, 2);
         return launch(k, dim3((unsigned)blocks, (unsigned)w.n_local), block, cfg.cooperative, stream, w, c);
     }
     auto k      = sum ? allreduce_two_shot_kernel<T, O, true, false> : allreduce_two_shot_kernel<T, O, false, false>;
-    int  blocks = pick_blocks(k, w, cfg, npacks, 8);
+    int  blocks = pick_blocks(k, w, cfg, npacks, 2);
     return launch(k, dim3((unsigned)blocks, (unsigned)w.n_local), block, cfg.cooperative, stream, w, c);
 }
 
@@ -580,7 +621,7 @@ xccl_status_t reduce_typed(const World &w, const Call &c, const LaunchCfg &cfg, 
     const size_t  npacks = (c.count + E - 1) / E;
     const bool    sum    = (c.op == XCCL_OP_SUM);
     auto          k      = sum ? reduce_kernel<T, O, true, kScatter> : reduce_kernel<T, O, false, kScatter>;
-    int           blocks = pick_blocks(k, w, cfg, npacks * (kScatter ? w.size : 1), 8);
+    int           blocks = pick_blocks(k, w, cfg, npacks * (kScatter ? w.size : 1), 2);
     return launch(k, dim3((unsigned)blocks, (unsigned)w.n_local), dim3((unsigned)cfg.threads), cfg.cooperative, stream,
                   w, c);
 }
@@ -625,7 +666,7 @@ static xccl_status_t mover(const World &w, const Call &c, const LaunchCfg &cfg, 
     size_t npacks = (seg + 15) / 16;
     if (npacks == 0) return XCCL_OK;
     auto k      = mover_kernel<KIND, kMc>;
-    int  blocks = pick_blocks(k, w, cfg, npacks * (KIND == MV_BCAST ? 1 : (size_t)w.size), 8);
+    int  blocks = pick_blocks(k, w, cfg, npacks * (KIND == MV_BCAST ? 1 : (size_t)w.size), 2);
     return launch(k, dim3((unsigned)blocks, (unsigned)w.n_local), dim3((unsigned)cfg.threads), cfg.cooperative, stream,
                   w, c);
 }
@@ -654,7 +695,7 @@ xccl_status_t launch_alltoallv(const World &w, const Call &c, size_t max_src_byt
     size_t need = kVHeaderBytes + max_src_bytes + (size_t)w.size * 16;
     if (need > w.ws_bytes / 2) return XCCL_ERR_BUFFER_TOO_SMALL;
     auto k      = alltoallv_kernel;
-    int  blocks = pick_blocks(k, w, cfg, (max_src_bytes + 15) / 16, 8);
+    int  blocks = pick_blocks(k, w, cfg, (max_src_bytes + 15) / 16, 2);
     return launch(k, dim3((unsigned)blocks, (unsigned)w.n_local), dim3((unsigned)cfg.threads), cfg.cooperative, stream,
                   w, c);
 }

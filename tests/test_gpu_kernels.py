@@ -315,3 +315,51 @@ def test_tp_mlp_end_to_end_from_pinned_host(dev):
         assert m.device.type == "cpu" and torch.isfinite(m)
     finally:
         mlp.close()
+
+
+# ----------------------------------------------------------------------------- fused MoE all-to-all
+@pytest.mark.parametrize("ranks", [1, 2, 4])
+def test_moe_dispatch_combine_matches_reference(dev, ranks):
+    """Routing, grouping by (expert, source) and the weighted combine, ranks emulated in one launch."""
+    from xccl_b200.ops.moe import MoeWorkspace
+    T, H, E, Kk = 96, 256, 8 * ranks, 4
+    EL = E // ranks
+    ws = MoeWorkspace(T, H, E, Kk, emu_ranks=ranks)
+    try:
+        g = torch.Generator(device="cpu").manual_seed(ranks)
+        xs = [torch.randn(T, H, generator=g).to(torch.bfloat16).to(dev) for _ in range(ranks)]
+        ids = [torch.stack([torch.randperm(E, generator=g)[:Kk] for _ in range(T)]).to(torch.int32).to(dev) for _ in range(ranks)]
+        ws_ = [torch.softmax(torch.randn(T, Kk, generator=g), -1).to(dev) for _ in range(ranks)]
+        for it in range(2):
+            ws.dispatch(xs, ids)
+            assert ws.error() == 0
+            # every rank holds, per local expert, exactly the rows routed to it, grouped by source
+            for r in range(ranks):
+                rows = ws.expert_rows(r).cpu().tolist()
+                recv, src = ws.recv(r), ws.row_source(r).cpu()
+                row = 0
+                for le in range(EL):
+                    e = r * EL + le
+                    want_n = sum(int((ids[s] == e).sum()) for s in range(ranks))
+                    assert rows[le] == want_n
+                    last_src = -1
+                    for i in range(rows[le]):
+                        s, t = divmod(int(src[row + i]), T)
+                        assert s >= last_src          # sources appear in rank order inside an expert
+                        last_src = s
+                        assert bool((ids[s][t] == e).any())
+                        assert torch.equal(recv[row + i], xs[s][t])
+                    row += rows[le]
+                assert rows[EL] == row
+                # "experts": scale each row by (1 + global expert id)
+                scale = torch.cat([torch.full((rows[le],), 1.0 + r * EL + le) for le in range(EL)]).to(dev)
+                ws.expert_out(r)[:row] = (recv[:row].float() * scale[:, None]).to(torch.bfloat16)
+            outs = [torch.zeros(T, H, dtype=torch.bfloat16, device=dev) for _ in range(ranks)]
+            ws.combine(ids, ws_, outs)
+            assert ws.error() == 0
+            for r in range(ranks):
+                y = (xs[r].float()[:, None, :] * (1.0 + ids[r].float())[:, :, None]).to(torch.bfloat16).float()
+                want = (y * ws_[r][:, :, None]).sum(1)
+                torch.testing.assert_close(outs[r].float(), want, rtol=2e-2, atol=2e-2)
+    finally:
+        ws.close()
