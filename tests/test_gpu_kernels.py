@@ -363,3 +363,17 @@ def test_moe_dispatch_combine_matches_reference(dev, ranks):
                 torch.testing.assert_close(outs[r].float(), want, rtol=2e-2, atol=2e-2)
     finally:
         ws.close()
+
+
+# ----------------------------------------------------------------------------- block-scaled fp8 GEMM
+@pytest.mark.parametrize("M,N,K_", [(128, 128, 128), (256, 384, 512), (1000, 256, 1024)])
+def test_gemm_fp8_blockscaled_matches_dequantised_reference(dev, M, N, K_):
+    from xccl_b200.ops import gemm
+    a = torch.randn(M, K_, device=dev) * torch.rand(M, 1, device=dev) * 3
+    b = torch.randn(N, K_, device=dev) * 0.05
+    a8, sa = gemm.quantize_act_1x128(a)
+    b8, sb = gemm.quantize_weight_128x128(b)
+    out = gemm.gemm_fp8_blockscaled(a8, sa, b8, sb)
+    assert gemm.last_error() == 0
+    want = gemm.dequantize(a8, sa, 1) @ gemm.dequantize(b8, sb, 128).t()
+    torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2 * float(want.abs().max()))
