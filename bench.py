@@ -32,28 +32,47 @@ METRIC = "tp_mlp_step_tokens_per_s"
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    """Samples SM clocks and throttle reasons of one GPU through NVML (read-only queries) from a
+    thread of this process, every few milliseconds, while a region runs."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    PERIOD_S = 0.004
 
     def __init__(self, index: int):
-        self.index, self.proc, self.lines = index, None, []
+        self.index, self.samples, self.handle, self.nv = index, [], None, None
+        self._stop = threading.Event()
+        self.thread = None
 
     def start(self) -> None:
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
-                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
+            import pynvml as nv
+            nv.nvmlInit()
+            try:
+                import torch
+                uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+                self.handle = nv.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+            except Exception:
+                self.handle = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.nv = nv
+        except Exception:
+            self.nv = None
+            return
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
 
-    def _read(self) -> None:
-        for line in self.proc.stdout:
-            self.lines.append((time.monotonic(), line.strip()))
+    def _sample(self) -> None:
+        nv = self.nv
+        try:
+            sm = nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)
+            reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle) if hasattr(
+                nv, "nvmlDeviceGetCurrentClocksEventReasons") else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+            self.samples.append((time.monotonic(), sm, int(reasons)))
+        except Exception:
+            pass
+
+    def _run(self) -> None:
+        while not self._stop.is_set():
+            self._sample()
+            time.sleep(self.PERIOD_S)
 
     def mark_begin(self) -> None:
         self.t0 = time.monotonic()
@@ -62,41 +81,31 @@ class ClockSampler:
         self.t1 = time.monotonic()
 
     def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
+        if self.nv is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml unavailable"]}
+        self._stop.set()
+        self.thread.join(timeout=2)
+        nv = self.nv
         try:
-            self.proc.wait(timeout=2)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, smax, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+            smax = nv.nvmlDeviceGetMaxClockInfo(self.handle, nv.NVML_CLOCK_SM)
+        except Exception:
+            smax = None
+        masks = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
         t0, t1 = getattr(self, "t0", 0.0), getattr(self, "t1", float("inf"))
-        for ts, ln in self.lines:
-            if ts < t0 or ts > t1 + 0.15:  # a sample printed just after the region was taken inside it
+        sm, reasons = [], set()
+        for ts, mhz, bits in self.samples:
+            if ts < t0 or ts > t1:
                 continue
-            parts = [p.strip() for p in ln.split(",")]
-            if len(parts) < 8:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                smax.append(float(parts[1]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[4:8]):
-                if val.lower().startswith("active"):
+            sm.append(mhz)
+            for name, m in masks.items():
+                if bits & m:
                     reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax, "samples": len(sm),
+                "reasons": sorted(reasons)}
 
 
-def reference_arm(args) -> None:
-    """The reference (openucx/xccl) is an autotools C library that needs UCX and MPI; neither is in
-    this image and it cannot be installed with pip, so there is no reference arm to run."""
-    print(json.dumps({"impl": "reference",
-                      "unavailable": "openucx/xccl is an autotools C library that requires UCX (configure.ac:92-95) "
-                                     "and MPI for any multi-rank run; neither exists in this image and "
-                                     "`pip install /root/reference` has no setup.py/pyproject.toml to build"}))
+def reference_unavailable(why: str) -> None:
+    print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
 
 
 def main() -> None:
@@ -107,9 +116,11 @@ def main() -> None:
     ap.add_argument("--impl", default="xccl", choices=["xccl", "reference", "torch"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.impl == "reference":
+    ref_root = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline")
+    if args.impl == "reference" and not os.path.exists(os.path.join(ref_root, "_ref", "lib", "libxccl.so")):
         if int(os.environ.get("RANK", "0")) == 0:
-            reference_arm(args)
+            reference_unavailable("baseline/_ref/lib/libxccl.so is missing: the reference has no pip-installable "
+                                  "package; it is built from its unmodified sources by python baseline/build_ref.py")
         return
 
     import torch
@@ -141,7 +152,32 @@ def main() -> None:
         return float(t.item())
 
     oob = None
-    if args.impl == "xccl":
+    ref_session = None
+    if args.impl == "reference":
+        # the unmodified reference library: its NCCL team for the collectives, cuBLAS (torch.matmul) for the GEMMs
+        sys.path.insert(0, ref_root)
+        import ref_api
+        from ref_tp_mlp import RefTpMlp
+        if world == 1:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            os.environ.setdefault("MASTER_PORT", "29531")
+            dist.init_process_group("gloo", rank=0, world_size=1)
+            oob_group = None
+        else:
+            oob_group = dist.new_group(backend="gloo")
+        try:
+            ref_session = ref_api.RefSession(group=oob_group, tls=ref_api.TL_NCCL)
+        except Exception as exc:  # the library could not bring up its NCCL team here
+            if rank == 0:
+                reference_unavailable(f"reference library failed to start: {exc}")
+            return
+        model = RefTpMlp(TOKENS, HIDDEN, FFN, tp=world, rank=rank, session=ref_session)
+        model.x_shard.copy_(torch.randn(TOKENS // world, HIDDEN, device=dev).to(torch.bfloat16))
+        xp = torch.randn(TOKENS // world, HIDDEN).to(torch.bfloat16).pin_memory()
+        step = lambda: model.forward()                 # noqa: E731
+        e2e_step = lambda: model.forward_from_host(xp)  # noqa: E731
+        launches_per_step = 0
+    elif args.impl == "xccl":
         from xccl_b200.models.tp_mlp import TpMlp
         if world > 1:
             from xccl_b200.api import ShmOob
@@ -217,6 +253,9 @@ def main() -> None:
         model.close()
         if oob is not None:
             oob.close()
+    if ref_session is not None:
+        model.close()
+        ref_session.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

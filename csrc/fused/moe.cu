@@ -191,27 +191,60 @@ __global__ void __launch_bounds__(512) moe_combine_kernel(MoeParams p)
         const size_t warp = tid / 32, nwarps = nthr / 32;
         const int    packs = p.H * 2 / 16;
         for (size_t t = warp; t < (size_t)p.T; t += nwarps) {
-            for (int k0 = lane; k0 < packs; k0 += 32) {
-                float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-                for (int k = 0; k < p.K; k++) {
-                    const size_t i = t * p.K + k;
+            // routing entries of this token, eight at a time: lane k holds entry k, the warp shares them
+            // (with more than eight entries the running sum passes through bf16 between groups)
+            for (int kb = 0; kb < p.K; kb += 8) {
+                const int kn = min(8, p.K - kb);
+                const uint4 *my_row = nullptr;
+                float        my_g   = 0.0f;
+                if (lane < kn) {
+                    const size_t i = t * p.K + kb + lane;
                     const int    e = p.ids[local][i];
-                    if (e < 0 || e >= p.E) continue;
-                    const float  g   = p.w[local][i];
-                    const uint4  v   = nvl::ld_nc16(reinterpret_cast<const uint4 *>(p.yout[e / EL] + (size_t)p.slot[local][i] * p.H) + k0);
-                    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&v);
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        float2 f = __bfloat1622float2(h[j]);
-                        acc[2 * j] += g * f.x;
-                        acc[2 * j + 1] += g * f.y;
+                    if (e >= 0 && e < p.E) {
+                        my_g   = p.w[local][i];
+                        my_row = reinterpret_cast<const uint4 *>(p.yout[e / EL] + (size_t)p.slot[local][i] * p.H);
                     }
                 }
-                uint4 o;
-                __nv_bfloat162 *oh = reinterpret_cast<__nv_bfloat162 *>(&o);
+                const uint4 *rows[8];
+                float        gs[8];
 #pragma unroll
-                for (int j = 0; j < 4; j++) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-                reinterpret_cast<uint4 *>(p.out[local] + t * p.H)[k0] = o;
+                for (int k = 0; k < 8; k++) {
+                    rows[k] = reinterpret_cast<const uint4 *>(__shfl_sync(0xffffffffu, (unsigned long long)my_row, k));
+                    gs[k]   = __shfl_sync(0xffffffffu, my_g, k);
+                }
+                for (int k0 = lane; k0 < packs; k0 += 32) {
+                    // all expert rows of the pack are requested before the first one is used
+                    uint4 raw[8];
+#pragma unroll
+                    for (int k = 0; k < 8; k++) raw[k] = rows[k] ? nvl::ld_nc16(rows[k] + k0) : make_uint4(0, 0, 0, 0);
+                    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                    uint4 *dst = reinterpret_cast<uint4 *>(p.out[local] + t * p.H) + k0;
+                    if (kb > 0) {
+                        const uint4 prev = *dst;
+                        const __nv_bfloat162 *ph = reinterpret_cast<const __nv_bfloat162 *>(&prev);
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            float2 f = __bfloat1622float2(ph[j]);
+                            acc[2 * j] = f.x;
+                            acc[2 * j + 1] = f.y;
+                        }
+                    }
+#pragma unroll
+                    for (int k = 0; k < 8; k++) {
+                        const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw[k]);
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            float2 f = __bfloat1622float2(h[j]);
+                            acc[2 * j] += gs[k] * f.x;
+                            acc[2 * j + 1] += gs[k] * f.y;
+                        }
+                    }
+                    uint4 o;
+                    __nv_bfloat162 *oh = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+                    *dst = o;
+                }
             }
         }
     }

@@ -106,13 +106,31 @@ __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x));
 
 // Copy CTAs of the allgather mode: pull the remote row shards into the local gathered buffer,
 // one 128-row block at a time, and count each finished slice into ready[block].
-__device__ void copy_cta_loop(const GemmParams &p, int rank, int local, int copy_idx, int n_copy, const AbortFlag &ab)
+// One thread drives a ring of kCopySlots shared-memory slots with untiled bulk copies: the load of
+// chunk i (peer memory -> slot) is issued kCopyAhead chunks before its store (slot -> local buffer),
+// so every copy CTA keeps kCopyAhead * kCopyChunk bytes in flight on the wire without holding them
+// in registers.
+constexpr int      kCopySlots = 12;
+constexpr int      kCopyAhead = 8;
+constexpr int      kCopyLag   = 2;       // a block is announced once the stores of 2 later chunks were issued
+constexpr uint32_t kCopyChunk = 16384;
+static_assert(kCopySlots * kCopyChunk <= kStages * kStageBytes, "the copy ring reuses the pipeline stages");
+static_assert(kCopySlots <= 2 * kStages + 4, "one mbarrier per slot in the barrier area");
+
+__device__ void copy_cta_loop(const GemmParams &p, int rank, int local, int copy_idx, int n_copy, const AbortFlag &ab,
+                              uint32_t ring, uint32_t bars)
 {
     const int    tiles_m = (p.M + kBM - 1) / kBM;
     const int    mbs     = tiles_m / p.tp_size;
-    const size_t blk_packs = (size_t)kBM * p.K * 2 / 16;  // 16-byte packs in one row block
+    const size_t blk_bytes = (size_t)kBM * p.K * 2;
+    const size_t blk_packs = blk_bytes / 16;  // 16-byte packs in one row block
     const size_t per   = (blk_packs + n_copy - 1) / n_copy;
-    const size_t lo    = min((size_t)copy_idx * per, blk_packs), hi = min(lo + per, blk_packs);
+    const size_t lo    = min((size_t)copy_idx * per, blk_packs) * 16, hi = min(((size_t)copy_idx + 1) * per, blk_packs) * 16;
+    const int    cpb   = (int)((hi - lo + kCopyChunk - 1) / kCopyChunk);  // chunks of this CTA per row block
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kCopySlots; s++) mbar_init(bars + 8u * s, 1);
+        mbar_fence_init();
+    }
     // peers must have published their shards before we read them: barrier among the copy CTAs
     uint32_t *epoch_slot = p.pad[rank] + nvl::kPadEpochOff + copy_idx;
     uint32_t  epoch      = *epoch_slot + 1;
@@ -130,30 +148,78 @@ __device__ void copy_cta_loop(const GemmParams &p, int rank, int local, int copy
         }
         return;
     }
-    for (int i = 1; i < p.tp_size; i++) {
-        const int shard = (rank + i) % p.tp_size;
-        for (int mb_in = 0; mb_in < mbs; mb_in++) {
-            const int    mb   = shard * mbs + mb_in;
-            const size_t base = (size_t)mb * blk_packs;
-            const uint4 *from = reinterpret_cast<const uint4 *>(p.xg[shard]) + base;
-            uint4       *to   = reinterpret_cast<uint4 *>(p.xg[rank]) + base;
-            size_t       k    = lo + threadIdx.x;
-            for (; k + 3 * blockDim.x < hi; k += 4 * blockDim.x) {
-                uint4 v0 = nvl::ld_nc16(from + k), v1 = nvl::ld_nc16(from + k + blockDim.x);
-                uint4 v2 = nvl::ld_nc16(from + k + 2 * blockDim.x), v3 = nvl::ld_nc16(from + k + 3 * blockDim.x);
-                to[k] = v0;
-                to[k + blockDim.x] = v1;
-                to[k + 2 * blockDim.x] = v2;
-                to[k + 3 * blockDim.x] = v3;
+    if (threadIdx.x == 0) {
+        const int n_blocks = (p.tp_size - 1) * mbs;
+        auto block_of = [&](int b) {  // b-th remote row block in the order this rank pulls them
+            const int shard = (rank + 1 + b / mbs) % p.tp_size;
+            return shard * mbs + b % mbs;
+        };
+        auto announce = [&](int b) {
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            __threadfence();
+            red_release_gpu_add(p.ready[local] + block_of(b), 1u);
+        };
+        if (cpb == 0) {
+            for (int b = 0; b < n_blocks; b++) announce(b);
+        } else {
+            const int total = n_blocks * cpb;
+            auto span = [&](int g, size_t &off, uint32_t &bytes) {
+                const int b = g / cpb, c = g % cpb;
+                const size_t in = lo + (size_t)c * kCopyChunk;
+                off   = (size_t)block_of(b) * blk_bytes + in;
+                bytes = (uint32_t)min((size_t)kCopyChunk, hi - in);
+            };
+            char *dst = reinterpret_cast<char *>(p.xg[rank]);
+            bool ok = true;
+            int  loads_issued = 0, stores_issued = 0;
+            for (int i = 0; i < total + kCopyAhead && ok; i++) {
+                if (i < total) {
+                    // the slot's previous store (chunk i - kCopySlots) must have left shared memory
+                    if (i >= kCopySlots) bulk_wait_read<kCopySlots - 1 - kCopyAhead>();
+                    size_t   off;
+                    uint32_t bytes;
+                    span(i, off, bytes);
+                    const int      shard = block_of(i / cpb) / mbs;
+                    const uint32_t bar   = bars + 8u * (i % kCopySlots);
+                    mbar_arrive_expect_tx(bar, bytes);
+                    bulk_load(ring + (i % kCopySlots) * kCopyChunk, reinterpret_cast<const char *>(p.xg[shard]) + off, bytes, bar);
+                    loads_issued = i + 1;
+                }
+                const int j = i - kCopyAhead;
+                if (j >= 0) {
+                    if (!mbar_wait(bars + 8u * (j % kCopySlots), (uint32_t)(j / kCopySlots) & 1u, ab, 7)) {
+                        ok = false;
+                        break;
+                    }
+                    size_t   off;
+                    uint32_t bytes;
+                    span(j, off, bytes);
+                    bulk_store(dst + off, ring + (j % kCopySlots) * kCopyChunk, bytes);
+                    bulk_commit();
+                    stores_issued = j + 1;
+                    const int done = j - kCopyLag;
+                    if (done >= 0 && done % cpb == cpb - 1) {
+                        bulk_wait<kCopyLag>();
+                        announce(done / cpb);
+                    }
+                }
             }
-            for (; k < hi; k += blockDim.x) to[k] = nvl::ld_nc16(from + k);
-            __syncthreads();
-            if (threadIdx.x == 0) {
-                __threadfence();
-                red_release_gpu_add(p.ready[local] + mb, 1u);
+            if (ok) {
+                bulk_wait<0>();
+                for (int done = max(total - kCopyLag, 0); done < total; done++)
+                    if (done % cpb == cpb - 1) announce(done / cpb);
+            } else {
+                // leave no copy in flight into this CTA's shared memory: bounded second wait per slot
+                for (int j = stores_issued; j < loads_issued; j++) {
+                    const unsigned long long t0 = now_ns();
+                    while (!mbar_try_wait(bars + 8u * (j % kCopySlots), (uint32_t)(j / kCopySlots) & 1u) &&
+                           now_ns() - t0 < ab.budget_ns) {}
+                }
+                bulk_wait<0>();
             }
         }
     }
+    __syncthreads();
     // closing barrier: nobody overwrites a shard that a peer may still be reading
     epoch++;
     __syncthreads();
@@ -197,7 +263,7 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
 
     // ---- copy CTAs (allgather mode) never touch the tensor cores
     if ((int)blockIdx.x >= p.n_gemm_ctas) {
-        copy_cta_loop(p, rank, local, blockIdx.x - p.n_gemm_ctas, gridDim.x - p.n_gemm_ctas, ab);
+        copy_cta_loop(p, rank, local, blockIdx.x - p.n_gemm_ctas, gridDim.x - p.n_gemm_ctas, ab, smem_base, bars);
         return;
     }
 
@@ -443,14 +509,22 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
                 float acc[8];
 #pragma unroll
                 for (int e = 0; e < 8; e++) acc[e] = 0.0f;
-                for (int src = 0; src < p.tp_size; src++) {
-                    uint4 v = nvl::ld_nc16(mine + (size_t)src * slot_elems + row * (size_t)p.N + col);
-                    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&v);
+                // all partials of this pack are requested before the first one is used
+                uint4 raw[kMaxTpRanks];
 #pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        float2 f = __bfloat1622float2(h[e]);
-                        acc[2 * e] += f.x;
-                        acc[2 * e + 1] += f.y;
+                for (int src = 0; src < kMaxTpRanks; src++) {
+                    if (src < p.tp_size) raw[src] = nvl::ld_nc16(mine + (size_t)src * slot_elems + row * (size_t)p.N + col);
+                }
+#pragma unroll
+                for (int src = 0; src < kMaxTpRanks; src++) {
+                    if (src < p.tp_size) {
+                        const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw[src]);
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            float2 f = __bfloat1622float2(h[e]);
+                            acc[2 * e] += f.x;
+                            acc[2 * e + 1] += f.y;
+                        }
                     }
                 }
                 uint4 o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),

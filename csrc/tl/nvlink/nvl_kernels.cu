@@ -397,6 +397,21 @@ template <int KIND, bool kMc> __global__ void __launch_bounds__(512) mover_kerne
         char        *mine  = w.ws[s.rank] + hoff;
 
         if (KIND != MV_BCAST || s.rank == c.root) {
+            const size_t cnt = r.hi - r.lo;
+            if (KIND == MV_ALLTOALL && cnt <= 4 * (size_t)blockDim.x) {
+                // short segments: one flat loop over (destination, pack) keeps every load in flight at once
+                const bool al = (((uintptr_t)src | seg_bytes) & 15) == 0;
+                stream_packs<4>(
+                    0, cnt * (size_t)w.size,
+                    [&](size_t it) {
+                        const uint32_t q = (uint32_t)it / (uint32_t)cnt;
+                        return load_pack<Byte>(src + (size_t)q * seg_bytes + b_off, r.lo + (it - q * cnt), left, al);
+                    },
+                    [&](size_t it, uint4 v) {
+                        const uint32_t q = (uint32_t)it / (uint32_t)cnt;
+                        st_16(mine + ((size_t)q * n + r.lo + (it - q * cnt)) * 16, v);
+                    });
+            } else
             for (int q = 0; q < nseg_ws; q++) {
                 const Byte *seg = src + (size_t)q * seg_bytes + b_off;
                 const bool  al  = ((uintptr_t)seg & 15) == 0;
@@ -427,6 +442,23 @@ template <int KIND, bool kMc> __global__ void __launch_bounds__(512) mover_kerne
                     r.lo, r.hi, [&](size_t i) { return ld_nc16(from + i * 16); },
                     [&](size_t i, uint4 v) { store_bytes(out, i, left, al, v); });
             }
+        } else if (r.hi - r.lo <= 4 * (size_t)blockDim.x) {
+            // short segments: pull from all peers in one flat loop, so the round trips overlap
+            const size_t cnt = r.hi - r.lo;
+            const int    seg = (KIND == MV_ALLTOALL) ? s.rank : 0;
+            const bool   al  = (((uintptr_t)dst | seg_bytes) & 15) == 0;
+            stream_packs<4>(
+                0, cnt * (size_t)w.size,
+                [&](size_t it) {
+                    const uint32_t q = (uint32_t)it / (uint32_t)cnt;
+                    const int      p = (s.rank + (int)q) % w.size;
+                    return ld_nc16(w.ws[p] + hoff + ((size_t)seg * n + r.lo + (it - q * cnt)) * 16);
+                },
+                [&](size_t it, uint4 v) {
+                    const uint32_t q = (uint32_t)it / (uint32_t)cnt;
+                    const int      p = (s.rank + (int)q) % w.size;
+                    store_bytes(dst + (size_t)p * seg_bytes + b_off, r.lo + (it - q * cnt), left, al, v);
+                });
         } else {
             for (int q = 0; q < w.size; q++) {
                 const int   p    = (s.rank + q) % w.size;

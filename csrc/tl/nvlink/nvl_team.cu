@@ -26,6 +26,7 @@ struct NvlCfg {
     bool   nvls          = true;
     size_t one_shot_max  = 128u << 10;
     size_t nvls_min      = 256u << 10;
+    size_t bcast_mc_min  = 0;
     int    max_blocks    = 64;
     int    threads       = 512;
     double wait_timeout_ms = 5000.0;
@@ -89,6 +90,10 @@ public:
         world.rank_base = rank;
         world.n_local   = 1;
         world.ws_bytes  = cfg.ws_bytes;
+        // crossover points measured on NVSwitch systems: with 8 ranks the one-shot kernel's all-to-all
+        // traffic loses to the two-step kernels earlier than with 4 or fewer
+        if (cfg.one_shot_max == 0) cfg.one_shot_max = size >= 8 ? (256u << 10) : (1u << 20);
+        if (cfg.nvls_min == 0) cfg.nvls_min = size >= 8 ? (1u << 20) : (128u << 10);
         world.wait_budget_ns = (unsigned long long)(cfg.wait_timeout_ms * 1e6);
         for (int p = 0; p < size; p++) {
             world.pad[p] = (uint32_t *)region->base[(size_t)p];
@@ -241,7 +246,7 @@ xccl_status_t NvlReq::post()
         team_->phase += chunks_used(w, XCCL_REDUCE_SCATTER, c.count, c.len, dt);
         break;
     case XCCL_BCAST: {
-        bool mc = w.mc_ws != nullptr && c.len >= team_->cfg.nvls_min;
+        bool mc = w.mc_ws != nullptr && c.len >= team_->cfg.bcast_mc_min;
         if (args_.alg.set_by_user) mc = (args_.alg.id == ALG_NVLS);
         st = launch_bcast(w, c, cfg, s, mc);
         team_->phase += chunks_used(w, XCCL_BCAST, c.count, c.len, dt);
@@ -354,9 +359,10 @@ public:
         return {
             {"WORKSPACE_SIZE", "128m", "Bytes of symmetric workspace per rank (two alternating halves)", OptType::MEMUNITS},
             {"NVLS", "try", "Bind the workspace to an NVSwitch multicast object and use multimem kernels", OptType::TERNARY},
-            {"ONE_SHOT_MAX", "128k", "Allreduce messages up to this size use the one-shot kernel", OptType::MEMUNITS},
-            {"NVLS_MIN", "256k", "Allreduce messages from this size use NVLS when available", OptType::MEMUNITS},
-            {"MAX_BLOCKS", "64", "Upper bound of thread blocks per collective kernel (at most 128)", OptType::UINT},
+            {"ONE_SHOT_MAX", "0", "Allreduce messages up to this size use the one-shot kernel (0: by team size, 256k from 8 ranks, else 1m)", OptType::MEMUNITS},
+            {"NVLS_MIN", "0", "Allreduce messages from this size use NVLS when available (0: by team size, 1m from 8 ranks, else 128k)", OptType::MEMUNITS},
+            {"BCAST_MC_MIN", "0", "Broadcasts from this size go through the NVSwitch multicast mapping when available", OptType::MEMUNITS},
+            {"MAX_BLOCKS", "128", "Upper bound of thread blocks per collective kernel (at most 128)", OptType::UINT},
             {"THREADS", "512", "Threads per block of the collective kernels", OptType::UINT},
             {"WAIT_TIMEOUT_MS", "5000", "Budget of every device-side wait for a peer", OptType::DOUBLE},
             {"TIMING", "no", "Record CUDA events around each collective (xccl_collective_elapsed_us)", OptType::BOOL},
@@ -386,6 +392,7 @@ public:
         c.nvls            = cfg.flag("NVLS");
         c.one_shot_max    = (size_t)cfg.num("ONE_SHOT_MAX");
         c.nvls_min        = (size_t)cfg.num("NVLS_MIN");
+        c.bcast_mc_min    = (size_t)cfg.num("BCAST_MC_MIN");
         c.max_blocks      = std::max(1, std::min((int)cfg.num("MAX_BLOCKS"), kMaxBlocks));
         c.threads         = std::max(32, std::min((int)cfg.num("THREADS"), 512)) / 32 * 32;
         c.wait_timeout_ms = cfg.real("WAIT_TIMEOUT_MS");

@@ -181,7 +181,7 @@ def main() -> None:
     ap.add_argument("--max-bytes", default="1g")
     ap.add_argument("--step", type=int, default=4)
     ap.add_argument("--workspace", default="512m")
-    ap.add_argument("--max-blocks", type=int, default=64)
+    ap.add_argument("--max-blocks", type=int, default=128)
     ap.add_argument("--table", default=None, help="write the derived selection table to this file")
     a = ap.parse_args()
     opts = {"colls": a.colls.split(","), "dtypes": a.dtypes.split(","), "workspace": a.workspace,

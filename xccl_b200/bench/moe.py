@@ -70,6 +70,13 @@ def _rank_main(rank: int, size: int, job: str, o: dict) -> list:
         ws.combine([ids], [w], [y])
 
     t_d = timed(dispatch_only, o["iters"])
+    # slot order inside an expert depends on arrival order, so the identity expert copies the rows of
+    # the LAST dispatch: combine then reads outputs that match the slots it was told about
+    torch.cuda.synchronize()
+    oob.allgather_bytes(b"x")
+    ws.expert_out(0)[:total_rows].copy_(ws.recv(0)[:total_rows])
+    torch.cuda.synchronize()
+    oob.allgather_bytes(b"x")
     t_c = timed(combine_only, o["iters"])
     err = ws.error()
     want = (x.float() * w.sum(1, keepdim=True)).to(torch.bfloat16)
