@@ -34,6 +34,10 @@ constexpr uint32_t kStageRowBytes = 144;                 // 128 B of payload + 1
 constexpr uint32_t kEpiBytes   = 4 * 32 * kStageRowBytes;
 constexpr uint32_t kTmemCols   = 512;
 constexpr uint32_t kSmemBytes  = kStages * kStageBytes + kEpiBytes + 256 + 1024;  // + barriers + alignment slack
+// CTA-pair mode (cta_group::2): a cluster of two CTAs owns a 256 x 256 tile; each CTA stages its
+// 128 rows of A and HALF of the B tile, so a stage is 32 KB and six of them fit in the same ring.
+constexpr int      kStagesPair = 6;
+static_assert(kStagesPair * (kABytes + kBBytes / 2) == kStages * kStageBytes, "both modes share one shared-memory layout");
 
 struct Tile {
     int mb, nb, shard;
@@ -236,27 +240,35 @@ __device__ void copy_cta_loop(const GemmParams &p, int rank, int local, int copy
     if (threadIdx.x == 0) *epoch_slot = epoch;
 }
 
+template <bool kPair>
 __global__ void __launch_bounds__(kThreads, 1)
 tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
 {
+    constexpr int      kNS = kPair ? kStagesPair : kStages;   // pipeline stages
+    constexpr uint32_t kBB = kPair ? kBBytes / 2 : kBBytes;   // bytes of B per stage in this CTA
+    constexpr uint32_t kSB = kABytes + kBB;                   // bytes per stage in this CTA
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t       *smem_gen  = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t sA        = smem_base;
-    const uint32_t sB        = smem_base + kStages * kABytes;
+    const uint32_t sB        = smem_base + kNS * kABytes;
     uint8_t       *epi_gen   = smem_gen + kStages * kStageBytes;
     const uint32_t bars      = smem_base + kStages * kStageBytes + kEpiBytes;
     auto full_bar       = [&](int s) { return bars + 8u * s; };
-    auto empty_bar      = [&](int s) { return bars + 8u * (kStages + s); };
-    auto tmem_full_bar  = [&](int a) { return bars + 8u * (2 * kStages + a); };
-    auto tmem_empty_bar = [&](int a) { return bars + 8u * (2 * kStages + 2 + a); };
-    volatile uint32_t *tmem_slot  = reinterpret_cast<volatile uint32_t *>(epi_gen + kEpiBytes + 8 * (2 * kStages + 4));
+    auto empty_bar      = [&](int s) { return bars + 8u * (kNS + s); };
+    auto tmem_full_bar  = [&](int a) { return bars + 8u * (2 * kNS + a); };
+    auto tmem_empty_bar = [&](int a) { return bars + 8u * (2 * kNS + 2 + a); };
+    volatile uint32_t *tmem_slot  = reinterpret_cast<volatile uint32_t *>(epi_gen + kEpiBytes + 8 * (2 * kNS + 4));
     volatile uint32_t *abort_slot = tmem_slot + 1;
 
     const int warp  = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int local = blockIdx.y;
     const int rank  = p.rank_base + local;
     AbortFlag ab{abort_slot, p.error, p.budget_ns};
+    // pair mode: rank of this CTA in its cluster of two (0 issues the MMAs), tile walker per cluster
+    const uint32_t cta_rank = kPair ? cluster_ctarank() : 0u;
+    const int      unit     = kPair ? (int)blockIdx.x / 2 : (int)blockIdx.x;
+    const int      n_units  = kPair ? p.n_gemm_ctas / 2 : p.n_gemm_ctas;
 
     if (threadIdx.x == 0) *abort_slot = 0;
     __syncthreads();
@@ -269,13 +281,13 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
 
     const CUtensorMap *tmA = &lp.tmA[local], *tmB0 = &lp.tmB0[local], *tmB1 = &lp.tmB1[local];
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; s++) {
+        for (int s = 0; s < kNS; s++) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
         }
         for (int a = 0; a < 2; a++) {
             mbar_init(tmem_full_bar(a), 1);
-            mbar_init(tmem_empty_bar(a), 4);
+            mbar_init(tmem_empty_bar(a), kPair ? 8 : 4);  // epilogue warps of every CTA of the tile
         }
         mbar_fence_init();
         tma_prefetch_desc(tmA);
@@ -283,16 +295,23 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
         if (p.epilogue == EPI_SWIGLU) tma_prefetch_desc(tmB1);
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32((const void *)tmem_slot), kTmemCols);
-        tmem_relinquish();
+        if (kPair) {
+            tmem_alloc_pair(smem_u32((const void *)tmem_slot), kTmemCols);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(smem_u32((const void *)tmem_slot), kTmemCols);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (kPair) cluster_sync_all();  // the peer's barriers exist before anything is signalled across
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int tiles_m = (p.M + kBM - 1) / kBM;
-    const int tiles_n = (p.N + kBN - 1) / kBN;
+    const int tiles_m128 = (p.M + kBM - 1) / kBM;                        // 128-row blocks
+    const int tiles_m    = kPair ? (tiles_m128 + 1) / 2 : tiles_m128;     // row blocks of a tile (256 rows in pair mode)
+    const int tiles_n    = (p.N + kBN - 1) / kBN;
     const int total   = tiles_m * tiles_n;
     const int kblocks = (p.K + kBK - 1) / kBK;
 
@@ -301,11 +320,12 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
         if (elect_one()) {
             int      s = 0;
             uint32_t phase = 0;
-            int      armed[kStages];
-            for (int i = 0; i < kStages; i++) armed[i] = -1;
+            int      armed[kNS];
+            for (int i = 0; i < kNS; i++) armed[i] = -1;
             bool ok = true;
-            for (int t = blockIdx.x; t < total && ok; t += p.n_gemm_ctas) {
-                const Tile tl = tile_of(p, rank, t, tiles_m, tiles_n);
+            for (int t = unit; t < total && ok; t += n_units) {
+                Tile tl = tile_of(p, rank, t, tiles_m, tiles_n);
+                if (kPair) tl.mb = tl.mb * 2 + (int)cta_rank;  // this CTA's 128-row block
                 if (p.comm == COMM_ALLGATHER_A && tl.shard != rank) {
                     // rows of this block are being copied in by the copy CTAs of this kernel
                     const uint32_t n_copy = gridDim.x - p.n_gemm_ctas;
@@ -318,16 +338,33 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
                         ok = false;
                         break;
                     }
-                    mbar_arrive_expect_tx(full_bar(s), kStageBytes);
-                    armed[s] = (int)phase;
-                    tma_load_2d(sA + s * kABytes, tmA, kb * kBK, tl.mb * kBM, full_bar(s));
-                    if (p.epilogue == EPI_SWIGLU) {
-                        tma_load_2d(sB + s * kBBytes, tmB0, kb * kBK, tl.nb * (kBN / 2), full_bar(s));
-                        tma_load_2d(sB + s * kBBytes + kBBytes / 2, tmB1, kb * kBK, tl.nb * (kBN / 2), full_bar(s));
+                    if (kPair) {
+                        // both CTAs' bytes are counted on the barrier of the CTA that issues the MMAs
+                        const uint32_t fb = map_to_cta(full_bar(s), 0);
+                        if (cta_rank == 0) {
+                            mbar_arrive_expect_tx(full_bar(s), 2 * kSB);
+                            armed[s] = (int)phase;
+                        }
+                        tma_load_2d_pair(sA + s * kABytes, tmA, kb * kBK, tl.mb * kBM, fb);
+                        if (p.epilogue == EPI_SWIGLU) {
+                            // columns 0..127 of the tile are "gate" (rank 0 stages them), 128..255 "up" (rank 1)
+                            tma_load_2d_pair(sB + s * kBB, cta_rank == 0 ? tmB0 : tmB1, kb * kBK, tl.nb * (kBN / 2), fb);
+                        } else {
+                            tma_load_2d_pair(sB + s * kBB, tmB0, kb * kBK, tl.nb * kBN + (int)cta_rank * (kBN / 2), fb);
+                        }
                     } else {
-                        tma_load_2d(sB + s * kBBytes, tmB0, kb * kBK, tl.nb * kBN, full_bar(s));
+                        mbar_arrive_expect_tx(full_bar(s), kSB);
+                        armed[s] = (int)phase;
+                        tma_load_2d(sA + s * kABytes, tmA, kb * kBK, tl.mb * kBM, full_bar(s));
+                        if (p.epilogue == EPI_SWIGLU) {
+                            tma_load_2d(sB + s * kBB, tmB0, kb * kBK, tl.nb * (kBN / 2), full_bar(s));
+                            tma_load_2d(sB + s * kBB + kBB / 2, tmB1, kb * kBK, tl.nb * (kBN / 2), full_bar(s));
+                        } else {
+                            tma_load_2d(sB + s * kBB, tmB0, kb * kBK, tl.nb * kBN, full_bar(s));
+                            tma_load_2d(sB + s * kBB + kBB / 2, tmB0, kb * kBK, tl.nb * kBN + kBN / 2, full_bar(s));
+                        }
                     }
-                    if (++s == kStages) {
+                    if (++s == kNS) {
                         s = 0;
                         phase ^= 1;
                     }
@@ -335,7 +372,7 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
             }
             if (!ok) {
                 // let the copies that are still in flight land before the CTA goes away
-                for (int i = 0; i < kStages; i++) {
+                for (int i = 0; i < kNS; i++) {
                     if (armed[i] < 0) continue;
                     for (int spin = 0; spin < (1 << 16); spin++) {
                         if (mbar_try_wait(full_bar(i), (uint32_t)armed[i])) break;
@@ -345,13 +382,22 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (elect_one()) {
-            const uint32_t idesc = make_idesc(1, 1, kBM, kBN);
+        if ((!kPair || cta_rank == 0) && elect_one()) {
+            const uint32_t idesc = make_idesc(1, 1, kPair ? 2 * kBM : kBM, kBN);
             int            s = 0;
             uint32_t       phase = 0, acc_phase = 0;
             int            a = 0;
             bool           ok = true;
-            for (int t = blockIdx.x; t < total && ok; t += p.n_gemm_ctas) {
+            // an MMA group's completion is announced to the barrier at the same offset in every CTA of the tile
+            auto commit = [&](uint32_t bar) {
+                if (kPair) {
+                    mma_commit_pair(map_to_cta(bar, 0));
+                    mma_commit_pair(map_to_cta(bar, 1));
+                } else {
+                    mma_commit(bar);
+                }
+            };
+            for (int t = unit; t < total && ok; t += n_units) {
                 if (!mbar_wait(tmem_empty_bar(a), acc_phase ^ 1, ab, 3)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)a * kBN;
@@ -362,20 +408,24 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
                     }
                     tc_fence_after();
                     const uint64_t da = make_desc_sw128(sA + s * kABytes);
-                    const uint64_t db = make_desc_sw128(sB + s * kBBytes);
+                    const uint64_t db = make_desc_sw128(sB + s * kBB);
 #pragma unroll
                     for (int k = 0; k < kBK / 16; k++) {
                         // 16 bf16 = 32 bytes further along K inside the 128-byte swizzle row
-                        mma_f16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+                        if (kPair) {
+                            mma_f16_pair(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+                        } else {
+                            mma_f16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+                        }
                     }
-                    mma_commit(empty_bar(s));
-                    if (++s == kStages) {
+                    commit(empty_bar(s));
+                    if (++s == kNS) {
                         s = 0;
                         phase ^= 1;
                     }
                 }
                 if (!ok) break;
-                mma_commit(tmem_full_bar(a));
+                commit(tmem_full_bar(a));
                 a ^= 1;
                 if (a == 0) acc_phase ^= 1;
             }
@@ -386,11 +436,12 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
         uint8_t       *stage   = epi_gen + (warp - 2) * 32 * kStageRowBytes;
         uint32_t       acc_phase = 0;
         int            a = 0;
-        const int      mbs  = (p.comm == COMM_NONE) ? tiles_m : tiles_m / p.tp_size;
+        const int      mbs  = (p.comm == COMM_NONE) ? tiles_m128 : tiles_m128 / p.tp_size;
         const int      out_cols_per_tile = (p.epilogue == EPI_SWIGLU) ? kBN / 2 : kBN;
         const int      n_out = (p.epilogue == EPI_SWIGLU) ? p.N / 2 : p.N;
-        for (int t = blockIdx.x; t < total; t += p.n_gemm_ctas) {
-            const Tile tl = tile_of(p, rank, t, tiles_m, tiles_n);
+        for (int t = unit; t < total; t += n_units) {
+            Tile tl = tile_of(p, rank, t, tiles_m, tiles_n);
+            if (kPair) tl.mb = tl.mb * 2 + (int)cta_rank;
             if (!mbar_wait(tmem_full_bar(a), acc_phase, ab, 5)) break;
             tc_fence_after();
             const uint32_t t_acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)a * kBN;
@@ -455,7 +506,13 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(tmem_empty_bar(a));
+            if (lane == 0) {
+                if (kPair) {
+                    mbar_arrive_cluster(map_to_cta(tmem_empty_bar(a), 0));
+                } else {
+                    mbar_arrive(tmem_empty_bar(a));
+                }
+            }
             if (p.comm == COMM_REDUCE_SCATTER_C) {
                 // all four epilogue warps have stored their rows: tell the owner one more tile arrived
                 asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -473,14 +530,19 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
 
     tc_fence_before();
     __syncthreads();
+    if (kPair) cluster_sync_all();  // nothing is signalled into a CTA that has gone, nor its tensor memory freed early
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, kTmemCols);
+        if (kPair) {
+            tmem_dealloc_pair(tmem_base, kTmemCols);
+        } else {
+            tmem_dealloc(tmem_base, kTmemCols);
+        }
     }
 
     // ---- reduce-scatter: add up the partial tiles that every rank stored for my rows
     if (p.comm == COMM_REDUCE_SCATTER_C && *abort_slot == 0) {
-        const int    mbs        = tiles_m / p.tp_size;
+        const int    mbs        = tiles_m128 / p.tp_size;
         const size_t shard_rows = (size_t)mbs * kBM;
         const size_t slot_elems = shard_rows * (size_t)p.N;
         const __nv_bfloat16 *mine = p.part[rank] + (size_t)(p.seq & 1) * p.tp_size * slot_elems;
@@ -581,7 +643,8 @@ xccl_status_t launch_gemm(const GemmParams &p_in, const GemmLaunch &l, cudaStrea
     XCCL_CUDA_CHECK(cudaGetDevice(&dev));
     XCCL_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     if (!attr_set[dev]) {
-        XCCL_CUDA_CHECK(cudaFuncSetAttribute(tp_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        XCCL_CUDA_CHECK(cudaFuncSetAttribute(tp_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        XCCL_CUDA_CHECK(cudaFuncSetAttribute(tp_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
         attr_set[dev] = true;
     }
     int ctas = l.ctas > 0 ? l.ctas : sms / std::max(l.n_local, 1);
@@ -590,17 +653,56 @@ xccl_status_t launch_gemm(const GemmParams &p_in, const GemmLaunch &l, cudaStrea
     if (p.error == nullptr) p.error = error_word();
     if (p.budget_ns == 0) p.budget_ns = 4000000000ull;
 
+    // CTA pairs (clusters of two, one 256-row tile per pair) when the shape allows: an even number of
+    // CTAs in each role and, with communication, row shards made of whole 256-row tiles.
+    static int pair_env = -1;
+    if (pair_env < 0) {
+        const char *e = getenv("XCCL_TP_GEMM_PAIR");
+        pair_env      = (e == nullptr || atoi(e) != 0) ? 1 : 0;
+    }
+    static bool pair_refused[64] = {false};  // the device could not place the clusters: stay with single CTAs
+    bool pair = pair_env == 1 && !pair_refused[dev];
+    if (pair && p.comm != COMM_NONE && (p.M / p.tp_size) % (2 * kBM) != 0) pair = false;
+    if (pair && ctas < 2) pair = false;
+
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim          = dim3((unsigned)ctas, (unsigned)l.n_local);
     cfg.blockDim         = dim3(kThreads);
     cfg.dynamicSmemBytes = kSmemBytes;
     cfg.stream           = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id              = cudaLaunchAttributeCooperative;
     attr[0].val.cooperative = l.cooperative ? 1 : 0;
     cfg.attrs               = attr;
     cfg.numAttrs            = 1;
-    XCCL_CUDA_CHECK(cudaLaunchKernelEx(&cfg, tp_gemm_kernel, p, l));
+    if (pair) {
+        GemmParams pp     = p;
+        int        pctas  = ctas & ~1;
+        int        n_copy = ctas - p.n_gemm_ctas;
+        n_copy            = (n_copy + 1) & ~1;
+        pp.n_gemm_ctas    = pctas - n_copy;
+        attr[1].id               = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = 2;
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = 1;
+        cfg.numAttrs             = 2;
+        cfg.gridDim              = dim3((unsigned)pctas, (unsigned)l.n_local);
+        // every CTA of the grid must be resident at once: roles wait for one another
+        int         max_clusters = 0;
+        cudaError_t oe           = cudaOccupancyMaxActiveClusters(&max_clusters, tp_gemm_kernel<true>, &cfg);
+        if (oe == cudaSuccess && pp.n_gemm_ctas >= 2 && max_clusters * 2 >= pctas * l.n_local) {
+            cudaError_t le = cudaLaunchKernelEx(&cfg, tp_gemm_kernel<true>, pp, l);
+            if (le == cudaSuccess) return XCCL_OK;
+            (void)cudaGetLastError();
+            xccl_warn("tp gemm: launch with CTA pairs refused (%s); using single CTAs", cudaGetErrorString(le));
+        } else {
+            (void)cudaGetLastError();
+            xccl_warn("tp gemm: %d clusters of two fit, %d CTAs wanted; using single CTAs", max_clusters, pctas * l.n_local);
+        }
+        pair_refused[dev] = true;
+        cfg.numAttrs      = 1;
+    }
+    cfg.gridDim = dim3((unsigned)ctas, (unsigned)l.n_local);
+    XCCL_CUDA_CHECK(cudaLaunchKernelEx(&cfg, tp_gemm_kernel<false>, p, l));
     return XCCL_OK;
 }
 
@@ -624,7 +726,7 @@ xccl_status_t xccl_gemm_bf16(const void *A, const void *B, void *C, int M, int N
     p.C[0]     = (__nv_bfloat16 *)C;
     xccl_status_t st = make_tensor_map_2d(&l.tmA[0], A, (uint64_t)M, (uint64_t)K, (uint64_t)K, kBM);
     if (st != XCCL_OK) return st;
-    st = make_tensor_map_2d(&l.tmB0[0], B, (uint64_t)N, (uint64_t)K, (uint64_t)K, kBN);
+    st = make_tensor_map_2d(&l.tmB0[0], B, (uint64_t)N, (uint64_t)K, (uint64_t)K, kBN / 2);
     if (st != XCCL_OK) return st;
     l.tmB1[0] = l.tmB0[0];
     return launch_gemm(p, l, (cudaStream_t)stream);

@@ -247,7 +247,7 @@ xccl_status_t xccl_tp_gemm_rs(xccl_tp_ws_h w, const void *const *Hin, const void
         p.C[i] = (__nv_bfloat16 *)Yout[i];
         xccl_status_t st = make_tensor_map_2d(&l.tmA[i], Hin[i], (uint64_t)w->M, (uint64_t)F_local, (uint64_t)F_local, kBM);
         if (st != XCCL_OK) return st;
-        st = make_tensor_map_2d(&l.tmB0[i], Wd[i], (uint64_t)w->N_rs, (uint64_t)F_local, (uint64_t)F_local, kBN);
+        st = make_tensor_map_2d(&l.tmB0[i], Wd[i], (uint64_t)w->N_rs, (uint64_t)F_local, (uint64_t)F_local, kBN / 2);
         if (st != XCCL_OK) return st;
         l.tmB1[i] = l.tmB0[i];
     }
