@@ -65,7 +65,11 @@ class ClockSampler:
             sm = nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)
             reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle) if hasattr(
                 nv, "nvmlDeviceGetCurrentClocksEventReasons") else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
-            self.samples.append((time.monotonic(), sm, int(reasons)))
+            try:
+                watts = nv.nvmlDeviceGetPowerUsage(self.handle) / 1000.0
+            except Exception:
+                watts = None
+            self.samples.append((time.monotonic(), sm, int(reasons), watts))
         except Exception:
             pass
 
@@ -92,15 +96,18 @@ class ClockSampler:
             smax = None
         masks = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
         t0, t1 = getattr(self, "t0", 0.0), getattr(self, "t1", float("inf"))
-        sm, reasons = [], set()
-        for ts, mhz, bits in self.samples:
+        sm, reasons, watts = [], set(), []
+        for ts, mhz, bits, w in self.samples:
             if ts < t0 or ts > t1:
                 continue
             sm.append(mhz)
+            if w is not None:
+                watts.append(w)
             for name, m in masks.items():
                 if bits & m:
                     reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax, "samples": len(sm),
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_min_mhz": min(sm) if sm else None,
+                "sm_max_mhz": smax, "samples": len(sm), "power_w": statistics.median(watts) if watts else None,
                 "reasons": sorted(reasons)}
 
 

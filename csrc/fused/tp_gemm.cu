@@ -52,10 +52,11 @@ __device__ __forceinline__ Tile tile_of(const GemmParams &p, int rank, int t, in
 {
     Tile tl;
     if (p.comm == COMM_NONE) {
-        const int group = 16 * tiles_n;
+        const int gr    = p.group_rows > 0 ? p.group_rows : 16;
+        const int group = gr * tiles_n;
         const int g = t / group, within = t % group;
-        const int gm = min(16, tiles_m - g * 16);
-        tl.mb    = g * 16 + within % gm;
+        const int gm = min(gr, tiles_m - g * gr);
+        tl.mb    = g * gr + within % gm;
         tl.nb    = within / gm;
         tl.shard = 0;
         return tl;
@@ -65,8 +66,12 @@ __device__ __forceinline__ Tile tile_of(const GemmParams &p, int rank, int t, in
     const int idx   = t / per, within = t % per;
     const int first = (p.comm == COMM_ALLGATHER_A) ? 0 : 1;
     tl.shard = (rank + first + idx) % p.tp_size;
-    tl.mb    = tl.shard * mbs + within % mbs;
-    tl.nb    = within / mbs;
+    // inside a shard: sub-groups of group_rows row blocks x all column blocks
+    const int gr  = (p.group_rows > 0 && p.group_rows < mbs) ? p.group_rows : mbs;
+    const int sub = within / (gr * tiles_n), rem = within % (gr * tiles_n);
+    const int gm  = min(gr, mbs - sub * gr);
+    tl.mb = tl.shard * mbs + sub * gr + rem % gm;
+    tl.nb = rem / gm;
     return tl;
 }
 
@@ -323,7 +328,22 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
             int      armed[kNS];
             for (int i = 0; i < kNS; i++) armed[i] = -1;
             bool ok = true;
-            for (int t = unit; t < total && ok; t += n_units) {
+            uint32_t *sync_ctr      = p.sync_ctr[local];
+            const int sync_per_tile = p.sync_kblocks > 0 ? (kblocks + p.sync_kblocks - 1) / p.sync_kblocks : 1;
+            int       wave          = 0;
+            const uint64_t pol_last = l2_policy_evict_last(), pol_first = l2_policy_evict_first();
+            const uint64_t pol_a = (p.l2_hint == 3) ? pol_first : pol_last;
+            const uint64_t pol_b = (p.l2_hint == 2) ? pol_first : pol_last;
+            auto load = [&](uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar, uint64_t pol) {
+                if (kPair) {
+                    if (p.l2_hint != 0) tma_load_2d_pair_hint(dst, map, x, y, bar, pol);
+                    else tma_load_2d_pair(dst, map, x, y, bar);
+                } else {
+                    if (p.l2_hint != 0) tma_load_2d_hint(dst, map, x, y, bar, pol);
+                    else tma_load_2d(dst, map, x, y, bar);
+                }
+            };
+            for (int t = unit; t < total && ok; t += n_units, wave++) {
                 Tile tl = tile_of(p, rank, t, tiles_m, tiles_n);
                 if (kPair) tl.mb = tl.mb * 2 + (int)cta_rank;  // this CTA's 128-row block
                 if (p.comm == COMM_ALLGATHER_A && tl.shard != rank) {
@@ -334,6 +354,17 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
                     if (!ok) break;
                 }
                 for (int kb = 0; kb < kblocks; kb++) {
+                    if (sync_ctr != nullptr && (kb == 0 || (p.sync_kblocks > 0 && kb % p.sync_kblocks == 0))) {
+                        const int point = wave * sync_per_tile + (p.sync_kblocks > 0 ? kb / p.sync_kblocks : 0);
+                        if (point < p.sync_points) {
+                            // walkers that have a tile in this wave
+                            const uint32_t want = (uint32_t)min(n_units, total - wave * n_units);
+                            if (cta_rank == 0) red_release_gpu_add(sync_ctr + point, 1u);
+                            const unsigned long long t0 = now_ns();
+                            while ((int32_t)(ld_acquire_gpu(sync_ctr + point) - want) < 0 &&
+                                   now_ns() - t0 < p.sync_budget_ns) {}
+                        }
+                    }
                     if (!mbar_wait(empty_bar(s), phase ^ 1, ab, 2)) {
                         ok = false;
                         break;
@@ -345,23 +376,23 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
                             mbar_arrive_expect_tx(full_bar(s), 2 * kSB);
                             armed[s] = (int)phase;
                         }
-                        tma_load_2d_pair(sA + s * kABytes, tmA, kb * kBK, tl.mb * kBM, fb);
+                        load(sA + s * kABytes, tmA, kb * kBK, tl.mb * kBM, fb, pol_a);
                         if (p.epilogue == EPI_SWIGLU) {
                             // columns 0..127 of the tile are "gate" (rank 0 stages them), 128..255 "up" (rank 1)
-                            tma_load_2d_pair(sB + s * kBB, cta_rank == 0 ? tmB0 : tmB1, kb * kBK, tl.nb * (kBN / 2), fb);
+                            load(sB + s * kBB, cta_rank == 0 ? tmB0 : tmB1, kb * kBK, tl.nb * (kBN / 2), fb, pol_b);
                         } else {
-                            tma_load_2d_pair(sB + s * kBB, tmB0, kb * kBK, tl.nb * kBN + (int)cta_rank * (kBN / 2), fb);
+                            load(sB + s * kBB, tmB0, kb * kBK, tl.nb * kBN + (int)cta_rank * (kBN / 2), fb, pol_b);
                         }
                     } else {
                         mbar_arrive_expect_tx(full_bar(s), kSB);
                         armed[s] = (int)phase;
-                        tma_load_2d(sA + s * kABytes, tmA, kb * kBK, tl.mb * kBM, full_bar(s));
+                        load(sA + s * kABytes, tmA, kb * kBK, tl.mb * kBM, full_bar(s), pol_a);
                         if (p.epilogue == EPI_SWIGLU) {
-                            tma_load_2d(sB + s * kBB, tmB0, kb * kBK, tl.nb * (kBN / 2), full_bar(s));
-                            tma_load_2d(sB + s * kBB + kBB / 2, tmB1, kb * kBK, tl.nb * (kBN / 2), full_bar(s));
+                            load(sB + s * kBB, tmB0, kb * kBK, tl.nb * (kBN / 2), full_bar(s), pol_b);
+                            load(sB + s * kBB + kBB / 2, tmB1, kb * kBK, tl.nb * (kBN / 2), full_bar(s), pol_b);
                         } else {
-                            tma_load_2d(sB + s * kBB, tmB0, kb * kBK, tl.nb * kBN, full_bar(s));
-                            tma_load_2d(sB + s * kBB + kBB / 2, tmB0, kb * kBK, tl.nb * kBN + kBN / 2, full_bar(s));
+                            load(sB + s * kBB, tmB0, kb * kBK, tl.nb * kBN, full_bar(s), pol_b);
+                            load(sB + s * kBB + kBB / 2, tmB0, kb * kBK, tl.nb * kBN + kBN / 2, full_bar(s), pol_b);
                         }
                     }
                     if (++s == kNS) {
@@ -499,7 +530,12 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
                     const int grow = quarter * 32 + r, gcol = col0 + chunk * 8;
                     if (grow < rows_valid && gcol < n_out) {
                         uint4 v = *reinterpret_cast<const uint4 *>(stage + r * kStageRowBytes + chunk * 16);
-                        *reinterpret_cast<uint4 *>(out + (size_t)(row0 + grow) * ld + gcol) = v;
+                        uint4 *dstp = reinterpret_cast<uint4 *>(out + (size_t)(row0 + grow) * ld + gcol);
+                        if (p.st_stream) {
+                            __stcs(dstp, v);
+                        } else {
+                            *dstp = v;
+                        }
                     }
                 }
                 __syncwarp();
@@ -614,6 +650,20 @@ uint32_t *error_word()
 
 size_t gemm_smem_bytes() { return kSmemBytes; }
 
+namespace {
+constexpr int kSyncPoints = 8192;  // lockstep counters per local rank
+uint32_t *sync_counters()
+{
+    static uint32_t *buf[64] = {nullptr};
+    int              dev = 0;
+    cudaGetDevice(&dev);
+    if (buf[dev] == nullptr) {
+        if (cudaMalloc((void **)&buf[dev], sizeof(uint32_t) * kSyncPoints * kMaxTpRanks) != cudaSuccess) return nullptr;
+    }
+    return buf[dev];
+}
+}  // namespace
+
 xccl_status_t make_tensor_map_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint64_t ld,
                                  uint32_t box_rows)
 {
@@ -623,9 +673,18 @@ xccl_status_t make_tensor_map_2d(CUtensorMap *map, const void *base, uint64_t ro
     cuuint64_t strides[1] = {ld * 2};
     cuuint32_t box[2]     = {(cuuint32_t)kBK, box_rows};
     cuuint32_t estr[2]    = {1, 1};
+    static int promo = -1;
+    if (promo < 0) {
+        const char *e = getenv("XCCL_TP_GEMM_L2PROMO");  // 0 none, 1 64 B, 2 128 B, 3 256 B
+        promo         = (e != nullptr) ? std::max(0, std::min(3, atoi(e))) : 3;
+    }
+    const CUtensorMapL2promotion pr = promo == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE
+                                    : promo == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+                                    : promo == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
+                                                 : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
     XCCL_CU_CHECK(cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims,
                                          strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+                                         pr, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
     return XCCL_OK;
 }
 
@@ -660,10 +719,65 @@ xccl_status_t launch_gemm(const GemmParams &p_in, const GemmLaunch &l, cudaStrea
         const char *e = getenv("XCCL_TP_GEMM_PAIR");
         pair_env      = (e == nullptr || atoi(e) != 0) ? 1 : 0;
     }
+    static int group_env = -1;
+    if (group_env < 0) {
+        const char *e = getenv("XCCL_TP_GEMM_GROUP");
+        group_env     = (e != nullptr && atoi(e) > 0) ? atoi(e) : 0;
+    }
+    if (p.group_rows <= 0) p.group_rows = group_env;
+    static int hint_env = -1, stcs_env = -1;
+    if (hint_env < 0) {
+        const char *e = getenv("XCCL_TP_GEMM_L2HINT");
+        hint_env      = (e != nullptr) ? std::max(0, std::min(3, atoi(e))) : 0;
+        e             = getenv("XCCL_TP_GEMM_STCS");
+        stcs_env      = (e != nullptr && atoi(e) != 0) ? 1 : 0;
+    }
+    static int sync_env = -1, sync_kb_env = 0, sync_ns_env = 30000;
+    if (sync_env < 0) {
+        const char *e = getenv("XCCL_TP_GEMM_SYNC");
+        sync_env      = (e == nullptr || atoi(e) != 0) ? 1 : 0;
+        e             = getenv("XCCL_TP_GEMM_SYNC_KBLOCKS");
+        if (e != nullptr) sync_kb_env = std::max(0, atoi(e));
+        e = getenv("XCCL_TP_GEMM_SYNC_NS");
+        if (e != nullptr) sync_ns_env = std::max(0, atoi(e));
+    }
+    for (int i = 0; i < kMaxTpRanks; i++) p.sync_ctr[i] = nullptr;
+    p.sync_points = 0;
+    if (sync_env == 1 && l.n_local <= kMaxTpRanks) {
+        uint32_t *ctr = sync_counters();
+        // worth it only when a walker has several tiles: the drift builds up over tiles
+        const int  tile_rows = 2 * kBM;
+        const long tiles     = (long)((p.M + tile_rows - 1) / tile_rows) * ((p.N + kBN - 1) / kBN);
+        const int  kblocks   = (p.K + kBK - 1) / kBK;
+        const int  per_tile  = sync_kb_env > 0 ? (kblocks + sync_kb_env - 1) / sync_kb_env : 1;
+        const long waves     = (tiles + std::max(1, ctas / 2) - 1) / std::max(1, ctas / 2) * 2 + 2;  // single-CTA walkers: half-size tiles
+        const long points    = std::min<long>(waves * per_tile, kSyncPoints);
+        if (ctr != nullptr && tiles > ctas) {
+            XCCL_CUDA_CHECK(cudaMemsetAsync(ctr, 0, sizeof(uint32_t) * kSyncPoints * (l.n_local - 1) + sizeof(uint32_t) * points, stream));
+            for (int i = 0; i < l.n_local; i++) p.sync_ctr[i] = ctr + (size_t)i * kSyncPoints;
+            p.sync_points    = (int)points;
+            p.sync_kblocks   = sync_kb_env;
+            p.sync_budget_ns = (unsigned)sync_ns_env;
+        }
+    }
+    p.l2_hint   = hint_env;
+    p.st_stream = (p.comm == COMM_REDUCE_SCATTER_C) ? 0 : stcs_env;  // partial tiles are read back at once
     static bool pair_refused[64] = {false};  // the device could not place the clusters: stay with single CTAs
     bool pair = pair_env == 1 && !pair_refused[dev];
     if (pair && p.comm != COMM_NONE && (p.M / p.tp_size) % (2 * kBM) != 0) pair = false;
     if (pair && ctas < 2) pair = false;
+
+    // Row blocks walked together before moving along N. Short K: as many rows of A as stay in L2 next
+    // to the streaming B (about 48 MiB); long K: the squarest arrangement of one wave of tiles, which
+    // needs the fewest distinct rows of A and B from DRAM.
+    auto auto_group = [&](int tile_rows, int wave_rows) {
+        if (p.group_rows > 0) return p.group_rows;
+        long rows = (48l << 20) / ((long)p.K * 2);
+        rows      = std::max<long>(wave_rows, std::min<long>(rows, 4096));
+        return (int)std::max<long>(1, (rows + tile_rows / 2) / tile_rows);
+    };
+    const int group_single = auto_group(kBM, 12 * kBM), group_pair = auto_group(2 * kBM, 8 * 2 * kBM);
+    p.group_rows           = group_single;
 
     cudaLaunchConfig_t cfg{};
     cfg.blockDim         = dim3(kThreads);
@@ -680,6 +794,7 @@ xccl_status_t launch_gemm(const GemmParams &p_in, const GemmLaunch &l, cudaStrea
         int        n_copy = ctas - p.n_gemm_ctas;
         n_copy            = (n_copy + 1) & ~1;
         pp.n_gemm_ctas    = pctas - n_copy;
+        pp.group_rows     = group_pair;
         attr[1].id               = cudaLaunchAttributeClusterDimension;
         attr[1].val.clusterDim.x = 2;
         attr[1].val.clusterDim.y = 1;

@@ -36,6 +36,17 @@ struct GemmParams {
     int tp_size;          // ranks taking part (1 without communication)
     int rank_base;        // team rank of blockIdx.y == 0
     int n_gemm_ctas;      // CTAs (per rank) that run MMA tiles; the rest copy (allgather mode)
+    int group_rows;       // row blocks of tiles walked together before moving along N (0 = chosen from the shape)
+    int l2_hint;          // operand loads: 0 no hint, 1 A and B evict_last, 2 A evict_last / B evict_first, 3 the reverse
+    int st_stream;        // 1: output stores are marked streaming (evict first)
+    // Soft lockstep of the tile walkers: before a tile (and every sync_kblocks K blocks inside it) a walker
+    // counts itself into sync_ctr[point] and waits, for at most sync_budget_ns, until all walkers of that
+    // point have done so. Walkers that share rows of A or B then ask L2 for the same lines within
+    // microseconds of each other; without it they drift apart over many tiles and each fetches from DRAM.
+    uint32_t *sync_ctr[kMaxTpRanks];      // per LOCAL rank, zeroed before the launch; null = no lockstep
+    int       sync_points;                // counters available
+    int       sync_kblocks;               // 0 = only at tile starts
+    unsigned  sync_budget_ns;
     uint32_t seq;         // launch sequence number (starts at 1): readiness counters and buffer parity follow it
     uint32_t rs_target;   // reduce-scatter: running total of tiles per (source, row block) for this parity
     unsigned long long budget_ns;
