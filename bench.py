@@ -121,6 +121,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="xccl", choices=["xccl", "reference", "torch"])
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"],
+                    help="fp8: the block-scaled e4m3 variant of the fused kernels (impl xccl only); the headline is bf16")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     ref_root = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline")
@@ -185,18 +187,18 @@ def main() -> None:
         e2e_step = lambda: model.forward_from_host(xp)  # noqa: E731
         launches_per_step = 0
     elif args.impl == "xccl":
-        from xccl_b200.models.tp_mlp import TpMlp
+        from xccl_b200.models.tp_mlp import TpMlp, TpMlpFp8
         if world > 1:
             from xccl_b200.api import ShmOob
             key = [uuid.uuid4().hex[:12] if rank == 0 else None]
             dist.broadcast_object_list(key, src=0)
             oob = ShmOob(key[0], rank, world)
-        model = TpMlp(TOKENS, HIDDEN, FFN, tp=world, rank=rank, oob=oob)
+        model = (TpMlpFp8 if args.dtype == "fp8" else TpMlp)(TOKENS, HIDDEN, FFN, tp=world, rank=rank, oob=oob)
         x_dev = [torch.randn(TOKENS // world, HIDDEN, device=dev).to(torch.bfloat16)]
         x_pin = [torch.randn(TOKENS // world, HIDDEN).to(torch.bfloat16).pin_memory()]
         step = lambda: model.forward(x_dev)           # noqa: E731
         e2e_step = lambda: model.forward_from_host(x_pin)  # noqa: E731
-        launches_per_step = 2
+        launches_per_step = 4 if args.dtype == "fp8" else 2
     else:
         from xccl_b200.models.tp_mlp import TorchTpMlp
         model = TorchTpMlp(TOKENS, HIDDEN, FFN, tp=world, rank=rank)
@@ -243,7 +245,7 @@ def main() -> None:
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": args.impl,
+            "vs_baseline": None, "dtype": args.dtype if args.impl == "xccl" else "bf16", "data": "synthetic", "impl": args.impl,
             "config": {"model": "llama-style MLP block (SwiGLU)", "global_batch": TOKENS, "seq_len": TOKENS,
                        "hidden": HIDDEN, "ffn": FFN, "parallelism": f"tp{world}",
                        "l2_policy": "operands larger than L2 (weights %.0f MB per GPU)" % (3 * HIDDEN * FFN // world * 2 / 1e6),

@@ -19,231 +19,11 @@
 #include "../cuda/cuda_common.h"
 #include "sm100_ptx.cuh"
 #include "tp_gemm.cuh"
+#include "tp_device.cuh"
 
 namespace xccl {
 namespace tp {
-
-using namespace sm100;
-
 namespace {
-
-constexpr uint32_t kABytes     = kBM * kBK * 2;          // 16 KB
-constexpr uint32_t kBBytes     = kBN * kBK * 2;          // 32 KB
-constexpr uint32_t kStageBytes = kABytes + kBBytes;
-constexpr uint32_t kStageRowBytes = 144;                 // 128 B of payload + 16 B pad: conflict-free transposes
-constexpr uint32_t kEpiBytes   = 4 * 32 * kStageRowBytes;
-constexpr uint32_t kTmemCols   = 512;
-constexpr uint32_t kSmemBytes  = kStages * kStageBytes + kEpiBytes + 256 + 1024;  // + barriers + alignment slack
-// CTA-pair mode (cta_group::2): a cluster of two CTAs owns a 256 x 256 tile; each CTA stages its
-// 128 rows of A and HALF of the B tile, so a stage is 32 KB and six of them fit in the same ring.
-constexpr int      kStagesPair = 6;
-static_assert(kStagesPair * (kABytes + kBBytes / 2) == kStages * kStageBytes, "both modes share one shared-memory layout");
-
-struct Tile {
-    int mb, nb, shard;
-};
-
-// Order in which a rank walks its output tiles.
-//  COMM_NONE            groups of 16 row blocks x all column blocks (L2 reuse of A and B)
-//  COMM_ALLGATHER_A     row shard by row shard, starting with the local one (its A is already here)
-//  COMM_REDUCE_SCATTER  row shard by row shard, starting with the next rank's and ending with the
-//                       local one, so remote partial tiles leave early and local ones need no wire
-__device__ __forceinline__ Tile tile_of(const GemmParams &p, int rank, int t, int tiles_m, int tiles_n)
-{
-    Tile tl;
-    if (p.comm == COMM_NONE) {
-        const int gr    = p.group_rows > 0 ? p.group_rows : 16;
-        const int group = gr * tiles_n;
-        const int g = t / group, within = t % group;
-        const int gm = min(gr, tiles_m - g * gr);
-        tl.mb    = g * gr + within % gm;
-        tl.nb    = within / gm;
-        tl.shard = 0;
-        return tl;
-    }
-    const int mbs   = tiles_m / p.tp_size;
-    const int per   = mbs * tiles_n;
-    const int idx   = t / per, within = t % per;
-    const int first = (p.comm == COMM_ALLGATHER_A) ? 0 : 1;
-    tl.shard = (rank + first + idx) % p.tp_size;
-    // inside a shard: sub-groups of group_rows row blocks x all column blocks
-    const int gr  = (p.group_rows > 0 && p.group_rows < mbs) ? p.group_rows : mbs;
-    const int sub = within / (gr * tiles_n), rem = within % (gr * tiles_n);
-    const int gm  = min(gr, mbs - sub * gr);
-    tl.mb = tl.shard * mbs + sub * gr + rem % gm;
-    tl.nb = rem / gm;
-    return tl;
-}
-
-__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p)
-{
-    uint32_t v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void red_release_gpu_add(uint32_t *p, uint32_t v)
-{
-    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
-// Bounded wait for a counter to reach `target` (wrap-safe); sys = counter written by another GPU.
-__device__ __forceinline__ bool wait_counter(const uint32_t *ctr, uint32_t target, bool sys, const AbortFlag &ab,
-                                             uint32_t where)
-{
-    const unsigned long long t0 = now_ns();
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 64; i++) {
-            uint32_t v = sys ? nvl::ld_acquire_sys(ctr) : ld_acquire_gpu(ctr);
-            if ((int32_t)(v - target) >= 0) return true;
-        }
-        if (*ab.smem != 0) return false;
-        if (now_ns() - t0 > ab.budget_ns) {
-            *ab.smem = 1;
-            atomicCAS(ab.global, 0u, 0x200u | where);
-            return false;
-        }
-    }
-}
-
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
-{
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t *>(&v);
-}
-__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
-
-// Copy CTAs of the allgather mode: pull the remote row shards into the local gathered buffer,
-// one 128-row block at a time, and count each finished slice into ready[block].
-// One thread drives a ring of kCopySlots shared-memory slots with untiled bulk copies: the load of
-// chunk i (peer memory -> slot) is issued kCopyAhead chunks before its store (slot -> local buffer),
-// so every copy CTA keeps kCopyAhead * kCopyChunk bytes in flight on the wire without holding them
-// in registers.
-constexpr int      kCopySlots = 12;
-constexpr int      kCopyAhead = 8;
-constexpr int      kCopyLag   = 2;       // a block is announced once the stores of 2 later chunks were issued
-constexpr uint32_t kCopyChunk = 16384;
-static_assert(kCopySlots * kCopyChunk <= kStages * kStageBytes, "the copy ring reuses the pipeline stages");
-static_assert(kCopySlots <= 2 * kStages + 4, "one mbarrier per slot in the barrier area");
-
-__device__ void copy_cta_loop(const GemmParams &p, int rank, int local, int copy_idx, int n_copy, const AbortFlag &ab,
-                              uint32_t ring, uint32_t bars)
-{
-    const int    tiles_m = (p.M + kBM - 1) / kBM;
-    const int    mbs     = tiles_m / p.tp_size;
-    const size_t blk_bytes = (size_t)kBM * p.K * 2;
-    const size_t blk_packs = blk_bytes / 16;  // 16-byte packs in one row block
-    const size_t per   = (blk_packs + n_copy - 1) / n_copy;
-    const size_t lo    = min((size_t)copy_idx * per, blk_packs) * 16, hi = min(((size_t)copy_idx + 1) * per, blk_packs) * 16;
-    const int    cpb   = (int)((hi - lo + kCopyChunk - 1) / kCopyChunk);  // chunks of this CTA per row block
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kCopySlots; s++) mbar_init(bars + 8u * s, 1);
-        mbar_fence_init();
-    }
-    // peers must have published their shards before we read them: barrier among the copy CTAs
-    uint32_t *epoch_slot = p.pad[rank] + nvl::kPadEpochOff + copy_idx;
-    uint32_t  epoch      = *epoch_slot + 1;
-    __syncthreads();
-    int bad = 0;
-    if ((int)threadIdx.x < p.tp_size) {
-        const int q = threadIdx.x;
-        nvl::st_release_sys(p.pad[q] + (size_t)copy_idx * nvl::kMaxRanks + rank, epoch);
-        if (!nvl::wait_flag(p.pad[rank] + (size_t)copy_idx * nvl::kMaxRanks + q, epoch, ab.budget_ns)) bad = 1;
-    }
-    if (__syncthreads_or(bad)) {
-        if (threadIdx.x == 0) {
-            *ab.smem = 1;
-            atomicCAS(ab.global, 0u, 0x300u);
-        }
-        return;
-    }
-    if (threadIdx.x == 0) {
-        const int n_blocks = (p.tp_size - 1) * mbs;
-        auto block_of = [&](int b) {  // b-th remote row block in the order this rank pulls them
-            const int shard = (rank + 1 + b / mbs) % p.tp_size;
-            return shard * mbs + b % mbs;
-        };
-        auto announce = [&](int b) {
-            asm volatile("fence.proxy.async.global;" ::: "memory");
-            __threadfence();
-            red_release_gpu_add(p.ready[local] + block_of(b), 1u);
-        };
-        if (cpb == 0) {
-            for (int b = 0; b < n_blocks; b++) announce(b);
-        } else {
-            const int total = n_blocks * cpb;
-            auto span = [&](int g, size_t &off, uint32_t &bytes) {
-                const int b = g / cpb, c = g % cpb;
-                const size_t in = lo + (size_t)c * kCopyChunk;
-                off   = (size_t)block_of(b) * blk_bytes + in;
-                bytes = (uint32_t)min((size_t)kCopyChunk, hi - in);
-            };
-            char *dst = reinterpret_cast<char *>(p.xg[rank]);
-            bool ok = true;
-            int  loads_issued = 0, stores_issued = 0;
-            for (int i = 0; i < total + kCopyAhead && ok; i++) {
-                if (i < total) {
-                    // the slot's previous store (chunk i - kCopySlots) must have left shared memory
-                    if (i >= kCopySlots) bulk_wait_read<kCopySlots - 1 - kCopyAhead>();
-                    size_t   off;
-                    uint32_t bytes;
-                    span(i, off, bytes);
-                    const int      shard = block_of(i / cpb) / mbs;
-                    const uint32_t bar   = bars + 8u * (i % kCopySlots);
-                    mbar_arrive_expect_tx(bar, bytes);
-                    bulk_load(ring + (i % kCopySlots) * kCopyChunk, reinterpret_cast<const char *>(p.xg[shard]) + off, bytes, bar);
-                    loads_issued = i + 1;
-                }
-                const int j = i - kCopyAhead;
-                if (j >= 0) {
-                    if (!mbar_wait(bars + 8u * (j % kCopySlots), (uint32_t)(j / kCopySlots) & 1u, ab, 7)) {
-                        ok = false;
-                        break;
-                    }
-                    size_t   off;
-                    uint32_t bytes;
-                    span(j, off, bytes);
-                    bulk_store(dst + off, ring + (j % kCopySlots) * kCopyChunk, bytes);
-                    bulk_commit();
-                    stores_issued = j + 1;
-                    const int done = j - kCopyLag;
-                    if (done >= 0 && done % cpb == cpb - 1) {
-                        bulk_wait<kCopyLag>();
-                        announce(done / cpb);
-                    }
-                }
-            }
-            if (ok) {
-                bulk_wait<0>();
-                for (int done = max(total - kCopyLag, 0); done < total; done++)
-                    if (done % cpb == cpb - 1) announce(done / cpb);
-            } else {
-                // leave no copy in flight into this CTA's shared memory: bounded second wait per slot
-                for (int j = stores_issued; j < loads_issued; j++) {
-                    const unsigned long long t0 = now_ns();
-                    while (!mbar_try_wait(bars + 8u * (j % kCopySlots), (uint32_t)(j / kCopySlots) & 1u) &&
-                           now_ns() - t0 < ab.budget_ns) {}
-                }
-                bulk_wait<0>();
-            }
-        }
-    }
-    __syncthreads();
-    // closing barrier: nobody overwrites a shard that a peer may still be reading
-    epoch++;
-    __syncthreads();
-    bad = 0;
-    if ((int)threadIdx.x < p.tp_size) {
-        const int q = threadIdx.x;
-        nvl::st_release_sys(p.pad[q] + (size_t)copy_idx * nvl::kMaxRanks + rank, epoch);
-        if (!nvl::wait_flag(p.pad[rank] + (size_t)copy_idx * nvl::kMaxRanks + q, epoch, ab.budget_ns)) bad = 1;
-    }
-    if (__syncthreads_or(bad) && threadIdx.x == 0) {
-        *ab.smem = 1;
-        atomicCAS(ab.global, 0u, 0x301u);
-    }
-    if (threadIdx.x == 0) *epoch_slot = epoch;
-}
 
 template <bool kPair>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -577,61 +357,7 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
     }
 
     // ---- reduce-scatter: add up the partial tiles that every rank stored for my rows
-    if (p.comm == COMM_REDUCE_SCATTER_C && *abort_slot == 0) {
-        const int    mbs        = tiles_m128 / p.tp_size;
-        const size_t shard_rows = (size_t)mbs * kBM;
-        const size_t slot_elems = shard_rows * (size_t)p.N;
-        const __nv_bfloat16 *mine = p.part[rank] + (size_t)(p.seq & 1) * p.tp_size * slot_elems;
-        const uint32_t *ctr_base  = p.pad[rank] + nvl::kPadCounterOff + (p.seq & 1) * p.tp_size * 64;
-        const int items = mbs * tiles_n;
-        __shared__ int item_ok;
-        for (int it = blockIdx.x; it < items; it += p.n_gemm_ctas) {
-            const int mb_in = it % mbs, nb = it / mbs;
-            if (threadIdx.x == 0) {
-                int good = 1;
-                for (int src = 0; src < p.tp_size && good; src++) {
-                    // rs_target = tiles that rank `src` has sent for this row block over all launches
-                    // of this parity, this one included (the host keeps the running total)
-                    good = wait_counter(ctr_base + src * 64 + mb_in, p.rs_target, true, ab, 6) ? 1 : 0;
-                }
-                item_ok = good;
-            }
-            __syncthreads();
-            if (!item_ok) break;
-            // 128 rows x 256 columns: 32 packs of 8 bf16 per row
-            for (int k = threadIdx.x; k < kBM * (kBN / 8); k += blockDim.x) {
-                const int    r = k / (kBN / 8), cpk = k % (kBN / 8);
-                const size_t row = (size_t)mb_in * kBM + r;
-                const int    col = nb * kBN + cpk * 8;
-                if (col >= p.N) continue;
-                float acc[8];
-#pragma unroll
-                for (int e = 0; e < 8; e++) acc[e] = 0.0f;
-                // all partials of this pack are requested before the first one is used
-                uint4 raw[kMaxTpRanks];
-#pragma unroll
-                for (int src = 0; src < kMaxTpRanks; src++) {
-                    if (src < p.tp_size) raw[src] = nvl::ld_nc16(mine + (size_t)src * slot_elems + row * (size_t)p.N + col);
-                }
-#pragma unroll
-                for (int src = 0; src < kMaxTpRanks; src++) {
-                    if (src < p.tp_size) {
-                        const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw[src]);
-#pragma unroll
-                        for (int e = 0; e < 4; e++) {
-                            float2 f = __bfloat1622float2(h[e]);
-                            acc[2 * e] += f.x;
-                            acc[2 * e + 1] += f.y;
-                        }
-                    }
-                }
-                uint4 o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
-                                     pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
-                *reinterpret_cast<uint4 *>(p.C[local] + row * (size_t)p.ldc + col) = o;
-            }
-            __syncthreads();
-        }
-    }
+    if (p.comm == COMM_REDUCE_SCATTER_C && *abort_slot == 0) rs_reduce_phase(p, rank, local, tiles_m128, ab);
 }
 
 }  // namespace

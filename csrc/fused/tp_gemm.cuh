@@ -58,6 +58,11 @@ struct GemmParams {
     // allgather mode: xg[r] is rank r's gathered A buffer [M,K] as mapped here; shard s of rank s is valid on entry
     __nv_bfloat16 *xg[kMaxTpRanks];       // indexed by TEAM rank
     uint32_t      *ready[kMaxTpRanks];    // per LOCAL rank: one flag per 128-row block of A, local memory
+    // block-scaled fp8 kernels (a_bytes == 1): A is e4m3 with one fp32 scale per row per 128 columns
+    int            a_bytes;                // bytes per element of A in xg: 0 or 2 = bf16, 1 = fp8
+    float         *sg[kMaxTpRanks];        // TEAM rank: scales of A, [M, K/128]; gathered together with xg in allgather mode
+    const float   *sb0[kMaxTpRanks];       // LOCAL rank: scales of B0, [rows/128, K/128]
+    const float   *sb1[kMaxTpRanks];       // LOCAL rank: scales of B1 (SwiGLU "up")
     // reduce-scatter mode: part[r] = rank r's partial buffer [tp_size][M/tp_size][N] as mapped here
     __nv_bfloat16 *part[kMaxTpRanks];     // indexed by TEAM rank
     uint32_t      *pad[kMaxTpRanks];      // signal pads (TEAM rank) for barriers and arrival counters
@@ -78,6 +83,10 @@ xccl_status_t make_tensor_map_2d(CUtensorMap *map, const void *base, uint64_t ro
                                  uint32_t box_rows);
 
 xccl_status_t launch_gemm(const GemmParams &p, const GemmLaunch &l, cudaStream_t stream);
+// The block-scaled fp8 kernel (tp_gemm_fp8.cu): same parameters; tmA / tmB0 / tmB1 are byte maps built by
+// make_tensor_map_u8 with boxes of 128 rows (A, plain B) or 64 rows (SwiGLU gate and up halves) x 128 bytes.
+xccl_status_t make_tensor_map_u8(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows);
+xccl_status_t launch_gemm_fp8(const GemmParams &p, const GemmLaunch &l, cudaStream_t stream);
 
 size_t gemm_smem_bytes();
 uint32_t *error_word();  // per-device error word shared by the GEMM kernels

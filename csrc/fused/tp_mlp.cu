@@ -7,6 +7,8 @@
 //   xg     [M, K]  gathered activations; rows [r*M/tp, (r+1)*M/tp) are rank r's own shard and are
 //          the only rows other ranks ever read
 //   part   [2][tp][M/tp][N_rs]  partial output tiles written by every rank, two parities
+#include <cuda_fp8.h>
+
 #include <algorithm>
 #include <cstring>
 #include <vector>
@@ -36,11 +38,39 @@ struct TpWorkspace {
     uint32_t      *pad(int r) const { return (uint32_t *)base[r]; }
     __nv_bfloat16 *xg(int r) const { return (__nv_bfloat16 *)(base[r] + off_xg); }
     __nv_bfloat16 *part(int r) const { return (__nv_bfloat16 *)(base[r] + off_part); }
+    // fp8 view of the gathered buffer: [M, K] e4m3 rows, then their [M, K/128] fp32 scales
+    float *sx(int r) const { return (float *)(base[r] + off_xg + (size_t)M * K); }
 };
 
 namespace {
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// One warp per (row, 128-column block): amax by shuffles, four values per lane.
+__global__ void __launch_bounds__(256) quantize_rows_1x128_kernel(const __nv_bfloat16 *x, int rows, int K, uint8_t *out,
+                                                                  float *scales)
+{
+    const int    kb_per_row = K / 128;
+    const size_t warp  = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) / 32;
+    const int    lane  = threadIdx.x % 32;
+    const size_t total = (size_t)rows * kb_per_row;
+    if (warp >= total) return;
+    const size_t row = warp / kb_per_row;
+    const int    kb  = (int)(warp % kb_per_row);
+    const uint2  raw = *reinterpret_cast<const uint2 *>(x + row * (size_t)K + (size_t)kb * 128 + lane * 4);
+    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+    const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+    float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y)));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float s = fmaxf(amax, 1e-12f) / 448.0f, inv = 1.0f / s;
+    uint32_t q = (uint32_t)__nv_cvt_float_to_fp8(a.x * inv, __NV_SATFINITE, __NV_E4M3) |
+                 ((uint32_t)__nv_cvt_float_to_fp8(a.y * inv, __NV_SATFINITE, __NV_E4M3) << 8) |
+                 ((uint32_t)__nv_cvt_float_to_fp8(b.x * inv, __NV_SATFINITE, __NV_E4M3) << 16) |
+                 ((uint32_t)__nv_cvt_float_to_fp8(b.y * inv, __NV_SATFINITE, __NV_E4M3) << 24);
+    *reinterpret_cast<uint32_t *>(out + row * (size_t)K + (size_t)kb * 128 + lane * 4) = q;
+    if (lane == 0) scales[row * kb_per_row + kb] = s;
+}
 
 void layout(TpWorkspace *w)
 {
@@ -252,6 +282,130 @@ xccl_status_t xccl_tp_gemm_rs(xccl_tp_ws_h w, const void *const *Hin, const void
         l.tmB1[i] = l.tmB0[i];
     }
     return launch_gemm(p, l, (cudaStream_t)stream);
+}
+
+
+xccl_status_t xccl_tp_quantize_rows(const void *x_bf16, int rows, int K, void *out8, float *scales, void *stream)
+{
+    if (x_bf16 == nullptr || out8 == nullptr || scales == nullptr || rows <= 0 || K <= 0 || K % 128 != 0) {
+        return XCCL_ERR_INVALID_PARAM;
+    }
+    const size_t warps  = (size_t)rows * (K / 128);
+    const size_t blocks = (warps * 32 + 255) / 256;
+    quantize_rows_1x128_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16 *)x_bf16, rows, K,
+                                                                                   (uint8_t *)out8, scales);
+    XCCL_CUDA_CHECK(cudaGetLastError());
+    return XCCL_OK;
+}
+
+void *xccl_tp_ws_x8_shard(xccl_tp_ws_h w, int local_rank)
+{
+    if (w == nullptr || local_rank < 0 || local_rank >= w->n_local) return nullptr;
+    int r = w->rank_base + local_rank;
+    return (uint8_t *)w->xg(r) + (size_t)r * (w->M / w->tp) * w->K;
+}
+
+float *xccl_tp_ws_sx_shard(xccl_tp_ws_h w, int local_rank)
+{
+    if (w == nullptr || local_rank < 0 || local_rank >= w->n_local || w->K % 128 != 0) return nullptr;
+    int r = w->rank_base + local_rank;
+    return w->sx(r) + (size_t)r * (w->M / w->tp) * (w->K / 128);
+}
+
+xccl_status_t xccl_tp_ag_gemm_swiglu_fp8(xccl_tp_ws_h w, const void *const *Wg8, const float *const *sWg,
+                                         const void *const *Wu8, const float *const *sWu, void *const *Hout, int F_local,
+                                         void *stream)
+{
+    if (w == nullptr || Wg8 == nullptr || sWg == nullptr || Wu8 == nullptr || sWu == nullptr || Hout == nullptr ||
+        F_local % 128 != 0 || w->K % 128 != 0) {
+        return XCCL_ERR_INVALID_PARAM;
+    }
+    GemmParams p{};
+    GemmLaunch l{};
+    p.M = w->M;
+    p.N = 2 * F_local;
+    p.K = w->K;
+    p.epilogue  = EPI_SWIGLU;
+    p.comm      = w->tp > 1 ? COMM_ALLGATHER_A : COMM_NONE;
+    p.tp_size   = w->tp;
+    p.rank_base = w->rank_base;
+    p.seq       = ++w->seq_ag;
+    p.error     = w->error;
+    p.ldc       = F_local;
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int ctas      = sms / w->n_local;
+    int copy_ctas = w->tp > 1 ? std::max(1, std::min(w->copy_ctas, ctas / 4)) : 0;
+    copy_ctas     = (copy_ctas + 1) & ~1;  // the same count as the bf16 kernel uses: the ready flags count copy CTAs
+    l.n_local     = w->n_local;
+    l.ctas        = ctas & ~1;
+    l.cooperative = w->tp > 1;
+    p.n_gemm_ctas = l.ctas - copy_ctas;
+    for (int r = 0; r < w->tp; r++) {
+        p.xg[r]  = w->xg(r);
+        p.sg[r]  = w->sx(r);
+        p.pad[r] = w->pad(r);
+    }
+    for (int i = 0; i < w->n_local; i++) {
+        p.C[i]     = (__nv_bfloat16 *)Hout[i];
+        p.ready[i] = w->ready[i];
+        p.sb0[i]   = sWg[i];
+        p.sb1[i]   = sWu[i];
+        xccl_status_t st = make_tensor_map_u8(&l.tmA[i], w->xg(w->rank_base + i), (uint64_t)w->M, (uint64_t)w->K, 128);
+        if (st != XCCL_OK) return st;
+        st = make_tensor_map_u8(&l.tmB0[i], Wg8[i], (uint64_t)F_local, (uint64_t)w->K, 64);
+        if (st != XCCL_OK) return st;
+        st = make_tensor_map_u8(&l.tmB1[i], Wu8[i], (uint64_t)F_local, (uint64_t)w->K, 64);
+        if (st != XCCL_OK) return st;
+    }
+    return launch_gemm_fp8(p, l, (cudaStream_t)stream);
+}
+
+xccl_status_t xccl_tp_gemm_rs_fp8(xccl_tp_ws_h w, const void *const *H8, const float *const *sH, const void *const *Wd8,
+                                  const float *const *sWd, void *const *Yout, int F_local, void *stream)
+{
+    if (w == nullptr || H8 == nullptr || sH == nullptr || Wd8 == nullptr || sWd == nullptr || Yout == nullptr ||
+        F_local % 128 != 0 || w->N_rs % 128 != 0) {
+        return XCCL_ERR_INVALID_PARAM;
+    }
+    GemmParams p{};
+    GemmLaunch l{};
+    p.M = w->M;
+    p.N = w->N_rs;
+    p.K = F_local;
+    p.epilogue  = EPI_STORE;
+    p.comm      = w->tp > 1 ? COMM_REDUCE_SCATTER_C : COMM_NONE;
+    p.tp_size   = w->tp;
+    p.rank_base = w->rank_base;
+    p.seq       = ++w->seq_rs;
+    p.error     = w->error;
+    p.ldc       = w->N_rs;
+    w->rs_count[p.seq & 1] += (uint32_t)(p.N / 128);  // tiles of 128 columns per row block
+    p.rs_target = w->rs_count[p.seq & 1];
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    l.n_local     = w->n_local;
+    l.ctas        = sms / w->n_local;
+    l.cooperative = w->emulated && w->tp > 1;
+    p.n_gemm_ctas = l.ctas;
+    for (int r = 0; r < w->tp; r++) {
+        p.part[r] = w->part(r);
+        p.pad[r]  = w->pad(r);
+    }
+    for (int i = 0; i < w->n_local; i++) {
+        p.C[i]   = (__nv_bfloat16 *)Yout[i];
+        p.sb0[i] = sWd[i];
+        // activation scales are local here: the kernel reads them through the TEAM-rank slot of this local rank
+        p.sg[w->rank_base + i] = const_cast<float *>(sH[i]);
+        xccl_status_t st = make_tensor_map_u8(&l.tmA[i], H8[i], (uint64_t)w->M, (uint64_t)F_local, 128);
+        if (st != XCCL_OK) return st;
+        st = make_tensor_map_u8(&l.tmB0[i], Wd8[i], (uint64_t)w->N_rs, (uint64_t)F_local, 128);
+        if (st != XCCL_OK) return st;
+        l.tmB1[i] = l.tmB0[i];
+    }
+    return launch_gemm_fp8(p, l, (cudaStream_t)stream);
 }
 
 }  // extern "C"

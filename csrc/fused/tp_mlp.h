@@ -36,6 +36,23 @@ xccl_status_t xccl_tp_ag_gemm_swiglu(xccl_tp_ws_h ws, const void *const *Wg, con
 xccl_status_t xccl_tp_gemm_rs(xccl_tp_ws_h ws, const void *const *Hin, const void *const *Wd, void *const *Yout,
                               int F_local, void *stream);
 
+
+// ---- block-scaled fp8 variants (e4m3 activations with 1 x 128 scales, e4m3 weights with 128 x 128 scales)
+// The fp8 rows and their scales live in the same gathered buffer as the bf16 rows ([M, K] bytes followed by
+// [M, K/128] fp32), so a workspace serves either precision, one at a time.
+// out8[rows, K] = e4m3(x / s), scales[rows, K/128] = amax over 128 columns / 448; K % 128 == 0
+xccl_status_t xccl_tp_quantize_rows(const void *x_bf16, int rows, int K, void *out8, float *scales, void *stream);
+void         *xccl_tp_ws_x8_shard(xccl_tp_ws_h ws, int local_rank);   // [M/tp, K] e4m3: this rank's rows
+float        *xccl_tp_ws_sx_shard(xccl_tp_ws_h ws, int local_rank);   // [M/tp, K/128] fp32: their scales
+// H[M, F_local] (bf16) = silu(X Wg^T) .* (X Wu^T); Wg8 / Wu8: [F_local, K] e4m3, sWg / sWu: [F_local/128, K/128]
+xccl_status_t xccl_tp_ag_gemm_swiglu_fp8(xccl_tp_ws_h ws, const void *const *Wg8, const float *const *sWg,
+                                         const void *const *Wu8, const float *const *sWu, void *const *Hout, int F_local,
+                                         void *stream);
+// Y[M/tp, N] (bf16) = reduce-scatter of H8 Wd8^T; H8: [M, F_local] e4m3 with sH [M, F_local/128];
+// Wd8: [N, F_local] e4m3 with sWd [N/128, F_local/128]
+xccl_status_t xccl_tp_gemm_rs_fp8(xccl_tp_ws_h ws, const void *const *H8, const float *const *sH, const void *const *Wd8,
+                                  const float *const *sWd, void *const *Yout, int F_local, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

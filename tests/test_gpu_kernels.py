@@ -377,3 +377,56 @@ def test_gemm_fp8_blockscaled_matches_dequantised_reference(dev, M, N, K_):
     assert gemm.last_error() == 0
     want = gemm.dequantize(a8, sa, 1) @ gemm.dequantize(b8, sb, 128).t()
     torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2 * float(want.abs().max()))
+
+
+def test_quantize_rows_kernel_matches_torch(dev):
+    from xccl_b200.ops import gemm
+    from xccl_b200.ops.tp import quantize_rows
+    x = (torch.randn(300, 512, device=dev) * torch.rand(300, 1, device=dev) * 5).to(torch.bfloat16)
+    x[7, 128:256] = 0  # an all-zero block keeps a finite scale
+    out8 = torch.empty(300, 512, dtype=torch.float8_e4m3fn, device=dev)
+    s = torch.empty(300, 4, dtype=torch.float32, device=dev)
+    quantize_rows(x, out8, s)
+    torch.cuda.synchronize()
+    q_ref, s_ref = gemm.quantize_act_1x128(x.float())
+    torch.testing.assert_close(s, s_ref, rtol=1e-6, atol=0)
+    # x / s and x * (1 / s) may round differently by one e4m3 step: compare the dequantised values
+    got, want = gemm.dequantize(out8, s, 1), gemm.dequantize(q_ref, s_ref, 1)
+    assert float((got - want).abs().max()) <= float(s.max()) * 32 + 1e-6   # one step at the top binade of e4m3
+    torch.testing.assert_close(got, x.float(), rtol=0.07, atol=1e-3)
+    _loaded_native()
+
+
+@pytest.mark.parametrize("tp", [1, 2, 4])
+def test_tp_mlp_fp8_fused_matches_dequantised_reference(dev, tp):
+    """fp8 allgather->GEMM+SwiGLU and GEMM->reduce-scatter (ranks emulated in one launch) against fp32
+    products of exactly the quantised operands the kernels consumed."""
+    from xccl_b200.models.tp_mlp import TpMlpFp8
+    from xccl_b200.ops import gemm
+    tokens, hidden, ffn = 1024, 512, 1024
+    mlp = TpMlpFp8(tokens, hidden, ffn, tp=tp, emulate=True)
+    try:
+        g = torch.Generator(device=dev).manual_seed(6)
+        x = torch.randn(tokens, hidden, device=dev, generator=g).to(torch.bfloat16)
+        shards = list(x.chunk(tp, 0))
+        for it in range(3):
+            y = mlp.forward(shards)
+            mlp.check_error()
+            xq = gemm.dequantize(torch.cat(mlp.x8, 0), torch.cat(mlp.sx, 0), 1)
+            y_want = torch.zeros(tokens, hidden, device=dev)
+            for r in range(tp):
+                wg = gemm.dequantize(mlp.w_gate8[r], mlp.s_gate[r], 128)
+                wu = gemm.dequantize(mlp.w_up8[r], mlp.s_up[r], 128)
+                wd = gemm.dequantize(mlp.w_down8[r], mlp.s_down[r], 128)
+                h_want = torch.nn.functional.silu(xq @ wg.t()) * (xq @ wu.t())
+                torch.testing.assert_close(mlp.h[r].float(), h_want, rtol=2e-2, atol=2e-2 * float(h_want.abs().max()))
+                y_want += gemm.dequantize(mlp.h8[r], mlp.sh[r], 1) @ wd.t()
+            got = torch.cat(y, 0).float()
+            torch.testing.assert_close(got, y_want, rtol=2e-2, atol=2e-2 * float(y_want.abs().max()))
+            # and the whole block stays close to the unquantised fp32 block
+            from xccl_b200.models.tp_mlp import reference_forward_fp32
+            full = reference_forward_fp32(x, *_full_weights(mlp))
+            assert float((got - full).abs().max()) <= 0.08 * float(full.abs().max()) + 1e-3
+    finally:
+        mlp.close()
+    _loaded_native()

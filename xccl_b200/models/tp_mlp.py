@@ -78,6 +78,46 @@ class TpMlp:
         self.ws.close()
 
 
+class TpMlpFp8(TpMlp):
+    """The same block on the fp8 tensor cores: activations quantised per row and 128 columns, weights per
+    128 x 128 block (e4m3, fp32 scales). Per step: quantise the input shard into the gathered buffer,
+    allgather->GEMM+SwiGLU (fp8 rows and scales travel together inside the kernel), quantise the
+    intermediate, GEMM->reduce-scatter. Four launches."""
+
+    def __init__(self, *args, **kw):
+        super().__init__(*args, **kw)
+        from ..ops.gemm import quantize_weight_128x128
+        from ..ops.tp import quantize_rows
+        self._quantize_rows = quantize_rows
+        qg = [quantize_weight_128x128(w) for w in self.w_gate]
+        qu = [quantize_weight_128x128(w) for w in self.w_up]
+        qd = [quantize_weight_128x128(w) for w in self.w_down]
+        self.w_gate8, self.s_gate = [q[0] for q in qg], [q[1] for q in qg]
+        self.w_up8, self.s_up = [q[0] for q in qu], [q[1] for q in qu]
+        self.w_down8, self.s_down = [q[0] for q in qd], [q[1] for q in qd]
+        f_local = self.ffn // self.tp
+        n = self.n_local
+        self.x_in = [torch.empty(self.tokens // self.tp, self.hidden, dtype=torch.bfloat16, device=self.device) for _ in range(n)]
+        self.x_shards = self.x_in          # the bf16 input of the step; its fp8 form goes into the gathered buffer
+        self.x8 = [self.ws.x8_shard(i) for i in range(n)]
+        self.sx = [self.ws.sx_shard(i) for i in range(n)]
+        self.h8 = [torch.empty(self.tokens, f_local, dtype=torch.float8_e4m3fn, device=self.device) for _ in range(n)]
+        self.sh = [torch.empty(self.tokens, f_local // 128, dtype=torch.float32, device=self.device) for _ in range(n)]
+
+    def forward(self, x_shards: Optional[list] = None) -> list:
+        if x_shards is not None:
+            for dst, src in zip(self.x_in, x_shards):
+                dst.copy_(src, non_blocking=True)
+        for i in range(self.n_local):
+            self._quantize_rows(self.x_in[i], self.x8[i], self.sx[i])
+        self.ws.ag_gemm_swiglu_fp8(self.w_gate8, self.s_gate, self.w_up8, self.s_up, self.h)
+        for i in range(self.n_local):
+            self._quantize_rows(self.h[i], self.h8[i], self.sh[i])
+        self.ws.gemm_rs_fp8(self.h8, self.sh, self.w_down8, self.s_down, self.y)
+        self.launches += 2 + 2 * self.n_local
+        return self.y
+
+
 class TorchTpMlp:
     """The same block with torch.distributed collectives and torch matmuls."""
 

@@ -22,6 +22,11 @@ K.optional("xccl_tp_ws_x_full", C.c_void_p, C.c_void_p, C.c_int)
 K.optional("xccl_tp_ws_error", C.c_uint32, C.c_void_p)
 K.optional("xccl_tp_ag_gemm_swiglu", C.c_int, C.c_void_p, _pp, _pp, _pp, C.c_int, C.c_void_p)
 K.optional("xccl_tp_gemm_rs", C.c_int, C.c_void_p, _pp, _pp, _pp, C.c_int, C.c_void_p)
+K.optional("xccl_tp_quantize_rows", C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p)
+K.optional("xccl_tp_ws_x8_shard", C.c_void_p, C.c_void_p, C.c_int)
+K.optional("xccl_tp_ws_sx_shard", C.c_void_p, C.c_void_p, C.c_int)
+K.optional("xccl_tp_ag_gemm_swiglu_fp8", C.c_int, C.c_void_p, _pp, _pp, _pp, _pp, _pp, C.c_int, C.c_void_p)
+K.optional("xccl_tp_gemm_rs_fp8", C.c_int, C.c_void_p, _pp, _pp, _pp, _pp, _pp, C.c_int, C.c_void_p)
 
 
 def _ptrs(ts: Sequence[torch.Tensor]):
@@ -31,6 +36,34 @@ def _ptrs(ts: Sequence[torch.Tensor]):
             raise ValueError("expected contiguous CUDA bf16 tensors")
         arr[i] = t.data_ptr()
     return arr
+
+
+def _raw_ptrs(ts: Sequence[torch.Tensor], dtype: torch.dtype):
+    arr = (C.c_void_p * len(ts))()
+    for i, t in enumerate(ts):
+        if t.dtype != dtype or not t.is_contiguous() or not t.is_cuda:
+            raise ValueError(f"expected contiguous CUDA {dtype} tensors")
+        arr[i] = t.data_ptr()
+    return arr
+
+
+def quantize_rows(x: torch.Tensor, out8: torch.Tensor, scales: torch.Tensor) -> None:
+    """``out8 [rows, K] = e4m3(x / s)``, ``scales [rows, K/128] = amax / 448`` (one CUDA kernel)."""
+    rows, Kd = x.shape
+    if x.dtype != torch.bfloat16 or not x.is_contiguous():
+        raise ValueError("expected a contiguous bf16 matrix")
+    st = K.load().xccl_tp_quantize_rows(x.data_ptr(), rows, Kd, out8.data_ptr(), scales.data_ptr(),
+                                        torch.cuda.current_stream().cuda_stream)
+    if st != K.OK:
+        raise XcclError(st, "xccl_tp_quantize_rows")
+
+
+def _as_typed(ptr: int, nbytes: int, device: torch.device) -> torch.Tensor:
+    """A uint8 view of library-owned device memory."""
+    class _Mem:
+        __cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+    return torch.as_tensor(_Mem(), device=device)
 
 
 def _as_tensor(ptr: int, shape: tuple, device: torch.device) -> torch.Tensor:
@@ -82,6 +115,35 @@ class TpWorkspace:
                                       torch.cuda.current_stream().cuda_stream)
         if st != K.OK:
             raise XcclError(st, "xccl_tp_gemm_rs")
+
+    # ---- block-scaled fp8 (the same buffers hold [M, K] e4m3 rows followed by [M, K/128] fp32 scales)
+    def x8_shard(self, local_rank: int = 0) -> torch.Tensor:
+        p = K.load().xccl_tp_ws_x8_shard(self.h, local_rank)
+        rows = self.M // self.tp
+        return _as_typed(p, rows * self.K, self.device).view(torch.float8_e4m3fn).view(rows, self.K)
+
+    def sx_shard(self, local_rank: int = 0) -> torch.Tensor:
+        p = K.load().xccl_tp_ws_sx_shard(self.h, local_rank)
+        rows = self.M // self.tp
+        return _as_typed(p, rows * (self.K // 128) * 4, self.device).view(torch.float32).view(rows, self.K // 128)
+
+    def ag_gemm_swiglu_fp8(self, w_gate8, s_gate, w_up8, s_up, out: Sequence[torch.Tensor]) -> None:
+        f_local = w_gate8[0].shape[0]
+        f8, f32 = torch.float8_e4m3fn, torch.float32
+        st = K.load().xccl_tp_ag_gemm_swiglu_fp8(self.h, _raw_ptrs(w_gate8, f8), _raw_ptrs(s_gate, f32), _raw_ptrs(w_up8, f8),
+                                                 _raw_ptrs(s_up, f32), _ptrs(out), f_local,
+                                                 torch.cuda.current_stream().cuda_stream)
+        if st != K.OK:
+            raise XcclError(st, "xccl_tp_ag_gemm_swiglu_fp8")
+
+    def gemm_rs_fp8(self, h8, s_h, w_down8, s_down, out: Sequence[torch.Tensor]) -> None:
+        f_local = h8[0].shape[1]
+        f8, f32 = torch.float8_e4m3fn, torch.float32
+        st = K.load().xccl_tp_gemm_rs_fp8(self.h, _raw_ptrs(h8, f8), _raw_ptrs(s_h, f32), _raw_ptrs(w_down8, f8),
+                                          _raw_ptrs(s_down, f32), _ptrs(out), f_local,
+                                          torch.cuda.current_stream().cuda_stream)
+        if st != K.OK:
+            raise XcclError(st, "xccl_tp_gemm_rs_fp8")
 
     def error(self) -> int:
         torch.cuda.synchronize()
