@@ -127,6 +127,21 @@ xccl_status_t xccl_nvlink_emu_collective(void *world, int coll_type, const void 
     cfg.blocks      = blocks;
     cudaStream_t  s = (cudaStream_t)stream;
     xccl_status_t st;
+    if (alg == ALG_DIRECT) {
+        // emulated ranks share one address space: the "registered" peer buffers are the buffers themselves
+        for (int r = 0; r < w.size; r++) {
+            c.peer_src[r] = c.src[r];
+            c.peer_dst[r] = c.dst[r];
+        }
+        st = launch_direct(w, c, coll_type, (xccl_dt_t)dt, (xccl_dt_t)out_dt, cfg, s);
+        if (st != XCCL_OK) return st;
+        XCCL_CUDA_CHECK(cudaStreamSynchronize(s));
+        for (int r = 0; r < w.size; r++) {
+            if (e->status(r).code == NVL_TIMEOUT) return XCCL_ERR_TIMED_OUT;
+            if (e->status(r).code != NVL_OK) return XCCL_ERR_NO_MESSAGE;
+        }
+        return XCCL_OK;
+    }
     switch (coll_type) {
     case XCCL_ALLREDUCE: {
         Alg a = (Alg)alg;

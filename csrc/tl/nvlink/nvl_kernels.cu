@@ -525,6 +525,77 @@ __global__ void __launch_bounds__(512) alltoallv_kernel(World w, Call c)
     self_end(w, s);
 }
 
+// ------------------------------------------------------------------ direct (zero-copy) algorithms
+// No workspace: the kernels read peers' user buffers and write peers' user buffers. The opening
+// barrier tells a block that the same block of every peer has started, hence that the peer's stream
+// has produced its source; the closing barrier tells it that every peer has finished reading from and
+// writing to this rank's buffers.
+
+// allreduce: rank r owns 1/N of the packs: it loads that share from all N sources, reduces (scale and
+// cast fused) and stores the result into all N destinations. In place is safe: a pack is read and
+// written by one thread only. reduce-scatter (kScatter): segment r of every source -> local dst.
+template <typename T, typename O, bool kSum, bool kScatter>
+__global__ void __launch_bounds__(512) direct_reduce_kernel(World w, Call c)
+{
+    using A           = typename Traits<T>::acc;
+    constexpr int E   = Epp<T>::value;
+    Self          s   = self_begin(w);
+    const size_t  npacks = (c.count + E - 1) / E;
+    block_barrier(w, s);
+    if (!s.failed) {
+        if (kScatter) {
+            // count = elements per segment; my segment of every peer
+            const Range r   = block_range(npacks);
+            O          *dst = (O *)c.dst[s.local];
+            const size_t seg_bytes = c.count * sizeof(T);
+            reduce_packs<T, kSum, 2>([&](int q) { return (const char *)c.peer_src[q] + (size_t)s.rank * seg_bytes; }, w.size, r.lo,
+                                     r.hi, c.op, [&](size_t i, A(&acc)[E]) {
+#pragma unroll
+                                         for (int e = 0; e < E; e++) acc[e] = dev::scaled(acc[e], c.scale, c.do_scale != 0);
+                                         store_out<O, E>(dst, i, c.count, true, acc);
+                                     });
+        } else {
+            const size_t per = (npacks + w.size - 1) / w.size;
+            const size_t lo  = min((size_t)s.rank * per, npacks), hi = min(lo + per, npacks);
+            const Range  r   = sub_range(Range{lo, hi}, gridDim.x, blockIdx.x);
+            reduce_packs<T, kSum, 2>([&](int q) { return (const char *)c.peer_src[q]; }, w.size, r.lo, r.hi, c.op,
+                                     [&](size_t i, A(&acc)[E]) {
+#pragma unroll
+                                         for (int e = 0; e < E; e++) acc[e] = dev::scaled(acc[e], c.scale, c.do_scale != 0);
+                                         for (int q = 0; q < w.size; q++) {
+                                             const int p = (s.rank + q) % w.size;
+                                             store_out<O, E>((O *)c.peer_dst[p], i, c.count, true, acc);
+                                         }
+                                     });
+        }
+        block_barrier(w, s);
+    }
+    self_end(w, s);
+}
+
+// allgather / alltoall: pull every peer's contribution straight into the local destination.
+template <int KIND> __global__ void __launch_bounds__(512) direct_mover_kernel(World w, Call c)
+{
+    Self         s   = self_begin(w);
+    Byte        *dst = (Byte *)c.dst[s.local];
+    const size_t seg_bytes = (KIND == MV_ALLGATHER) ? c.len / w.size : c.len;
+    const size_t npacks    = seg_bytes / 16;
+    block_barrier(w, s);
+    if (!s.failed) {
+        const Range r = block_range(npacks);
+        for (int q = 0; q < w.size; q++) {
+            const int   p    = (s.rank + q) % w.size;
+            const char *from = (const char *)c.peer_src[p] + ((KIND == MV_ALLTOALL) ? (size_t)s.rank * seg_bytes : 0);
+            char       *out  = (char *)dst + (size_t)p * seg_bytes;
+            if (from == out) continue;  // in-place allgather: my own segment is where it belongs
+            stream_packs<4>(
+                r.lo, r.hi, [&](size_t i) { return ld_nc16(from + i * 16); }, [&](size_t i, uint4 v) { st_16(out + i * 16, v); });
+        }
+        block_barrier(w, s);
+    }
+    self_end(w, s);
+}
+
 // ------------------------------------------------------------------ synchronisation only
 
 __global__ void sync_kernel(World w, Call c, int kind)
@@ -659,6 +730,70 @@ xccl_status_t reduce_typed(const World &w, const Call &c, const LaunchCfg &cfg, 
 }
 
 }  // namespace
+
+bool direct_shape_ok(int coll, const Call &c, xccl_dt_t dt, int team_size)
+{
+    auto al = [](const void *p) { return ((uintptr_t)p & 15) == 0; };
+    for (int r = 0; r < team_size; r++) {
+        if (c.peer_src[r] == nullptr || !al(c.peer_src[r])) return false;
+        if (coll == XCCL_ALLREDUCE && (c.peer_dst[r] == nullptr || !al(c.peer_dst[r]))) return false;
+    }
+    switch (coll) {
+    case XCCL_ALLREDUCE:
+    case XCCL_REDUCE_SCATTER: return (c.count * xccl_dt_size(dt)) % 16 == 0 && c.count > 0;
+    case XCCL_ALLGATHER: return c.len % ((size_t)team_size * 16) == 0 && c.len > 0;
+    case XCCL_ALLTOALL: return c.len % 16 == 0 && c.len > 0;
+    default: return false;
+    }
+}
+
+namespace {
+template <typename T, typename O, bool kScatter>
+xccl_status_t direct_reduce_typed(const World &w, const Call &c, const LaunchCfg &cfg, cudaStream_t stream)
+{
+    constexpr int E      = Epp<T>::value;
+    const size_t  npacks = (c.count + E - 1) / E;
+    const bool    sum    = (c.op == XCCL_OP_SUM);
+    auto          k      = sum ? direct_reduce_kernel<T, O, true, kScatter> : direct_reduce_kernel<T, O, false, kScatter>;
+    const size_t  mine   = kScatter ? npacks : (npacks + w.size - 1) / w.size;
+    int           blocks = pick_blocks(k, w, cfg, mine, 2);
+    return launch(k, dim3((unsigned)blocks, (unsigned)w.n_local), dim3((unsigned)cfg.threads), cfg.cooperative, stream, w, c);
+}
+template <bool kScatter>
+xccl_status_t direct_reduce_dispatch(const World &w, const Call &c, xccl_dt_t dt, xccl_dt_t out_dt, const LaunchCfg &cfg,
+                                     cudaStream_t stream)
+{
+    if (out_dt == XCCL_DT_UNSUPPORTED || out_dt == XCCL_DT_LAST_PREDEFINED) out_dt = dt;
+    if (!reduce_op_ok(dt, (xccl_op_t)c.op)) return XCCL_ERR_UNSUPPORTED;
+    // the direct kernels cover the gradient types; everything else keeps the staged kernels
+    if (dt == XCCL_DT_FLOAT32 && out_dt == XCCL_DT_FLOAT32) return direct_reduce_typed<float, float, kScatter>(w, c, cfg, stream);
+    if (dt == XCCL_DT_FLOAT32 && out_dt == XCCL_DT_BFLOAT16) return direct_reduce_typed<float, __nv_bfloat16, kScatter>(w, c, cfg, stream);
+    if (dt == XCCL_DT_BFLOAT16 && out_dt == XCCL_DT_BFLOAT16) return direct_reduce_typed<__nv_bfloat16, __nv_bfloat16, kScatter>(w, c, cfg, stream);
+    if (dt == XCCL_DT_FLOAT16 && out_dt == XCCL_DT_FLOAT16) return direct_reduce_typed<__half, __half, kScatter>(w, c, cfg, stream);
+    return XCCL_ERR_UNSUPPORTED;
+}
+}  // namespace
+
+xccl_status_t launch_direct(const World &w, const Call &c, int coll, xccl_dt_t dt, xccl_dt_t out_dt, const LaunchCfg &cfg,
+                            cudaStream_t stream)
+{
+    if (!direct_shape_ok(coll, c, dt, w.size)) return XCCL_ERR_INVALID_PARAM;
+    switch (coll) {
+    case XCCL_ALLREDUCE: return direct_reduce_dispatch<false>(w, c, dt, out_dt, cfg, stream);
+    case XCCL_REDUCE_SCATTER: return direct_reduce_dispatch<true>(w, c, dt, out_dt, cfg, stream);
+    case XCCL_ALLGATHER: {
+        auto k      = direct_mover_kernel<MV_ALLGATHER>;
+        int  blocks = pick_blocks(k, w, cfg, c.len / 16, 4);
+        return launch(k, dim3((unsigned)blocks, (unsigned)w.n_local), dim3((unsigned)cfg.threads), cfg.cooperative, stream, w, c);
+    }
+    case XCCL_ALLTOALL: {
+        auto k      = direct_mover_kernel<MV_ALLTOALL>;
+        int  blocks = pick_blocks(k, w, cfg, c.len * (size_t)w.size / 16, 4);
+        return launch(k, dim3((unsigned)blocks, (unsigned)w.n_local), dim3((unsigned)cfg.threads), cfg.cooperative, stream, w, c);
+    }
+    default: return XCCL_ERR_UNSUPPORTED;
+    }
+}
 
 bool nvls_supported(xccl_dt_t dt, xccl_op_t op)
 {

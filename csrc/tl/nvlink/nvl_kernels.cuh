@@ -22,9 +22,13 @@ struct Call {
     int             do_scale;
     int             parity;            // which half of the workspace this launch uses
     int             src_es, dst_es;    // alltoallv element sizes
+    // Direct algorithms: every rank's user buffers as mapped in this process, by TEAM rank (peer
+    // mappings of registered buffers in a real team, the plain pointers when ranks are emulated).
+    const void     *peer_src[kMaxRanks];
+    void           *peer_dst[kMaxRanks];
 };
 
-enum Alg { ALG_AUTO = 0, ALG_ONE_SHOT = 1, ALG_TWO_SHOT = 2, ALG_NVLS = 3 };
+enum Alg { ALG_AUTO = 0, ALG_ONE_SHOT = 1, ALG_TWO_SHOT = 2, ALG_NVLS = 3, ALG_DIRECT = 4 };
 
 struct LaunchCfg {
     int  blocks  = 0;      // 0 = choose from the message size
@@ -49,6 +53,12 @@ xccl_status_t launch_allgather(const World &w, const Call &c, const LaunchCfg &c
 xccl_status_t launch_alltoall(const World &w, const Call &c, const LaunchCfg &cfg, cudaStream_t stream);
 xccl_status_t launch_alltoallv(const World &w, const Call &c, size_t max_src_bytes, const LaunchCfg &cfg,
                                cudaStream_t stream);
+// Direct (zero-copy) algorithms on registered user buffers, for messages where staging through the
+// workspace costs more than it hides. coll: XCCL_ALLREDUCE, XCCL_REDUCE_SCATTER, XCCL_ALLGATHER or
+// XCCL_ALLTOALL. All buffers 16-byte aligned, byte counts multiples of 16.
+xccl_status_t launch_direct(const World &w, const Call &c, int coll, xccl_dt_t dt, xccl_dt_t out_dt, const LaunchCfg &cfg,
+                            cudaStream_t stream);
+bool          direct_shape_ok(int coll, const Call &c, xccl_dt_t dt, int team_size);
 // kind: XCCL_BARRIER, XCCL_FANIN or XCCL_FANOUT
 xccl_status_t launch_sync(const World &w, const Call &c, int kind, const LaunchCfg &cfg, cudaStream_t stream);
 // A barrier whose flags nobody sets, with a short budget: reports NVL_TIMEOUT in the status

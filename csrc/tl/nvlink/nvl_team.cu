@@ -9,6 +9,9 @@
 // a measured table can be applied without rebuilding.
 #include <cstdlib>
 #include <cstring>
+#include <map>
+#include <string>
+#include <vector>
 
 #include "../../core/core.h"
 #include "../../cuda/cuda_common.h"
@@ -27,6 +30,8 @@ struct NvlCfg {
     size_t one_shot_max  = 128u << 10;
     size_t nvls_min      = 256u << 10;
     size_t bcast_mc_min  = 0;
+    size_t direct_min    = 32u << 20;   // messages from this size register their buffers and skip the workspace
+    bool   direct        = true;
     int    max_blocks    = 64;
     int    threads       = 512;
     double wait_timeout_ms = 5000.0;
@@ -56,6 +61,11 @@ private:
     double              elapsed_us_ = -1.0;
     uint32_t           *vmeta_ = nullptr;
     size_t              max_src_bytes_ = 0;
+    // direct algorithms: every rank's buffers of this request, mapped here at init
+    xccl_status_t       register_buffers(void *src, void *dst, size_t src_bytes, size_t dst_bytes);
+    bool                direct_ = false;
+    const void         *peer_src_[kMaxRanks] = {nullptr};
+    void               *peer_dst_[kMaxRanks] = {nullptr};
 };
 
 class NvlTeam final : public TlTeam {
@@ -67,12 +77,29 @@ public:
             cudaStreamSynchronize(stream);
             cudaStreamDestroy(stream);
         }
+        for (auto &kv : ipc_cache) cudaIpcCloseMemHandle(kv.second);
         delete region;
         if (status_host != nullptr) cudaFreeHost(status_host);
     }
 
+    // Mapping of a peer's allocation (legacy CUDA IPC), opened once per allocation and kept until the team goes.
+    void *open_peer(const cudaIpcMemHandle_t &h)
+    {
+        std::string key((const char *)&h, sizeof(h));
+        auto        it = ipc_cache.find(key);
+        if (it != ipc_cache.end()) return it->second;
+        void *p = nullptr;
+        if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        ipc_cache[key] = p;
+        return p;
+    }
+
     xccl_status_t init(const OobGroup &g)
     {
+        oob  = g;
         rank = g.rank;
         size = g.size;
         if (size > kMaxRanks) return XCCL_ERR_UNSUPPORTED;
@@ -122,6 +149,8 @@ public:
 
     TeamLib         *tl_;
     NvlCfg           cfg;
+    OobGroup         oob;
+    std::map<std::string, void *> ipc_cache;
     SymmetricRegion *region = nullptr;
     World            world{};
     HostStatus      *status_host = nullptr;
@@ -177,6 +206,106 @@ xccl_status_t NvlReq::prepare()
     }
     XCCL_CUDA_CHECK(cudaEventCreateWithFlags(&done_, team_->cfg.timing ? cudaEventDefault : cudaEventDisableTiming));
     if (team_->cfg.timing) XCCL_CUDA_CHECK(cudaEventCreate(&start_));
+    // Large messages (or an explicit request for the direct algorithm) register their buffers with the
+    // peers now: one out-of-band exchange at init buys posts that never touch the workspace.
+    const bool forced = args_.alg.set_by_user && args_.alg.id == ALG_DIRECT;
+    size_t     src_bytes = 0, dst_bytes = 0, msg = 0;
+    switch (args_.coll_type) {
+    case XCCL_ALLREDUCE:
+        src_bytes = dst_bytes = msg = args_.reduce_info.count * xccl_dt_size(args_.reduce_info.dt);
+        if (args_.field_mask & XCCL_COLL_OP_ARGS_FIELD_EPILOGUE) {
+            xccl_dt_t o = args_.epilogue.out_dt;
+            if (o != XCCL_DT_UNSUPPORTED && o != XCCL_DT_LAST_PREDEFINED) dst_bytes = args_.reduce_info.count * xccl_dt_size(o);
+        }
+        break;
+    case XCCL_REDUCE_SCATTER: {
+        size_t cnt = args_.reduce_info.count;
+        if (cnt == 0 && bi.len != 0) cnt = bi.len / xccl_dt_size(args_.reduce_info.dt) / (size_t)n;
+        src_bytes = msg = cnt * xccl_dt_size(args_.reduce_info.dt) * (size_t)n;
+        dst_bytes = 0;  // written locally only
+        break;
+    }
+    case XCCL_ALLGATHER:
+        src_bytes = bi.len / (size_t)n;
+        msg       = bi.len;
+        break;
+    case XCCL_ALLTOALL:
+        src_bytes = msg = bi.len * (size_t)n;
+        break;
+    default: break;
+    }
+    if (msg != 0 && team_->cfg.direct && (forced || msg >= team_->cfg.direct_min)) {
+        void *src = bi.src_buffer, *dst = bi.dst_buffer;
+        if (src == XCCL_IN_PLACE || src == nullptr) {
+            src = dst;
+            if (args_.coll_type == XCCL_ALLGATHER) src = (char *)dst + (size_t)team_->rank * (bi.len / (size_t)n);
+        }
+        xccl_status_t st = register_buffers(src, dst, src_bytes, dst_bytes);
+        if (st != XCCL_OK) return st;
+    }
+    return XCCL_OK;
+}
+
+// Collective over the team (every member calls collective_init in the same order): exchanges CUDA IPC
+// handles of the allocations that hold src and dst, maps the peers', and agrees on whether all succeeded.
+xccl_status_t NvlReq::register_buffers(void *src, void *dst, size_t src_bytes, size_t dst_bytes)
+{
+    struct Info {
+        cudaIpcMemHandle_t src_h, dst_h;
+        size_t             src_off, dst_off;
+        int                src_ok, dst_ok;
+    };
+    const int n = team_->size;
+    XCCL_DRIVER_FN(cuMemGetAddressRange);
+    auto describe = [&](void *p, size_t bytes, cudaIpcMemHandle_t *h, size_t *off) -> int {
+        if (p == nullptr || bytes == 0) return 0;
+        CUdeviceptr base = 0;
+        size_t      size = 0;
+        if (cuMemGetAddressRange(&base, &size, (CUdeviceptr)p) != CUDA_SUCCESS) return 0;
+        if ((CUdeviceptr)p + bytes > base + size) return 0;
+        if (cudaIpcGetMemHandle(h, (void *)base) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return 0;
+        }
+        *off = (size_t)((CUdeviceptr)p - base);
+        return 1;
+    };
+    Info mine{};
+    mine.src_ok = describe(src, src_bytes, &mine.src_h, &mine.src_off);
+    mine.dst_ok = dst_bytes != 0 ? describe(dst, dst_bytes, &mine.dst_h, &mine.dst_off) : 1;
+    std::vector<Info> all((size_t)n);
+    xccl_status_t     st = team_->oob.allgather_blocking(&mine, all.data(), sizeof(Info));
+    if (st != XCCL_OK) return st;
+    int ok = 1;
+    for (int p = 0; p < n && ok; p++) ok = all[(size_t)p].src_ok && all[(size_t)p].dst_ok;
+    for (int p = 0; p < n && ok; p++) {
+        if (p == team_->rank) {
+            peer_src_[p] = src;
+            peer_dst_[p] = dst;
+            continue;
+        }
+        char *ms = (char *)team_->open_peer(all[(size_t)p].src_h);
+        if (ms == nullptr) {
+            ok = 0;
+            break;
+        }
+        peer_src_[p] = ms + all[(size_t)p].src_off;
+        if (dst_bytes != 0) {
+            char *md = (char *)team_->open_peer(all[(size_t)p].dst_h);
+            if (md == nullptr) {
+                ok = 0;
+                break;
+            }
+            peer_dst_[p] = md + all[(size_t)p].dst_off;
+        }
+    }
+    // one rank that could not map a peer sends everybody back to the staged kernels
+    std::vector<int> oks((size_t)n);
+    st = team_->oob.allgather_blocking(&ok, oks.data(), sizeof(int));
+    if (st != XCCL_OK) return st;
+    for (int p = 0; p < n; p++) ok = ok && oks[(size_t)p];
+    direct_ = ok != 0;
+    if (!direct_) tl_debug(team_->tl_, "nvlink: buffers of this request could not be registered, staging through the workspace");
     return XCCL_OK;
 }
 
@@ -218,6 +347,25 @@ xccl_status_t NvlReq::post()
     const xccl_dt_t dt = args_.reduce_info.dt;
     if (start_ != nullptr) XCCL_CUDA_CHECK(cudaEventRecord(start_, s));
     xccl_status_t st;
+    if (direct_) {
+        for (int p = 0; p < team_->size; p++) {
+            c.peer_src[p] = peer_src_[p];
+            c.peer_dst[p] = peer_dst_[p];
+        }
+        if (args_.coll_type == XCCL_REDUCE_SCATTER && c.count == 0 && c.len != 0) {
+            c.count = c.len / xccl_dt_size(dt) / (size_t)team_->size;
+        }
+        if (direct_shape_ok((int)args_.coll_type, c, dt, team_->size)) {
+            st = launch_direct(w, c, (int)args_.coll_type, dt, out_dt, cfg, s);
+            if (st == XCCL_OK) {
+                XCCL_CUDA_CHECK(cudaEventRecord(done_, s));
+                in_flight_ = true;
+                return XCCL_OK;
+            }
+            if (st != XCCL_ERR_UNSUPPORTED) return st;
+        }
+        direct_ = false;  // shape or type outside the direct kernels: same answer on every rank
+    }
     switch (args_.coll_type) {
     case XCCL_ALLREDUCE: {
         const size_t bytes = c.count * xccl_dt_size(dt);
@@ -362,6 +510,8 @@ public:
             {"ONE_SHOT_MAX", "0", "Allreduce messages up to this size use the one-shot kernel (0: by team size, 256k from 8 ranks, else 1m)", OptType::MEMUNITS},
             {"NVLS_MIN", "0", "Allreduce messages from this size use NVLS when available (0: by team size, 1m from 8 ranks, else 128k)", OptType::MEMUNITS},
             {"BCAST_MC_MIN", "0", "Broadcasts from this size go through the NVSwitch multicast mapping when available", OptType::MEMUNITS},
+            {"DIRECT", "y", "Register the buffers of large messages with the peers (CUDA IPC) and run zero-copy kernels on them", OptType::BOOL},
+            {"DIRECT_MIN", "32m", "Messages from this size use the direct (zero-copy) kernels", OptType::MEMUNITS},
             {"MAX_BLOCKS", "128", "Upper bound of thread blocks per collective kernel (at most 128)", OptType::UINT},
             {"THREADS", "512", "Threads per block of the collective kernels", OptType::UINT},
             {"WAIT_TIMEOUT_MS", "5000", "Budget of every device-side wait for a peer", OptType::DOUBLE},
@@ -393,6 +543,8 @@ public:
         c.one_shot_max    = (size_t)cfg.num("ONE_SHOT_MAX");
         c.nvls_min        = (size_t)cfg.num("NVLS_MIN");
         c.bcast_mc_min    = (size_t)cfg.num("BCAST_MC_MIN");
+        c.direct_min      = (size_t)cfg.num("DIRECT_MIN");
+        c.direct          = cfg.flag("DIRECT");
         c.max_blocks      = std::max(1, std::min((int)cfg.num("MAX_BLOCKS"), kMaxBlocks));
         c.threads         = std::max(32, std::min((int)cfg.num("THREADS"), 512)) / 32 * 32;
         c.wait_timeout_ms = cfg.real("WAIT_TIMEOUT_MS");

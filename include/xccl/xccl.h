@@ -394,7 +394,8 @@ enum xccl_nvlink_alg_id {               /* nvlink team allreduce */
     XCCL_NVLINK_ALG_AUTO = 0,
     XCCL_NVLINK_ALG_ONE_SHOT = 1,
     XCCL_NVLINK_ALG_TWO_SHOT = 2,
-    XCCL_NVLINK_ALG_NVLS = 3
+    XCCL_NVLINK_ALG_NVLS = 3,
+    XCCL_NVLINK_ALG_DIRECT = 4   /* zero-copy kernels on buffers registered with the peers at init */
 };
 
 /* Persistent request life cycle. init captures the arguments; post starts one execution and

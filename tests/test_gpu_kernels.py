@@ -185,6 +185,55 @@ def test_emu_bcast_allgather_alltoall(world4, dev):
             assert torch.equal(dsts[r], want)
 
 
+def test_emu_direct_zero_copy_algorithms(world4, dev):
+    """The direct kernels read and write the ranks' own buffers (no workspace): allreduce with the fused
+    scale and cast, in place, reduce-scatter, allgather (also in place) and alltoall."""
+    n = 4
+    D = K.NVLINK_ALG_DIRECT
+    for dtype, count in ((torch.float32, 4 * 5000), (torch.bfloat16, 8 * 70001), (torch.float16, 8 * 16)):
+        srcs = _ints(n, count, dtype, dev, seed=11)
+        dsts = [torch.zeros(count, dtype=dtype, device=dev) for _ in range(n)]
+        world4.allreduce(srcs, dsts, alg=D)
+        want = torch.stack([s.float() for s in srcs]).sum(0)
+        for d in dsts:
+            assert torch.equal(d.float(), want)
+    srcs = [torch.randn(4 * 3000, device=dev) for _ in range(n)]
+    want = torch.stack(srcs).sum(0) * 0.25
+    outs = [torch.zeros(4 * 3000, dtype=torch.bfloat16, device=dev) for _ in range(n)]
+    world4.allreduce(srcs, outs, alg=D, scale=0.25)          # fp32 -> bf16 with the average fused
+    for o in outs:
+        torch.testing.assert_close(o.float(), want, rtol=1e-2, atol=1e-2)
+    bufs = [s.clone() for s in srcs]
+    world4.allreduce(bufs, bufs, alg=D, op=K.OP_MAX)        # in place
+    for b in bufs:
+        assert torch.equal(b, torch.stack(srcs).max(0).values)
+    per = 4 * 1237
+    srcs = _ints(n, per * n, torch.float32, dev, seed=12)
+    dsts = [torch.zeros(per, device=dev) for _ in range(n)]
+    world4.reduce_scatter(srcs, dsts, alg=D)
+    full = torch.stack(srcs).sum(0)
+    for r in range(n):
+        assert torch.equal(dsts[r], full[r * per:(r + 1) * per])
+    per = 16 * 4099
+    srcs = [torch.randint(0, 255, (per,), dtype=torch.uint8, device=dev) for _ in range(n)]
+    dsts = [torch.zeros(per * n, dtype=torch.uint8, device=dev) for _ in range(n)]
+    world4.allgather(srcs, dsts, alg=D)
+    for d in dsts:
+        assert torch.equal(d, torch.cat(srcs))
+    inplace = [torch.zeros(per * n, dtype=torch.uint8, device=dev) for _ in range(n)]
+    for r in range(n):
+        inplace[r][r * per:(r + 1) * per] = srcs[r]
+    world4.allgather([inplace[r][r * per:(r + 1) * per] for r in range(n)], inplace, alg=D)
+    for d in inplace:
+        assert torch.equal(d, torch.cat(srcs))
+    per = 4 * 25001
+    srcs = [torch.randn(per * n, device=dev) for _ in range(n)]
+    dsts = [torch.zeros(per * n, device=dev) for _ in range(n)]
+    world4.alltoall(srcs, dsts, alg=D)
+    for r in range(n):
+        assert torch.equal(dsts[r], torch.cat([srcs[s][r * per:(r + 1) * per] for s in range(n)]))
+
+
 def test_emu_alltoallv(world4, dev):
     n = 4
     sc = [[(s * 3 + d * 5 + 1) for d in range(n)] for s in range(n)]  # elements rank s sends to rank d

@@ -112,6 +112,46 @@ def _rank_main(rank, size, job, tls, nvls):
         dst = torch.zeros(sum(rc), device=dev)
         team.alltoallv(src, sc, sd, dst, rc, rd, stream=stream).run().finalize()
         assert torch.equal(dst.cpu(), torch.cat([torch.full((rc[s],), float(s * 100 + rank)) for s in range(size)]))
+        # direct (zero-copy) kernels on buffers registered with the peers through CUDA IPC at init;
+        # persistent requests posted several times, sub-allocations of torch's caching allocator
+        D = K.NVLINK_ALG_DIRECT
+        for dtype, count in ((torch.float32, 4 * 100003), (torch.bfloat16, 8 * 300007)):
+            src = _vals(rank, count, dtype, seed=21).to(dev)
+            dst = torch.zeros_like(src)
+            req = team.allreduce(src, dst, alg=D, stream=stream)
+            want = torch.stack([_vals(r, count, dtype, seed=21).double() for r in range(size)]).sum(0).to(dtype)
+            for _ in range(3):
+                dst.zero_()
+                req.post().wait()
+                assert torch.equal(dst.cpu(), want), ("direct allreduce", dtype)
+            req.finalize()
+        src = torch.randn(4 * 50000, device=dev, generator=torch.Generator(device=dev).manual_seed(rank + 40))
+        out16 = torch.empty(4 * 50000, device=dev, dtype=torch.bfloat16)
+        req = team.allreduce(src, out16, alg=D, scale=1.0 / size, out_dt=K.DT_BFLOAT16, stream=stream)
+        req.post().wait()
+        req.finalize()
+        allv = [torch.randn(4 * 50000, device=dev, generator=torch.Generator(device=dev).manual_seed(r + 40)) for r in range(size)]
+        torch.testing.assert_close(out16.float(), (torch.stack(allv).double().sum(0) / size).float(), rtol=1e-2, atol=2e-2)
+        per = 16 * 4099
+        src = _vals(rank, per, torch.int32, seed=23).to(dev)
+        dst = torch.zeros(per * size, dtype=torch.int32, device=dev)
+        team.allgather(src, dst, stream=stream, alg=D).run().finalize()
+        assert torch.equal(dst.cpu(), torch.cat([_vals(r, per, torch.int32, seed=23) for r in range(size)]))
+        src = (torch.arange(per * size, dtype=torch.float32) + rank * 1e6).to(dev)
+        dst = torch.zeros_like(src)
+        req = team.alltoall(src, dst, alg=D, stream=stream)
+        for _ in range(2):
+            req.post().wait()
+        req.finalize()
+        want = torch.cat([(torch.arange(per * size, dtype=torch.float32) + r * 1e6)[rank * per:(rank + 1) * per]
+                          for r in range(size)])
+        assert torch.equal(dst.cpu(), want)
+        src = _vals(rank, 4 * 1237 * size, torch.float32, seed=25).to(dev)
+        dst = torch.zeros(4 * 1237, device=dev)
+        team.reduce_scatter(src, dst, stream=stream, alg=D).run().finalize()
+        full = torch.stack([_vals(r, 4 * 1237 * size, torch.float32, seed=25) for r in range(size)]).sum(0)
+        assert torch.equal(dst.cpu(), full[rank * 4 * 1237:(rank + 1) * 4 * 1237])
+        out["direct"] = "ok"
         # stream-ordered barrier served by the nvlink team
         assert team.coll_tl(K.BARRIER, K.MEM_HOST) == K.TL_NVLINK
         for _ in range(3):

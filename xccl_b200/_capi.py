@@ -49,7 +49,7 @@ MEM_MAP_ADDRESS, MEM_MAP_LENGTH, MEM_MAP_ROOT = 1, 2, 4
 IN_PLACE = 1
 
 HOST_ALG_LINEAR, HOST_ALG_KNOMIAL, HOST_ALG_SRA = 0, 1, 2
-NVLINK_ALG_AUTO, NVLINK_ALG_ONE_SHOT, NVLINK_ALG_TWO_SHOT, NVLINK_ALG_NVLS = 0, 1, 2, 3
+NVLINK_ALG_AUTO, NVLINK_ALG_ONE_SHOT, NVLINK_ALG_TWO_SHOT, NVLINK_ALG_NVLS, NVLINK_ALG_DIRECT = 0, 1, 2, 3, 4
 
 
 # ---------------------------------------------------------------- structures

@@ -319,9 +319,9 @@ class Team:
         a.root = root
         return Request(self, a, tuple(keep))
 
-    def allgather(self, src: Any, dst: Any, stream: Any = None) -> Request:
+    def allgather(self, src: Any, dst: Any, stream: Any = None, alg: Optional[int] = None) -> Request:
         keep: list = []
-        a = self._args(K.ALLGATHER, src, dst, nbytes_of(dst), None, stream, keep)
+        a = self._args(K.ALLGATHER, src, dst, nbytes_of(dst), alg, stream, keep)
         return Request(self, a, tuple(keep))
 
     def alltoall(self, src: Any, dst: Any, bytes_per_peer: Optional[int] = None, alg: Optional[int] = None,

@@ -45,7 +45,9 @@ def _rank_main(rank: int, size: int, job: str, opts: dict) -> list:
     lib = Lib()
     results = []
     impls = []
-    cfg = {K.TL_NVLINK: {"WORKSPACE_SIZE": opts["workspace"], "MAX_BLOCKS": str(opts["max_blocks"])}}
+    # DIRECT_MIN out of reach: the sweep names every algorithm itself ("direct" rows force it)
+    cfg = {K.TL_NVLINK: {"WORKSPACE_SIZE": opts["workspace"], "MAX_BLOCKS": str(opts["max_blocks"]),
+                         "DIRECT_MIN": "1024g"}}
     ctx_n = Context(lib, oob, tls=K.TL_NVLINK | K.TL_UCX, config=cfg)
     team_n = Team(ctx_n)
     impls.append(("nvlink", team_n))
@@ -76,19 +78,19 @@ def _rank_main(rank: int, size: int, job: str, opts: dict) -> list:
             per = max(nbytes // n // es, 1)
             src = torch.randn(per * n, device=dev).to(dtype)
             dst = torch.empty_like(src)
-            req = team.alltoall(src, dst, stream=sh)
+            req = team.alltoall(src, dst, stream=sh, alg=alg)
             factor, total = (n - 1) / n, per * n * es
         elif coll == "allgather":
             per = max(nbytes // n // es, 1)
             src = torch.randn(per, device=dev).to(dtype)
             dst = torch.empty(per * n, device=dev, dtype=dtype)
-            req = team.allgather(src, dst, stream=sh)
+            req = team.allgather(src, dst, stream=sh, alg=alg)
             factor, total = (n - 1) / n, per * n * es
         elif coll == "reduce_scatter":
             per = max(nbytes // n // es, 1)
             src = torch.randn(per * n, device=dev).to(dtype)
             dst = torch.empty(per, device=dev, dtype=dtype)
-            req = team.reduce_scatter(src, dst, stream=sh, alg=None)
+            req = team.reduce_scatter(src, dst, stream=sh, alg=alg)
             factor, total = (n - 1) / n, per * n * es
         elif coll == "bcast":
             buf = torch.randn(max(nbytes // es, 1), device=dev).to(dtype)
@@ -142,6 +144,9 @@ def _rank_main(rank: int, size: int, job: str, opts: dict) -> list:
                     cases.append(("nvlink", team_n, K.NVLINK_ALG_NVLS, "multicast"))
                 else:
                     cases.append(("nvlink", team_n, None, "pull"))
+                if coll in ("allreduce", "alltoall", "allgather", "reduce_scatter") and nbytes >= (1 << 20):
+                    # zero-copy kernels on buffers registered with the peers when the request is initialised
+                    cases.append(("nvlink", team_n, K.NVLINK_ALG_DIRECT, "direct"))
                 cases.append(("nccl", team_c, None, "nccl"))
                 for impl, team, alg, name in cases:
                     r = run_case(coll, impl, team, nbytes, dtype, alg, name)

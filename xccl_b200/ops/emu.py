@@ -60,17 +60,17 @@ class EmuWorld:
     def reduce(self, srcs, dsts, root, op=K.OP_SUM, scale=1.0) -> None:
         self._run(K.REDUCE, srcs, dsts, count=srcs[0].numel(), dt=dtype_of(srcs[0]), op=op, root=root, scale=scale)
 
-    def reduce_scatter(self, srcs, dsts, op=K.OP_SUM) -> None:
-        self._run(K.REDUCE_SCATTER, srcs, dsts, count=dsts[0].numel(), dt=dtype_of(srcs[0]), op=op)
+    def reduce_scatter(self, srcs, dsts, op=K.OP_SUM, alg=0) -> None:
+        self._run(K.REDUCE_SCATTER, srcs, dsts, count=dsts[0].numel(), dt=dtype_of(srcs[0]), op=op, alg=alg)
 
     def bcast(self, srcs, dsts, root) -> None:
         self._run(K.BCAST, srcs, dsts, length=dsts[0].numel() * dsts[0].element_size(), root=root)
 
-    def allgather(self, srcs, dsts) -> None:
-        self._run(K.ALLGATHER, srcs, dsts, length=dsts[0].numel() * dsts[0].element_size())
+    def allgather(self, srcs, dsts, alg=0) -> None:
+        self._run(K.ALLGATHER, srcs, dsts, length=dsts[0].numel() * dsts[0].element_size(), alg=alg)
 
-    def alltoall(self, srcs, dsts) -> None:
-        self._run(K.ALLTOALL, srcs, dsts, length=dsts[0].numel() * dsts[0].element_size() // self.n)
+    def alltoall(self, srcs, dsts, alg=0) -> None:
+        self._run(K.ALLTOALL, srcs, dsts, length=dsts[0].numel() * dsts[0].element_size() // self.n, alg=alg)
 
     def alltoallv(self, srcs, dsts, metas, max_src_bytes) -> None:
         self._run(K.ALLTOALLV, srcs, dsts, vmeta=metas, max_src_bytes=max_src_bytes, es=srcs[0].element_size())
