@@ -282,7 +282,7 @@ xccl_status_t NcclReq::start(cudaStream_t s)
 
 xccl_status_t NcclReq::post()
 {
-    if (in_flight_) return XCCL_ERR_NO_RESOURCE;
+    // re-posting a request that is still in flight is allowed: the stream orders the posts
     cudaStream_t s = team_->stream;
     if ((args_.field_mask & XCCL_COLL_OP_ARGS_FIELD_STREAM) && args_.stream.stream != nullptr) {
         s = *(cudaStream_t *)args_.stream.stream;

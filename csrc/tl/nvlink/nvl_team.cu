@@ -311,7 +311,8 @@ xccl_status_t NvlReq::register_buffers(void *src, void *dst, size_t src_bytes, s
 
 xccl_status_t NvlReq::post()
 {
-    if (in_flight_) return XCCL_ERR_NO_RESOURCE;
+    // A request that is still in flight may be posted again: posts of one request are ordered by its stream, and
+    // test / wait then refer to the latest post (the reference's NCCL team behaves the same way).
     if (team_->poisoned) return XCCL_ERR_NO_PROGRESS;
     const auto  &bi = args_.buffer_info;
     cudaStream_t s  = team_->stream;

@@ -3,8 +3,8 @@ NCCL team, one process per GPU.
 
     python -m xccl_b200.bench.collectives --gpus 8 [--colls allreduce,alltoall] [--max-bytes 1g]
 
-Every number is device time (CUDA events around `iters` back-to-back posts on one stream),
-the maximum over ranks, after warm-up. Bus bandwidth uses the usual factors: allreduce
+Every number is device time (CUDA events around `iters` back-to-back posts of one persistent request
+on one stream, no host wait between posts), the maximum over ranks, after warm-up. Bus bandwidth uses the usual factors: allreduce
 2(N-1)/N * S / t, allgather / reduce-scatter / alltoall (N-1)/N * S / t, bcast S / t.
 Allreduce runs with the fused 1/N post-scale, as gradient averaging would.
 Output: one JSON object per line on stdout (rank 0) and, with --table, a selection table
@@ -110,12 +110,10 @@ def _rank_main(rank: int, size: int, job: str, opts: dict) -> list:
             with torch.cuda.stream(stream):
                 e0.record(stream)
                 for _ in range(iters):
+                    # posts of one request are ordered by its stream: no host wait between them, so the
+                    # number is device time per operation, not launch-and-synchronise time
                     req.post()
-                    # completion is stream-ordered; the host only needs the event of the LAST post.
-                    # wait() is a cudaEventSynchronize on that event, the kernels stay back to back
-                    # because the next launch is already enqueued by the time it returns for small
-                    # sizes, and dominated by device time for large ones.
-                    req.wait()
+                req.wait()
                 e1.record(stream)
             stream.synchronize()
             ms = e0.elapsed_time(e1) / iters
