@@ -54,5 +54,6 @@ struct xccl_team {
     size_t                                     n_posted = 0;
     bool                                       created  = false;
     xccl_status_t                              failed   = XCCL_OK;
+    double                                     t_posted = 0.0;  // steady-clock seconds of xccl_team_create_post
     int coll_team_id[XCCL_COLL_LAST][XCCL_MEMORY_TYPE_LAST];
 };

@@ -134,6 +134,16 @@ xccl_status_t xccl_team_create_test(xccl_team_h team)
     if (team == nullptr) return XCCL_ERR_INVALID_PARAM;
     if (team->created) return XCCL_OK;
     if (team->failed != XCCL_OK) return team->failed;
+    // Creation is non-blocking, but not open-ended: a member that never joins must not leave the others
+    // polling forever. The deadline is the same as for a blocking out-of-band exchange (XCCL_OOB_TIMEOUT).
+    auto now_s = [] { return std::chrono::duration<double>(std::chrono::steady_clock::now().time_since_epoch()).count(); };
+    if (team->t_posted == 0.0) team->t_posted = now_s();
+    const double limit = global_state().opts.real("OOB_TIMEOUT");
+    if (limit > 0 && now_s() - team->t_posted > limit) {
+        team->failed = XCCL_ERR_TIMED_OUT;
+        xccl_error("team creation did not finish within %.1f s (a member never joined?)", limit);
+        return team->failed;
+    }
     if (!team->tl_teams.empty()) {
         TlTeam       *last = team->tl_teams.back().get();
         xccl_status_t st   = last->create_test();
