@@ -169,10 +169,14 @@ def load() -> C.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    if not _LIB_PATH.exists():
+    path = _LIB_PATH
+    alt = os.environ.get("XCCL_B200_LIB")  # e.g. the sanitizer build, xccl_b200/lib/libxccl_address.so
+    if alt:
+        path = Path(alt)
+    elif not _LIB_PATH.exists():
         from . import build as _build
         _build.build_native()
-    _lib = C.CDLL(str(_LIB_PATH), mode=C.RTLD_GLOBAL)
+    _lib = C.CDLL(str(path), mode=C.RTLD_GLOBAL)
     _declare(_lib)
     return _lib
 

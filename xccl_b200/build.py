@@ -55,31 +55,41 @@ def _sources() -> list[Path]:
     return out
 
 
-def _obj_for(src: Path) -> Path:
+def _obj_for(src: Path, sanitize: str | None = None) -> Path:
     rel = src.relative_to(CSRC)
-    return OBJ_DIR / (str(rel).replace("/", "__") + ".o")
+    base = OBJ_DIR if not sanitize else OBJ_DIR.parent / f"obj-{sanitize}"
+    return base / (str(rel).replace("/", "__") + ".o")
 
 
-def _compile(src: Path, obj: Path, verbose: bool, ptxas_v: bool) -> tuple[Path, int, str]:
+def _compile(src: Path, obj: Path, verbose: bool, ptxas_v: bool, sanitize: str | None = None) -> tuple[Path, int, str]:
+    san = [f"-fsanitize={sanitize}", "-fno-omit-frame-pointer"] if sanitize else []
     if src.suffix == ".cu":
         cmd = [NVCC, *NVCC_FLAGS, *COMMON_INC, "-c", str(src), "-o", str(obj)]
+        for f in san:
+            cmd[1:1] = ["-Xcompiler", f]
         if ptxas_v:
             cmd[1:1] = ["-Xptxas", "-v"]
     else:
-        cmd = [CXX, *CXX_FLAGS, *COMMON_INC, *_cuda_include(), "-c", str(src), "-o", str(obj)]
+        cmd = [CXX, *CXX_FLAGS, *san, *COMMON_INC, *_cuda_include(), "-c", str(src), "-o", str(obj)]
     if verbose:
         print(" ".join(cmd), flush=True)
     r = subprocess.run(cmd, capture_output=True, text=True)
     return src, r.returncode, (r.stdout + r.stderr)
 
 
-def build_native(force: bool = False, verbose: bool = False, ptxas_v: bool = False, jobs: int | None = None) -> Path:
+def build_native(force: bool = False, verbose: bool = False, ptxas_v: bool = False, jobs: int | None = None,
+                 sanitize: str | None = None) -> Path:
+    """sanitize = "address" or "thread": host code (and the host side of the .cu files) is compiled with that
+    sanitizer into xccl_b200/lib/libxccl_<sanitize>.so; run the CPU tests on it with
+    ``LD_PRELOAD=$(gcc -print-file-name=libasan.so) XCCL_B200_LIB=.../libxccl_address.so python -m pytest ...``."""
     OUT_DIR.mkdir(parents=True, exist_ok=True)
     OBJ_DIR.mkdir(parents=True, exist_ok=True)
+    if sanitize:
+        (OBJ_DIR.parent / f"obj-{sanitize}").mkdir(parents=True, exist_ok=True)
     hdr = _newest_header()
     todo, objs = [], []
     for src in _sources():
-        obj = _obj_for(src)
+        obj = _obj_for(src, sanitize)
         objs.append(obj)
         stale = force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, hdr)
         if stale:
@@ -87,7 +97,7 @@ def build_native(force: bool = False, verbose: bool = False, ptxas_v: bool = Fal
     failed = False
     if todo:
         with cf.ThreadPoolExecutor(max_workers=jobs or os.cpu_count() or 4) as ex:
-            futs = [ex.submit(_compile, s, o, verbose, ptxas_v) for s, o in todo]
+            futs = [ex.submit(_compile, s, o, verbose, ptxas_v, sanitize) for s, o in todo]
             for f in cf.as_completed(futs):
                 src, rc, log = f.result()
                 if rc != 0:
@@ -97,10 +107,12 @@ def build_native(force: bool = False, verbose: bool = False, ptxas_v: bool = Fal
                     print(f"--- {src.relative_to(ROOT)}\n{log}", flush=True)
     if failed:
         raise RuntimeError("native build failed")
-    lib = OUT_DIR / "libxccl.so"
+    lib = OUT_DIR / ("libxccl.so" if not sanitize else f"libxccl_{sanitize}.so")
     if todo or not lib.exists():
         cmd = [NVCC, "-shared", *ARCH_FLAGS, "-o", str(lib), *map(str, objs), "-lpthread", "-ldl", "-lrt",
                "-cudart", "static"]
+        if sanitize:
+            cmd += ["-Xcompiler", f"-fsanitize={sanitize}"]
         if verbose:
             print(" ".join(cmd), flush=True)
         r = subprocess.run(cmd, capture_output=True, text=True)
@@ -149,8 +161,10 @@ def main() -> None:
     ap.add_argument("--ptxas-v", action="store_true", help="print registers / spills / shared memory per kernel")
     ap.add_argument("--torch", action="store_true", help="also build the c10d backend extension")
     ap.add_argument("-j", type=int, default=None)
+    ap.add_argument("--sanitize", choices=["address", "thread"], default=None,
+                    help="build libxccl_<sanitizer>.so with the host code instrumented (CPU tests only)")
     a = ap.parse_args()
-    lib = build_native(a.force, a.verbose, a.ptxas_v, a.j)
+    lib = build_native(a.force, a.verbose, a.ptxas_v, a.j, a.sanitize)
     print(f"built {lib}")
     if a.torch:
         t = build_torch_ext(a.force, a.verbose)
