@@ -2,10 +2,43 @@
 // Reference behaviour: src/core/xccl_collective.c:16-92, src/core/xccl_mm.c:3-72.
 #include <chrono>
 
+#include <nvtx3/nvToolsExt.h>  // header-only: resolves to no-ops unless a profiler injects itself
+
 #include "../utils/mem.h"
 #include "core.h"
 
 using namespace xccl;
+
+namespace {
+// XCCL_NVTX=y: ranges "xccl:<collective>:post" / ":wait" around the calls, so a timeline shows which
+// collective a kernel or a host wait belongs to. Read once.
+bool nvtx_on()
+{
+    static int on = -1;
+    if (on < 0) on = global_state().opts.flag("NVTX") ? 1 : 0;
+    return on == 1;
+}
+const char *coll_name(int t)
+{
+    static const char *names[] = {"barrier", "bcast", "allreduce", "reduce", "alltoall", "alltoallv", "allgather",
+                                  "fanin", "fanout", "fanout_get", "reduce_scatter"};
+    return (t >= 0 && t < (int)(sizeof(names) / sizeof(names[0]))) ? names[t] : "collective";
+}
+struct NvtxRange {
+    bool on;
+    NvtxRange(const xccl_coll_req *r, const char *what) : on(nvtx_on())
+    {
+        if (!on) return;
+        char buf[64];
+        std::snprintf(buf, sizeof(buf), "xccl:%s:%s", coll_name(r != nullptr ? r->coll_type : -1), what);
+        nvtxRangePushA(buf);
+    }
+    ~NvtxRange()
+    {
+        if (on) nvtxRangePop();
+    }
+};
+}  // namespace
 
 xccl_status_t xccl_coll_req::wait()
 {
@@ -100,18 +133,23 @@ xccl_status_t xccl_collective_init(xccl_coll_op_args_t *args, xccl_coll_req_h *r
     xccl_status_t  st  = tt->collective_init(*args, mem, &req);
     if (st != XCCL_OK) return st;
     req->core_team = team;
+    req->coll_type = (int)args->coll_type;
     *request       = req;
     return XCCL_OK;
 }
 
 xccl_status_t xccl_collective_post(xccl_coll_req_h request)
 {
-    return request != nullptr ? request->post() : XCCL_ERR_INVALID_PARAM;
+    if (request == nullptr) return XCCL_ERR_INVALID_PARAM;
+    NvtxRange r(request, "post");
+    return request->post();
 }
 
 xccl_status_t xccl_collective_wait(xccl_coll_req_h request)
 {
-    return request != nullptr ? request->wait() : XCCL_ERR_INVALID_PARAM;
+    if (request == nullptr) return XCCL_ERR_INVALID_PARAM;
+    NvtxRange r(request, "wait");
+    return request->wait();
 }
 
 xccl_status_t xccl_collective_test(xccl_coll_req_h request)

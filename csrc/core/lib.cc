@@ -23,6 +23,7 @@ static const std::vector<OptField> kGlobalFields = {
     {"LF_TASKS_QUEUE_SIZE", "8", "Slots per pool of the multi-thread progress queue (fixed at 8)", OptType::UINT},
     {"OOB_TIMEOUT", "120", "Seconds a blocking out-of-band exchange may take before it fails", OptType::DOUBLE},
     {"WAIT_TIMEOUT", "600", "Seconds xccl_collective_wait may spin before it returns XCCL_ERR_TIMED_OUT", OptType::DOUBLE},
+    {"NVTX", "n", "Wrap xccl_collective_post and xccl_collective_wait in NVTX ranges named after the collective", OptType::BOOL},
 };
 
 GlobalState &global_state()

@@ -27,6 +27,7 @@ struct xccl_coll_req {
     virtual xccl_status_t finalize() { return XCCL_OK; }  // refuse (INPROGRESS / error) when in flight
     virtual double        elapsed_us() { return -1.0; }
     xccl_team *core_team = nullptr;
+    int        coll_type = -1;   // xccl_collective_type_t, set by xccl_collective_init (tracing)
 };
 
 struct xccl_mem_handle {

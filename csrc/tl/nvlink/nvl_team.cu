@@ -31,7 +31,9 @@ struct NvlCfg {
     size_t nvls_min      = 256u << 10;
     size_t bcast_mc_min  = 0;
     size_t direct_min    = 32u << 20;   // messages from this size register their buffers and skip the workspace
+    bool   direct_min_set = false;      // given explicitly: a tuning file does not override it
     bool   direct        = true;
+    std::string tuning_file;
     int    max_blocks    = 64;
     int    threads       = 512;
     double wait_timeout_ms = 5000.0;
@@ -39,6 +41,34 @@ struct NvlCfg {
 };
 
 class NvlTeam;
+
+}  // namespace
+
+// Reads the line of a tuning file that matches `team_size` (`team_size one_shot_max nvls_min [direct_min]`, `#`
+// starts a comment, -1 keeps the built-in value; the last matching line wins). Returns the number of values set.
+extern "C" int xccl_nvlink_tuning_lookup(const char *path, int team_size, long long *one_shot_max, long long *nvls_min,
+                                         long long *direct_min)
+{
+    if (path == nullptr || path[0] == '\0') return 0;
+    FILE *f = std::fopen(path, "r");
+    if (f == nullptr) return 0;
+    char line[256];
+    int  set = 0;
+    while (std::fgets(line, sizeof(line), f) != nullptr) {
+        if (line[0] == '#') continue;
+        long long n = 0, a = -1, b = -1, c = -1;
+        int       got = std::sscanf(line, "%lld %lld %lld %lld", &n, &a, &b, &c);
+        if (got < 3 || n != team_size) continue;
+        set = 0;
+        if (a >= 0 && one_shot_max != nullptr) { *one_shot_max = a; set++; }
+        if (b >= 0 && nvls_min != nullptr) { *nvls_min = b; set++; }
+        if (got >= 4 && c >= 0 && direct_min != nullptr) { *direct_min = c; set++; }
+    }
+    std::fclose(f);
+    return set;
+}
+
+namespace {
 
 class NvlReq final : public xccl_coll_req {
 public:
@@ -119,6 +149,17 @@ public:
         world.ws_bytes  = cfg.ws_bytes;
         // crossover points measured on NVSwitch systems: with 8 ranks the one-shot kernel's all-to-all
         // traffic loses to the two-step kernels earlier than with 4 or fewer
+        if (!cfg.tuning_file.empty()) {
+            // thresholds measured on this machine by `python -m xccl_b200.bench.collectives --table FILE`
+            long long a = -1, b = -1, c = -1;
+            if (xccl_nvlink_tuning_lookup(cfg.tuning_file.c_str(), size, &a, &b, &c) > 0) {
+                if (a >= 0 && cfg.one_shot_max == 0) cfg.one_shot_max = (size_t)a;
+                if (b >= 0 && cfg.nvls_min == 0) cfg.nvls_min = (size_t)b;
+                if (c >= 0 && !cfg.direct_min_set) cfg.direct_min = (size_t)c;
+                tl_info(tl_, "nvlink team: thresholds of %d ranks from %s: one-shot <= %lld, NVLS >= %lld, direct >= %lld",
+                        size, cfg.tuning_file.c_str(), a, b, c);
+            }
+        }
         if (cfg.one_shot_max == 0) cfg.one_shot_max = size >= 8 ? (256u << 10) : (1u << 20);
         if (cfg.nvls_min == 0) cfg.nvls_min = size >= 8 ? (1u << 20) : (128u << 10);
         world.wait_budget_ns = (unsigned long long)(cfg.wait_timeout_ms * 1e6);
@@ -512,7 +553,8 @@ public:
             {"NVLS_MIN", "0", "Allreduce messages from this size use NVLS when available (0: by team size, 1m from 8 ranks, else 128k)", OptType::MEMUNITS},
             {"BCAST_MC_MIN", "0", "Broadcasts from this size go through the NVSwitch multicast mapping when available", OptType::MEMUNITS},
             {"DIRECT", "y", "Register the buffers of large messages with the peers (CUDA IPC) and run zero-copy kernels on them", OptType::BOOL},
-            {"DIRECT_MIN", "32m", "Messages from this size use the direct (zero-copy) kernels", OptType::MEMUNITS},
+            {"DIRECT_MIN", "0", "Messages from this size use the direct (zero-copy) kernels (0: tuning file, else 32m)", OptType::MEMUNITS},
+            {"TUNING_FILE", "", "Measured thresholds, lines of `team_size one_shot_max nvls_min direct_min` (see bench/collectives.py --table)", OptType::STRING},
             {"MAX_BLOCKS", "128", "Upper bound of thread blocks per collective kernel (at most 128)", OptType::UINT},
             {"THREADS", "512", "Threads per block of the collective kernels", OptType::UINT},
             {"WAIT_TIMEOUT_MS", "5000", "Budget of every device-side wait for a peer", OptType::DOUBLE},
@@ -545,6 +587,9 @@ public:
         c.nvls_min        = (size_t)cfg.num("NVLS_MIN");
         c.bcast_mc_min    = (size_t)cfg.num("BCAST_MC_MIN");
         c.direct_min      = (size_t)cfg.num("DIRECT_MIN");
+        c.direct_min_set  = c.direct_min != 0;
+        if (!c.direct_min_set) c.direct_min = 32u << 20;
+        c.tuning_file     = cfg.str("TUNING_FILE");
         c.direct          = cfg.flag("DIRECT");
         c.max_blocks      = std::max(1, std::min((int)cfg.num("MAX_BLOCKS"), kMaxBlocks));
         c.threads         = std::max(32, std::min((int)cfg.num("THREADS"), 512)) / 32 * 32;

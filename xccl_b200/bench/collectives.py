@@ -156,7 +156,9 @@ def _rank_main(rank: int, size: int, job: str, opts: dict) -> list:
 
 
 def selection_table(rows: list[dict]) -> dict:
-    """Per team size: the largest size where one-shot is fastest and the smallest where NVLS is."""
+    """Per team size: the largest size where one-shot is fastest, the smallest where NVLS is, and the smallest
+    from which the direct (registered-buffer) kernel stays fastest. The file written with --table is what
+    XCCL_TEAM_NVLINK_TUNING_FILE reads: lines of `team_size one_shot_max nvls_min direct_min`, -1 = keep the default."""
     out = {}
     ar = [r for r in rows if r.get("coll") == "allreduce" and r.get("impl") == "nvlink" and "us" in r]
     for n in sorted({r["gpus"] for r in ar}):
@@ -164,14 +166,18 @@ def selection_table(rows: list[dict]) -> dict:
         for r in ar:
             if r["gpus"] == n and r["dtype"] == "float32":
                 by_size.setdefault(r["bytes"], {})[r["alg"]] = r["us"]
-        one_shot_max, nvls_min = 0, None
+        one_shot_max, nvls_min, direct_min = 0, None, None
         for s in sorted(by_size):
             best = min(by_size[s], key=by_size[s].get)
             if best == "one_shot":
                 one_shot_max = s
             if best == "nvls" and nvls_min is None:
                 nvls_min = s
-        out[n] = {"one_shot_max": one_shot_max, "nvls_min": nvls_min}
+            if best == "direct":
+                direct_min = s if direct_min is None else direct_min
+            elif "direct" in by_size[s]:
+                direct_min = None          # something else won again at a larger size
+        out[n] = {"one_shot_max": one_shot_max, "nvls_min": nvls_min, "direct_min": direct_min}
     return out
 
 
@@ -196,7 +202,8 @@ def main() -> None:
         tab = selection_table(res[0])
         with open(a.table, "a") as f:
             for n, t in tab.items():
-                f.write(f"{n} {t['one_shot_max']} {t['nvls_min'] if t['nvls_min'] is not None else -1}\n")
+                f.write(f"{n} {t['one_shot_max']} {t['nvls_min'] if t['nvls_min'] is not None else -1} "
+                        f"{t['direct_min'] if t['direct_min'] is not None else -1}\n")
         print(json.dumps({"selection_table": tab}), file=sys.stderr)
 
 
