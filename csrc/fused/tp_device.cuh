@@ -135,6 +135,13 @@ __device__ void copy_cta_loop(const GemmParams &p, int rank, int local, int copy
         for (int s = 0; s < kCopySlots; s++) mbar_init(bars + 8u * s, 1);
         mbar_fence_init();
     }
+    // my own shard may still be arriving from the host: the peers are told to read it only when all of it is here
+    if (p.in_ready[local] != nullptr && threadIdx.x == 0) {
+        const int chunks = (p.M / p.tp_size + p.in_rows_per_flag - 1) / p.in_rows_per_flag;
+        for (int c = 0; c < chunks; c++) {
+            if (!wait_counter(p.in_ready[local] + c, p.in_target, true, ab, 9)) break;
+        }
+    }
     // peers must have published their shards before we read them: barrier among the copy CTAs
     uint32_t *epoch_slot = p.pad[rank] + nvl::kPadEpochOff + copy_idx;
     uint32_t  epoch      = *epoch_slot + 1;

@@ -132,6 +132,13 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
                     ok = wait_counter(p.ready[local] + tl.mb, p.seq * n_copy, false, ab, 1);
                     asm volatile("fence.proxy.async.global;" ::: "memory");
                     if (!ok) break;
+                } else if (p.in_ready[local] != nullptr && p.comm != COMM_REDUCE_SCATTER_C) {
+                    // local rows that the copy engine is still bringing in from the host
+                    const int shard_row0 = (p.comm == COMM_ALLGATHER_A) ? rank * (p.M / p.tp_size) : 0;
+                    const int last_row   = min(tl.mb * kBM + kBM, p.M) - 1 - shard_row0;
+                    ok = wait_counter(p.in_ready[local] + last_row / p.in_rows_per_flag, p.in_target, true, ab, 8);
+                    asm volatile("fence.proxy.async.global;" ::: "memory");
+                    if (!ok) break;
                 }
                 for (int kb = 0; kb < kblocks; kb++) {
                     if (sync_ctr != nullptr && (kb == 0 || (p.sync_kblocks > 0 && kb % p.sync_kblocks == 0))) {

@@ -58,6 +58,13 @@ struct GemmParams {
     // allgather mode: xg[r] is rank r's gathered A buffer [M,K] as mapped here; shard s of rank s is valid on entry
     __nv_bfloat16 *xg[kMaxTpRanks];       // indexed by TEAM rank
     uint32_t      *ready[kMaxTpRanks];    // per LOCAL rank: one flag per 128-row block of A, local memory
+    // Input rows that are still arriving from the host (optional): the local shard was split into chunks of
+    // in_rows_per_flag rows; a stream-ordered 32-bit write sets in_ready[chunk] = in_target after each chunk's
+    // host->device copy. Tiles of local rows wait for their chunk; the copy CTAs wait for all chunks before
+    // they tell the peers that this rank's shard may be read. Null = the rows are there when the kernel starts.
+    const uint32_t *in_ready[kMaxTpRanks];   // per LOCAL rank
+    uint32_t        in_target;
+    int             in_rows_per_flag;
     // block-scaled fp8 kernels (a_bytes == 1): A is e4m3 with one fp32 scale per row per 128 columns
     int            a_bytes;                // bytes per element of A in xg: 0 or 2 = bf16, 1 = fp8
     float         *sg[kMaxTpRanks];        // TEAM rank: scales of A, [M, K/128]; gathered together with xg in allgather mode

@@ -34,6 +34,12 @@ struct TpWorkspace {
     size_t    off_xg = 0, off_part = 0, total = 0;
     uint32_t  seq_ag = 0, seq_rs = 0, rs_count[2] = {0, 0};
     int       copy_ctas = 16;
+    // input rows arriving from the host while the allgather->GEMM kernel already runs
+    uint32_t   *in_flags[kMaxTpRanks] = {nullptr};  // per LOCAL rank: one word per chunk of in_rows rows
+    uint32_t    in_seq = 0;
+    bool        in_active = false;
+    int         in_rows = 256;
+    cudaEvent_t in_consumed = nullptr;
 
     uint32_t      *pad(int r) const { return (uint32_t *)base[r]; }
     __nv_bfloat16 *xg(int r) const { return (__nv_bfloat16 *)(base[r] + off_xg); }
@@ -148,6 +154,15 @@ xccl_status_t xccl_tp_ws_create(const xccl_oob_collectives_t *oob, int emu_ranks
         cudaMemset(p, 0, (size_t)tiles_m * 4);
         w->allocs.push_back(p);
         w->ready[l] = (uint32_t *)p;
+        void  *f = nullptr;
+        size_t chunks = (size_t)(M / w->tp + w->in_rows - 1) / w->in_rows;
+        if (cudaMalloc(&f, chunks * 4) != cudaSuccess) {
+            st = XCCL_ERR_NO_MEMORY;
+            break;
+        }
+        cudaMemset(f, 0, chunks * 4);
+        w->allocs.push_back(f);
+        w->in_flags[l] = (uint32_t *)f;
     }
     if (st == XCCL_OK) {
         void *p = nullptr;
@@ -173,6 +188,7 @@ void xccl_tp_ws_destroy(xccl_tp_ws_h w)
     if (w == nullptr) return;
     cudaDeviceSynchronize();
     for (void *p : w->allocs) cudaFree(p);
+    if (w->in_consumed != nullptr) cudaEventDestroy(w->in_consumed);
     delete w->region;
     delete w;
 }
@@ -239,8 +255,42 @@ xccl_status_t xccl_tp_ag_gemm_swiglu(xccl_tp_ws_h w, const void *const *Wg, cons
         if (st != XCCL_OK) return st;
         st = make_tensor_map_2d(&l.tmB1[i], Wu[i], (uint64_t)F_local, (uint64_t)w->K, (uint64_t)w->K, kBN / 2);
         if (st != XCCL_OK) return st;
+        if (w->in_active) p.in_ready[i] = w->in_flags[i];
     }
-    return launch_gemm(p, l, (cudaStream_t)stream);
+    if (w->in_active) {
+        p.in_target        = w->in_seq;
+        p.in_rows_per_flag = w->in_rows;
+    }
+    xccl_status_t lst = launch_gemm(p, l, (cudaStream_t)stream);
+    if (w->in_active && lst == XCCL_OK) {
+        // the next host->device copy into the shard may start once this kernel has consumed it
+        if (w->in_consumed == nullptr) XCCL_CUDA_CHECK(cudaEventCreateWithFlags(&w->in_consumed, cudaEventDisableTiming));
+        XCCL_CUDA_CHECK(cudaEventRecord(w->in_consumed, (cudaStream_t)stream));
+    }
+    w->in_active = false;
+    return lst;
+}
+
+xccl_status_t xccl_tp_h2d_begin(xccl_tp_ws_h w, const void *const *host_x, void *copy_stream)
+{
+    if (w == nullptr || host_x == nullptr) return XCCL_ERR_INVALID_PARAM;
+    XCCL_DRIVER_FN(cuStreamWriteValue32);
+    cudaStream_t cs = (cudaStream_t)copy_stream;
+    if (w->in_consumed != nullptr) XCCL_CUDA_CHECK(cudaStreamWaitEvent(cs, w->in_consumed, 0));
+    w->in_seq++;
+    const size_t rows = (size_t)w->M / w->tp, row_bytes = (size_t)w->K * 2;
+    for (int i = 0; i < w->n_local; i++) {
+        char       *dst = (char *)xccl_tp_ws_x_shard(w, i);
+        const char *src = (const char *)host_x[i];
+        size_t      c   = 0;
+        for (size_t r0 = 0; r0 < rows; r0 += (size_t)w->in_rows, c++) {
+            const size_t n = std::min((size_t)w->in_rows, rows - r0);
+            XCCL_CUDA_CHECK(cudaMemcpyAsync(dst + r0 * row_bytes, src + r0 * row_bytes, n * row_bytes, cudaMemcpyHostToDevice, cs));
+            XCCL_CU_CHECK(cuStreamWriteValue32((CUstream)cs, (CUdeviceptr)(w->in_flags[i] + c), w->in_seq, 0));
+        }
+    }
+    w->in_active = true;
+    return XCCL_OK;
 }
 
 xccl_status_t xccl_tp_gemm_rs(xccl_tp_ws_h w, const void *const *Hin, const void *const *Wd, void *const *Yout,

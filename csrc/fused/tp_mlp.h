@@ -36,6 +36,11 @@ xccl_status_t xccl_tp_ag_gemm_swiglu(xccl_tp_ws_h ws, const void *const *Wg, con
 xccl_status_t xccl_tp_gemm_rs(xccl_tp_ws_h ws, const void *const *Hin, const void *const *Wd, void *const *Yout,
                               int F_local, void *stream);
 
+// Starts the host->device copy of this step's input shards (host_x[i]: pinned [M/tp, K] bf16 of local rank i) on
+// `copy_stream`, chunk by chunk, each chunk followed by a stream-ordered flag write. The NEXT xccl_tp_ag_gemm_swiglu
+// call (on its own stream, no event between the two) starts at once and consumes the rows as their chunks land, so
+// the copy hides behind the first tiles instead of preceding the kernel.
+xccl_status_t xccl_tp_h2d_begin(xccl_tp_ws_h ws, const void *const *host_x, void *copy_stream);
 
 // ---- block-scaled fp8 variants (e4m3 activations with 1 x 128 scales, e4m3 weights with 128 x 128 scales)
 // The fp8 rows and their scales live in the same gathered buffer as the bf16 rows ([M, K] bytes followed by

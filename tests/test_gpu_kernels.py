@@ -5,6 +5,8 @@ whose blockIdx.y is the rank); the real multi-process path has its own test modu
 """
 import ctypes as C
 
+import os
+
 import pytest
 import torch
 
@@ -362,6 +364,29 @@ def test_tp_mlp_end_to_end_from_pinned_host(dev):
         m = mlp.forward_from_host([x])
         mlp.check_error()
         assert m.device.type == "cpu" and torch.isfinite(m)
+    finally:
+        mlp.close()
+
+
+@pytest.mark.skipif(os.environ.get("XCCL_TEST_H2D_OVERLAP") != "1",
+                    reason="opt-in feature: set XCCL_TEST_H2D_OVERLAP=1 to run its test")
+@pytest.mark.parametrize("tp", [1, 2])
+def test_tp_mlp_input_arriving_from_host_overlaps_first_kernel(dev, tp, monkeypatch):
+    """The chunked host->device copy with stream-ordered flags: the kernel starts before the rows are there and
+    must produce the same output as the plain copy-then-launch path, step after step."""
+    from xccl_b200.models.tp_mlp import TpMlp, reference_forward_fp32
+    monkeypatch.setenv("XCCL_TP_H2D_OVERLAP", "1")
+    tokens, hidden, ffn = 1024, 512, 1024
+    mlp = TpMlp(tokens, hidden, ffn, tp=tp, emulate=(tp > 1))
+    try:
+        assert mlp.overlap_h2d
+        for it in range(3):
+            x = torch.randn(tokens, hidden, generator=torch.Generator().manual_seed(it)).to(torch.bfloat16)
+            pinned = [c.contiguous().pin_memory() for c in x.chunk(tp, 0)]
+            mlp.forward_from_host(pinned)
+            mlp.check_error()
+            want = reference_forward_fp32(x.to(dev), *_full_weights(mlp))
+            torch.testing.assert_close(torch.cat(mlp.y, 0).float(), want, rtol=3e-2, atol=3e-2)
     finally:
         mlp.close()
 

@@ -10,6 +10,7 @@ is the comparison point, not a fallback.
 """
 from __future__ import annotations
 
+import os
 from typing import Any, Optional
 
 import torch
@@ -48,6 +49,9 @@ class TpMlp:
         self.y = [torch.empty(tokens // tp, hidden, dtype=torch.bfloat16, device=self.device) for _ in ranks]
         self.x_shards = [self.ws.x_shard(i) for i in range(self.n_local)]
         self.launches = 0
+        # opt-in: overlap the host->device copy of the input with the first kernel (XCCL_TP_H2D_OVERLAP=1)
+        self.overlap_h2d = os.environ.get("XCCL_TP_H2D_OVERLAP", "0") == "1"
+        self._copy_stream = None
 
     def forward(self, x_shards: Optional[list] = None) -> list:
         """x_shards: one [tokens/tp, hidden] bf16 tensor per local rank, or None when the input was
@@ -63,8 +67,14 @@ class TpMlp:
     def forward_from_host(self, x_pinned: list) -> torch.Tensor:
         """End-to-end step: host->device copy of this step's input shards from pinned memory,
         the block, and a device->host read of a scalar metric of the result."""
-        for dst, src in zip(self.x_shards, x_pinned):
-            dst.copy_(src, non_blocking=True)
+        if self.overlap_h2d:
+            # the copy runs on its own stream in chunks; the first kernel starts at once and waits per chunk
+            if self._copy_stream is None:
+                self._copy_stream = torch.cuda.Stream()
+            self.ws.h2d_begin(x_pinned, self._copy_stream)
+        else:
+            for dst, src in zip(self.x_shards, x_pinned):
+                dst.copy_(src, non_blocking=True)
         y = self.forward()
         metric = y[0].float().square().mean()
         return metric.cpu()

@@ -22,6 +22,7 @@ K.optional("xccl_tp_ws_x_full", C.c_void_p, C.c_void_p, C.c_int)
 K.optional("xccl_tp_ws_error", C.c_uint32, C.c_void_p)
 K.optional("xccl_tp_ag_gemm_swiglu", C.c_int, C.c_void_p, _pp, _pp, _pp, C.c_int, C.c_void_p)
 K.optional("xccl_tp_gemm_rs", C.c_int, C.c_void_p, _pp, _pp, _pp, C.c_int, C.c_void_p)
+K.optional("xccl_tp_h2d_begin", C.c_int, C.c_void_p, _pp, C.c_void_p)
 K.optional("xccl_tp_quantize_rows", C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p)
 K.optional("xccl_tp_ws_x8_shard", C.c_void_p, C.c_void_p, C.c_int)
 K.optional("xccl_tp_ws_sx_shard", C.c_void_p, C.c_void_p, C.c_int)
@@ -115,6 +116,18 @@ class TpWorkspace:
                                       torch.cuda.current_stream().cuda_stream)
         if st != K.OK:
             raise XcclError(st, "xccl_tp_gemm_rs")
+
+    def h2d_begin(self, x_pinned: Sequence[torch.Tensor], copy_stream: "torch.cuda.Stream") -> None:
+        """Starts the chunked host->device copy of this step's input shards on `copy_stream`; the next
+        ``ag_gemm_swiglu`` consumes the rows as they land (no event between the two streams is needed)."""
+        arr = (C.c_void_p * len(x_pinned))()
+        for i, t in enumerate(x_pinned):
+            if t.dtype != torch.bfloat16 or not t.is_contiguous() or not t.is_pinned():
+                raise ValueError("expected contiguous pinned bf16 host tensors")
+            arr[i] = t.data_ptr()
+        st = K.load().xccl_tp_h2d_begin(self.h, arr, copy_stream.cuda_stream)
+        if st != K.OK:
+            raise XcclError(st, "xccl_tp_h2d_begin")
 
     # ---- block-scaled fp8 (the same buffers hold [M, K] e4m3 rows followed by [M, K/128] fp32 scales)
     def x8_shard(self, local_rank: int = 0) -> torch.Tensor:
