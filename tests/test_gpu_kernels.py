@@ -368,8 +368,6 @@ def test_tp_mlp_end_to_end_from_pinned_host(dev):
         mlp.close()
 
 
-@pytest.mark.skipif(os.environ.get("XCCL_TEST_H2D_OVERLAP") != "1",
-                    reason="opt-in feature: set XCCL_TEST_H2D_OVERLAP=1 to run its test")
 @pytest.mark.parametrize("tp", [1, 2])
 def test_tp_mlp_input_arriving_from_host_overlaps_first_kernel(dev, tp, monkeypatch):
     """The chunked host->device copy with stream-ordered flags: the kernel starts before the rows are there and
