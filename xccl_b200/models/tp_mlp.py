@@ -99,6 +99,7 @@ class TpMlpFp8(TpMlp):
 
     def __init__(self, *args, **kw):
         super().__init__(*args, **kw)
+        self.overlap_h2d = False   # the input is quantised by a kernel first: it is copied whole, then quantised
         from ..ops.gemm import quantize_weight_128x128
         from ..ops.tp import quantize_rows
         self._quantize_rows = quantize_rows
