@@ -2,7 +2,7 @@
 team from a read-only source tree into ``baseline/_ref/lib`` against the UCS stand-in headers of
 ``baseline/ucs_shim`` (the image has no UCX, MPI or autotools, so ``./configure`` cannot run).
 
-    python baseline/build_ref.py [--src /root/reference]
+    python baseline/build_ref.py [--src <checkout of openucx/xccl>]   (default: the directory `reference` beside this repository)
 
 Layout produced (what the reference's own plugin loader expects next to libxccl.so):
     baseline/_ref/lib/libxccl.so
@@ -74,6 +74,6 @@ def build(src: Path) -> Path:
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser(description=__doc__)
-    ap.add_argument("--src", default="/root/reference")
+    ap.add_argument("--src", default=str(HERE.parent.parent / "reference"))
     a = ap.parse_args()
     print(build(Path(a.src)))
