@@ -30,7 +30,7 @@ struct NvlCfg {
     size_t one_shot_max  = 128u << 10;
     size_t nvls_min      = 256u << 10;
     size_t bcast_mc_min  = 0;
-    size_t direct_min    = 32u << 20;   // messages from this size register their buffers and skip the workspace
+    size_t direct_min    = ~(size_t)0;  // messages from this size register their buffers and skip the workspace
     bool   direct_min_set = false;      // given explicitly: a tuning file does not override it
     bool   direct        = true;
     std::string tuning_file;
@@ -553,7 +553,7 @@ public:
             {"NVLS_MIN", "0", "Allreduce messages from this size use NVLS when available (0: by team size, 1m from 8 ranks, else 128k)", OptType::MEMUNITS},
             {"BCAST_MC_MIN", "0", "Broadcasts from this size go through the NVSwitch multicast mapping when available", OptType::MEMUNITS},
             {"DIRECT", "y", "Register the buffers of large messages with the peers (CUDA IPC) and run zero-copy kernels on them", OptType::BOOL},
-            {"DIRECT_MIN", "0", "Messages from this size use the direct (zero-copy) kernels (0: tuning file, else 32m)", OptType::MEMUNITS},
+            {"DIRECT_MIN", "0", "Messages from this size register their buffers and use the direct (zero-copy) kernels (0: from the tuning file, else only on request; measured crossover 32m-256m)", OptType::MEMUNITS},
             {"TUNING_FILE", "", "Measured thresholds, lines of `team_size one_shot_max nvls_min direct_min` (see bench/collectives.py --table)", OptType::STRING},
             {"MAX_BLOCKS", "128", "Upper bound of thread blocks per collective kernel (at most 128)", OptType::UINT},
             {"THREADS", "512", "Threads per block of the collective kernels", OptType::UINT},
@@ -588,7 +588,10 @@ public:
         c.bcast_mc_min    = (size_t)cfg.num("BCAST_MC_MIN");
         c.direct_min      = (size_t)cfg.num("DIRECT_MIN");
         c.direct_min_set  = c.direct_min != 0;
-        if (!c.direct_min_set) c.direct_min = 32u << 20;
+        // Not given: registration happens only on request (XCCL_NVLINK_ALG_DIRECT) or from a tuning file. Registered
+        // buffers must stay allocated while the team lives (the peers keep the allocation mapped), which a
+        // caller has to know about - the same contract as explicit buffer registration in other libraries.
+        if (!c.direct_min_set) c.direct_min = ~(size_t)0;
         c.tuning_file     = cfg.str("TUNING_FILE");
         c.direct          = cfg.flag("DIRECT");
         c.max_blocks      = std::max(1, std::min((int)cfg.num("MAX_BLOCKS"), kMaxBlocks));
