@@ -21,10 +21,12 @@
 #include <chrono>
 #include <cstdlib>
 #include <map>
+#include <memory>
 #include <sstream>
 
 #include "xccl/xccl.h"
 #include "xccl/xccl_oob.h"
+#include "../tl/nccl/nccl_tl.h"  // xccl_p2p_* (extension: point-to-point on NCCL)
 
 namespace {
 
@@ -70,6 +72,7 @@ struct StoreOob {
     c10::intrusive_ptr<c10d::Store> store;
     int                             rank, size;
     std::map<std::string, uint64_t> counters;  // per member-set sequence numbers
+    std::string                     prefix;    // key namespace (pairwise bootstraps of send/recv use their own)
 };
 
 struct StoreReq {
@@ -92,7 +95,7 @@ int store_allgather(void *sbuf, void *rbuf, size_t bytes, int my_rank, xccl_ep_r
     std::ostringstream sig;
     for (int m : members) sig << m << ".";
     uint64_t    seq  = o->counters[sig.str()]++;
-    std::string base = "xccl/oob/" + sig.str() + "/" + std::to_string(seq) + "/";
+    std::string base = "xccl/oob/" + o->prefix + sig.str() + "/" + std::to_string(seq) + "/";
     auto       *r    = new StoreReq{o, {}, static_cast<char *>(rbuf), bytes};
     for (size_t i = 0; i < members.size(); i++) r->keys.push_back(base + std::to_string(i));
     std::vector<uint8_t> mine(static_cast<uint8_t *>(sbuf), static_cast<uint8_t *>(sbuf) + bytes);
@@ -151,7 +154,7 @@ class ProcessGroupXccl : public c10d::Backend {
 public:
     ProcessGroupXccl(const c10::intrusive_ptr<c10d::Store> &store, int rank, int size) : c10d::Backend(rank, size)
     {
-        oob_state_ = StoreOob{store, rank, size, {}};
+        oob_state_ = StoreOob{store, rank, size, {}, ""};
         oob_.allgather    = store_allgather;
         oob_.req_test     = store_test;
         oob_.req_free     = store_free;
@@ -180,6 +183,7 @@ public:
 
     ~ProcessGroupXccl() override
     {
+        for (auto &kv : pairs_) xccl_p2p_comm_destroy(kv.second->comm);
         if (team_ != nullptr) xccl_team_destroy(team_);
         if (ctx_ != nullptr) xccl_context_destroy(ctx_);
         if (lib_ != nullptr) xccl_lib_cleanup(lib_);
@@ -393,7 +397,67 @@ public:
 
     void shutdown() override { reap(true); }
 
+    // Point-to-point on NCCL p2p (pipeline stages). A two-rank communicator per peer is created by both sides at
+    // their first send/recv with each other, bootstrapped through the store under a pair-specific key prefix.
+    c10::intrusive_ptr<c10d::Work> send(std::vector<at::Tensor> &tensors, int dstRank, int /*tag*/) override
+    {
+        return p2p(tensors, dstRank, true);
+    }
+    c10::intrusive_ptr<c10d::Work> recv(std::vector<at::Tensor> &tensors, int srcRank, int /*tag*/) override
+    {
+        return p2p(tensors, srcRank, false);
+    }
+
 private:
+    struct PairComm {
+        StoreOob               state;
+        xccl_oob_collectives_t oob{};
+        void                  *comm = nullptr;
+    };
+
+    PairComm &pair_comm(int peer)
+    {
+        auto it = pairs_.find(peer);
+        if (it != pairs_.end()) return *it->second;
+        const int me = getRank(), lo = std::min(me, peer), hi = std::max(me, peer);
+        auto      pc = std::make_unique<PairComm>();
+        pc->state    = StoreOob{oob_state_.store, me == lo ? 0 : 1, 2, {}, "p2p/" + std::to_string(lo) + "-" + std::to_string(hi) + "/"};
+        pc->oob.allgather    = store_allgather;
+        pc->oob.req_test     = store_test;
+        pc->oob.req_free     = store_free;
+        pc->oob.coll_context = &pc->state;
+        pc->oob.rank         = pc->state.rank;
+        pc->oob.size         = 2;
+        check(xccl_p2p_comm_create(&pc->oob, &pc->comm), "xccl_p2p_comm_create");
+        return *pairs_.emplace(peer, std::move(pc)).first->second;
+    }
+
+    c10::intrusive_ptr<c10d::Work> p2p(std::vector<at::Tensor> &tensors, int peer, bool is_send)
+    {
+        TORCH_CHECK(tensors.size() == 1, "xccl: send/recv take one tensor");
+        at::Tensor &t = tensors[0];
+        TORCH_CHECK(t.is_cuda() && t.is_contiguous(), "xccl: send/recv need a contiguous CUDA tensor");
+        TORCH_CHECK(peer != getRank() && peer >= 0 && peer < getSize(), "xccl: bad peer rank");
+        c10::cuda::CUDAGuard dev_guard(t.device());
+        PairComm            &pc   = pair_comm(peer);
+        auto                 work = c10::make_intrusive<WorkXccl>(is_send ? c10d::OpType::SEND : c10d::OpType::RECV,
+                                                  std::vector<at::Tensor>{t}, true);
+        auto                 cur  = c10::cuda::getCurrentCUDAStream();
+        auto                 comm = comm_stream(t.device().index());
+        at::cuda::CUDAEvent  ready;
+        ready.record(cur);
+        ready.block(comm);
+        c10::cuda::CUDACachingAllocator::recordStream(t.storage().data_ptr(), comm);
+        const int    peer_in_pair = pc.state.rank == 0 ? 1 : 0;
+        const size_t bytes        = static_cast<size_t>(t.numel()) * t.element_size();
+        check(is_send ? xccl_p2p_send(pc.comm, t.data_ptr(), bytes, peer_in_pair, comm.stream())
+                      : xccl_p2p_recv(pc.comm, t.data_ptr(), bytes, peer_in_pair, comm.stream()),
+              is_send ? "xccl_p2p_send" : "xccl_p2p_recv");
+        c10::cuda::CUDAStreamGuard guard(comm);
+        work->complete();
+        return work;
+    }
+
     c10::cuda::CUDAStream comm_stream(c10::DeviceIndex dev)
     {
         auto it = streams_.find(dev);
@@ -422,6 +486,7 @@ private:
     xccl_team_h                                    team_ = nullptr;
     std::map<c10::DeviceIndex, c10::cuda::CUDAStream> streams_;
     std::vector<xccl_coll_req_h>                   pending_;
+    std::map<int, std::unique_ptr<PairComm>>       pairs_;
 };
 
 c10::intrusive_ptr<c10d::Backend> create_backend(const c10::intrusive_ptr<c10d::Store> &store, int rank, int size,

@@ -56,3 +56,42 @@ def test_pipeline_send_recv_two_stages():
         pytest.skip("needs 2 GPUs")
     res = run_ranks(_stage_main, 2, timeout=180, start_method="spawn", env={"NCCL_NVLS_ENABLE": "0"})
     assert res == ["ok", "ok"]
+
+
+def _torch_p2p_main(rank, size, job, port):
+    import os
+
+    import torch.distributed as dist
+
+    import xccl_b200.parallel.torch_backend as tb
+    os.environ.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port)})
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    tb.register()
+    dist.init_process_group(tb.BACKEND, rank=rank, world_size=size)
+    try:
+        peer = 1 - rank
+        for it in range(3):
+            t = torch.full((1 << 14,), float(10 * rank + it), device=dev)
+            if rank == 0:
+                dist.send(t, dst=peer)
+                dist.recv(t, src=peer)
+                want = float(10 * peer + it)
+            else:
+                got = torch.empty_like(t)
+                dist.recv(got, src=peer)
+                dist.send(t, dst=peer)
+                t, want = got, float(10 * peer + it)
+            torch.cuda.synchronize()
+            assert torch.all(t == want)
+        return "ok"
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.xfail(reason="first hardware run of the backend's send/recv is pending", strict=False)
+def test_torch_backend_send_recv():
+    if _ngpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    res = run_ranks(_torch_p2p_main, 2, 29877, timeout=180, start_method="spawn", env={"NCCL_NVLS_ENABLE": "0"})
+    assert res == ["ok", "ok"]
