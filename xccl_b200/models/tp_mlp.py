@@ -79,7 +79,8 @@ class TpMlp:
             for dst, src in zip(self.x_shards, x_pinned):
                 dst.copy_(src, non_blocking=True)
         y = self.forward()
-        metric = y[0].float().square().mean()
+        # mean of squares in ONE reduction kernel (fp32 accumulation), no fp32 copy of the output
+        metric = torch.linalg.vector_norm(y[0], dtype=torch.float32).square() / y[0].numel()
         return metric.cpu()
 
     def check_error(self) -> None:
@@ -162,7 +163,7 @@ class TorchTpMlp:
     def forward_from_host(self, x_pinned: torch.Tensor) -> torch.Tensor:
         self.x_shard.copy_(x_pinned, non_blocking=True)
         y = self.forward()
-        return y.float().square().mean().cpu()
+        return (torch.linalg.vector_norm(y, dtype=torch.float32).square() / y.numel()).cpu()
 
 
 def reference_forward_fp32(x_full: torch.Tensor, w_gate_full: torch.Tensor, w_up_full: torch.Tensor,
