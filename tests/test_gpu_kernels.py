@@ -236,6 +236,56 @@ def test_emu_direct_zero_copy_algorithms(world4, dev):
         assert torch.equal(dsts[r], torch.cat([srcs[s][r * per:(r + 1) * per] for s in range(n)]))
 
 
+class _Guarded:
+    """A byte buffer with 256 sentinel bytes before and after the part a kernel may touch, placed at an odd
+    offset so that the payload is not 16-byte aligned: an out-of-bounds pack store shows up in the guards."""
+    PAD = 256
+
+    def __init__(self, nbytes, dev, fill=0xA5, skew=3):
+        self.raw = torch.full((nbytes + 2 * self.PAD + 16,), fill, dtype=torch.uint8, device=dev)
+        self.off = self.PAD + skew
+        self.n, self.fill = nbytes, fill
+
+    @property
+    def view(self):
+        return self.raw[self.off:self.off + self.n]
+
+    def guards_intact(self):
+        return bool(torch.all(self.raw[:self.off] == self.fill)) and bool(torch.all(self.raw[self.off + self.n:] == self.fill))
+
+
+@pytest.mark.xfail(reason="guard-band checks: first hardware run pending", strict=False)
+def test_emu_byte_collectives_stay_inside_their_buffers(world4, dev):
+    """bcast / allgather / alltoall on unaligned, odd-sized byte buffers: results exact, sources untouched,
+    not one byte written outside the destination."""
+    n = 4
+    for per in (1, 13, 4099, 70001):
+        srcs = [_Guarded(per, dev, fill=0x11) for _ in range(n)]
+        for r, g in enumerate(srcs):
+            g.view.copy_(torch.randint(0, 255, (per,), dtype=torch.uint8, generator=torch.Generator().manual_seed(per + r)).to(dev))
+        keep = [g.view.clone() for g in srcs]
+        dsts = [_Guarded(per * n, dev) for _ in range(n)]
+        world4.allgather([g.view for g in srcs], [g.view for g in dsts])
+        for g in dsts:
+            assert torch.equal(g.view, torch.cat(keep)) and g.guards_intact(), ("allgather", per)
+        a_src = [_Guarded(per * n, dev, fill=0x22) for _ in range(n)]
+        for r, g in enumerate(a_src):
+            g.view.copy_(torch.randint(0, 255, (per * n,), dtype=torch.uint8, generator=torch.Generator().manual_seed(7 * per + r)).to(dev))
+        a_keep = [g.view.clone() for g in a_src]
+        a_dst = [_Guarded(per * n, dev) for _ in range(n)]
+        world4.alltoall([g.view for g in a_src], [g.view for g in a_dst])
+        for r in range(n):
+            want = torch.cat([a_keep[s][r * per:(r + 1) * per] for s in range(n)])
+            assert torch.equal(a_dst[r].view, want) and a_dst[r].guards_intact(), ("alltoall", per)
+        for g, k in zip(srcs + a_src, keep + a_keep):
+            assert torch.equal(g.view, k) and g.guards_intact(), ("source modified", per)
+        bufs = [_Guarded(per, dev) for _ in range(n)]
+        bufs[1].view.copy_(keep[1])
+        world4.bcast([g.view for g in bufs], [g.view for g in bufs], root=1)
+        for g in bufs:
+            assert torch.equal(g.view, keep[1]) and g.guards_intact(), ("bcast", per)
+
+
 def test_emu_alltoallv(world4, dev):
     n = 4
     sc = [[(s * 3 + d * 5 + 1) for d in range(n)] for s in range(n)]  # elements rank s sends to rank d
