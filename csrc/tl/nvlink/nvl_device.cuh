@@ -41,6 +41,8 @@ struct World {
     char     *mc_ws;              // multicast (NVLS) view of the workspaces, or nullptr
     size_t    ws_bytes;           // bytes of one workspace (two halves of ws_bytes / 2)
     unsigned long long wait_budget_ns;
+    size_t    mc_bcast_cap;       // multicast bcast: packs per chunk (0 = a whole workspace half), so that copying chunk k
+                                  // out overlaps the root's push of chunk k+1
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v)

@@ -59,7 +59,7 @@ HostStatus EmuWorld::status(int i) const { return status_host_[i]; }
 
 void EmuWorld::clear_status() { std::memset(status_host_, 0, sizeof(HostStatus) * kMaxRanks); }
 
-int chunks_used(const World &w, xccl_collective_type_t coll, size_t count, size_t len, xccl_dt_t dt)
+int chunks_used(const World &w, xccl_collective_type_t coll, size_t count, size_t len, xccl_dt_t dt, bool multicast)
 {
     const size_t half = w.ws_bytes / 2, cap = half / 16;
     const size_t es   = std::max<size_t>(xccl_dt_size(dt), 1);
@@ -80,6 +80,7 @@ int chunks_used(const World &w, xccl_collective_type_t coll, size_t count, size_
     default: return 1;
     }
     size_t c = std::max<size_t>(cap / div, 1);
+    if (coll == XCCL_BCAST && multicast && w.mc_bcast_cap != 0) c = std::min(c, w.mc_bcast_cap);  // as in mover_kernel
     return (int)std::max<size_t>((packs + c - 1) / c, 1);
 }
 

@@ -385,7 +385,8 @@ template <int KIND, bool kMc> __global__ void __launch_bounds__(512) mover_kerne
     const int     nseg_ws   = (KIND == MV_ALLTOALL) ? w.size : 1;
     const size_t  npacks    = (seg_bytes + 15) / 16;
     const size_t  half      = w.ws_bytes / 2;
-    const size_t  cap       = half / 16 / nseg_ws;
+    size_t        cap       = half / 16 / nseg_ws;
+    if (KIND == MV_BCAST && kMc && w.mc_bcast_cap != 0) cap = min(cap, w.mc_bcast_cap);  // same rule as chunks_used()
     int           parity    = c.parity;
 
     for (size_t c0 = 0; c0 < npacks; c0 += cap, parity ^= 1) {

@@ -30,6 +30,7 @@ struct NvlCfg {
     size_t one_shot_max  = 128u << 10;
     size_t nvls_min      = 256u << 10;
     size_t bcast_mc_min  = 0;
+    size_t bcast_mc_chunk = 0;          // 0: one workspace half per step
     size_t direct_min    = ~(size_t)0;  // messages from this size register their buffers and skip the workspace
     bool   direct_min_set = false;      // given explicitly: a tuning file does not override it
     bool   direct        = true;
@@ -147,6 +148,7 @@ public:
         world.rank_base = rank;
         world.n_local   = 1;
         world.ws_bytes  = cfg.ws_bytes;
+        world.mc_bcast_cap = cfg.bcast_mc_chunk / 16;
         // crossover points measured on NVSwitch systems: with 8 ranks the one-shot kernel's all-to-all
         // traffic loses to the two-step kernels earlier than with 4 or fewer
         if (!cfg.tuning_file.empty()) {
@@ -439,7 +441,7 @@ xccl_status_t NvlReq::post()
         bool mc = w.mc_ws != nullptr && c.len >= team_->cfg.bcast_mc_min;
         if (args_.alg.set_by_user) mc = (args_.alg.id == ALG_NVLS);
         st = launch_bcast(w, c, cfg, s, mc);
-        team_->phase += chunks_used(w, XCCL_BCAST, c.count, c.len, dt);
+        team_->phase += chunks_used(w, XCCL_BCAST, c.count, c.len, dt, mc);
         break;
     }
     case XCCL_ALLGATHER:
@@ -551,6 +553,7 @@ public:
             {"NVLS", "try", "Bind the workspace to an NVSwitch multicast object and use multimem kernels", OptType::TERNARY},
             {"ONE_SHOT_MAX", "0", "Allreduce messages up to this size use the one-shot kernel (0: by team size, 256k from 8 ranks, else 1m)", OptType::MEMUNITS},
             {"NVLS_MIN", "0", "Allreduce messages from this size use NVLS when available (0: by team size, 1m from 8 ranks, else 128k)", OptType::MEMUNITS},
+            {"BCAST_MC_CHUNK", "0", "Multicast broadcasts move this many bytes per step, copy-out overlapping the next push (0: a workspace half)", OptType::MEMUNITS},
             {"BCAST_MC_MIN", "0", "Broadcasts from this size go through the NVSwitch multicast mapping when available", OptType::MEMUNITS},
             {"DIRECT", "y", "Register the buffers of large messages with the peers (CUDA IPC) and run zero-copy kernels on them", OptType::BOOL},
             {"DIRECT_MIN", "0", "Messages from this size register their buffers and use the direct (zero-copy) kernels (0: from the tuning file, else only on request; measured crossover 32m-256m)", OptType::MEMUNITS},
@@ -586,6 +589,7 @@ public:
         c.one_shot_max    = (size_t)cfg.num("ONE_SHOT_MAX");
         c.nvls_min        = (size_t)cfg.num("NVLS_MIN");
         c.bcast_mc_min    = (size_t)cfg.num("BCAST_MC_MIN");
+        c.bcast_mc_chunk  = (size_t)cfg.num("BCAST_MC_CHUNK");
         c.direct_min      = (size_t)cfg.num("DIRECT_MIN");
         c.direct_min_set  = c.direct_min != 0;
         // Not given: registration happens only on request (XCCL_NVLINK_ALG_DIRECT) or from a tuning file. Registered

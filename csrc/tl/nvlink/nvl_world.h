@@ -39,7 +39,7 @@ private:
 };
 
 // Number of workspace halves a launch consumes (so the caller can advance `parity`).
-int chunks_used(const World &w, xccl_collective_type_t coll, size_t count, size_t len, xccl_dt_t dt);
+int chunks_used(const World &w, xccl_collective_type_t coll, size_t count, size_t len, xccl_dt_t dt, bool multicast = false);
 
 }  // namespace nvl
 }  // namespace xccl
