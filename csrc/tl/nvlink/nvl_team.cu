@@ -108,6 +108,10 @@ public:
             cudaStreamSynchronize(stream);
             cudaStreamDestroy(stream);
         }
+        // which algorithm served how many posts (log level info): the quickest check of a selection table
+        tl_info(tl_, "nvlink team rank %d: allreduce posts one-shot %llu, two-shot %llu, NVLS %llu, direct %llu; other "
+                "collectives %llu (direct %llu)", rank, stats.one_shot, stats.two_shot, stats.nvls, stats.direct_allreduce,
+                stats.other, stats.direct_other);
         for (auto &kv : ipc_cache) cudaIpcCloseMemHandle(kv.second);
         delete region;
         if (status_host != nullptr) cudaFreeHost(status_host);
@@ -194,6 +198,9 @@ public:
     NvlCfg           cfg;
     OobGroup         oob;
     std::map<std::string, void *> ipc_cache;
+    struct {
+        unsigned long long one_shot = 0, two_shot = 0, nvls = 0, direct_allreduce = 0, other = 0, direct_other = 0;
+    } stats;
     SymmetricRegion *region = nullptr;
     World            world{};
     HostStatus      *status_host = nullptr;
@@ -402,6 +409,7 @@ xccl_status_t NvlReq::post()
         if (direct_shape_ok((int)args_.coll_type, c, dt, team_->size)) {
             st = launch_direct(w, c, (int)args_.coll_type, dt, out_dt, cfg, s);
             if (st == XCCL_OK) {
+                (args_.coll_type == XCCL_ALLREDUCE ? team_->stats.direct_allreduce : team_->stats.direct_other)++;
                 XCCL_CUDA_CHECK(cudaEventRecord(done_, s));
                 in_flight_ = true;
                 return XCCL_OK;
@@ -425,6 +433,7 @@ xccl_status_t NvlReq::post()
             }
         }
         st = launch_allreduce(w, c, dt, out_dt, alg, cfg, s);
+        (alg == ALG_ONE_SHOT ? team_->stats.one_shot : alg == ALG_NVLS ? team_->stats.nvls : team_->stats.two_shot)++;
         team_->phase += (alg == ALG_ONE_SHOT) ? 1 : chunks_used(w, XCCL_ALLREDUCE, c.count, c.len, dt);
         break;
     }
@@ -461,6 +470,7 @@ xccl_status_t NvlReq::post()
     default: st = launch_sync(w, c, (int)args_.coll_type, cfg, s); break;
     }
     if (st != XCCL_OK) return st;
+    if (args_.coll_type != XCCL_ALLREDUCE) team_->stats.other++;
     XCCL_CUDA_CHECK(cudaEventRecord(done_, s));
     in_flight_ = true;
     return XCCL_OK;
