@@ -56,7 +56,7 @@ class RefTpMlp:
     def forward_from_host(self, x_pinned: torch.Tensor) -> torch.Tensor:
         self.x_shard.copy_(x_pinned, non_blocking=True)
         y = self.forward()
-        return (torch.linalg.vector_norm(y, dtype=torch.float32).square() / y.numel()).cpu()
+        return torch.linalg.vector_norm(y, dtype=torch.float32).cpu().square() / y.numel()
 
     def close(self) -> None:
         torch.cuda.synchronize()

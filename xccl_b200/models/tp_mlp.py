@@ -80,8 +80,8 @@ class TpMlp:
                 dst.copy_(src, non_blocking=True)
         y = self.forward()
         # mean of squares in ONE reduction kernel (fp32 accumulation), no fp32 copy of the output
-        metric = torch.linalg.vector_norm(y[0], dtype=torch.float32).square() / y[0].numel()
-        return metric.cpu()
+        norm = torch.linalg.vector_norm(y[0], dtype=torch.float32).cpu()   # the device->host read of the step
+        return norm.square() / y[0].numel()                                 # finished on the host
 
     def check_error(self) -> None:
         e = self.ws.error()
@@ -163,7 +163,7 @@ class TorchTpMlp:
     def forward_from_host(self, x_pinned: torch.Tensor) -> torch.Tensor:
         self.x_shard.copy_(x_pinned, non_blocking=True)
         y = self.forward()
-        return (torch.linalg.vector_norm(y, dtype=torch.float32).square() / y.numel()).cpu()
+        return torch.linalg.vector_norm(y, dtype=torch.float32).cpu().square() / y.numel()
 
 
 def reference_forward_fp32(x_full: torch.Tensor, w_gate_full: torch.Tensor, w_up_full: torch.Tensor,
