@@ -216,3 +216,42 @@ def test_tp_mlp_fused_across_gpus(size):
         pytest.skip(f"needs {size} GPUs")
     res = run_ranks(_tp_rank_main, size, timeout=300, start_method="spawn")
     print("tp mlp max abs err per rank:", res)
+
+
+def _host_team_cuda_main(rank, size, job):
+    """The host team serving CUDA buffers (the reference's CUDA tests run its UCX team on device memory,
+    test/test_mpi_cuda_allreduce.c, test_mpi_cuda_reduce.c): staged through pinned memory, started in
+    stream order."""
+    from xccl_b200.api import Context, Lib, ShmOob, Team
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    oob = ShmOob(job, rank, size)
+    lib = Lib()
+    ctx = Context(lib, oob, tls=K.TL_UCX)
+    team = Team(ctx)
+    assert team.coll_tl(K.ALLREDUCE, K.MEM_CUDA) == K.TL_UCX
+    stream = torch.cuda.current_stream().cuda_stream
+    for dtype, count in ((torch.float32, 1), (torch.int32, 1000), (torch.float32, 70001)):
+        src = _vals(rank, count, dtype, seed=31).to(dev)
+        dst = torch.zeros_like(src)
+        team.allreduce(src, dst, stream=stream).run().finalize()
+        want = torch.stack([_vals(r, count, dtype, seed=31).double() for r in range(size)]).sum(0).to(dtype)
+        assert torch.equal(dst.cpu(), want), (dtype, count)
+    src = _vals(rank, 5000, torch.float32, seed=32).to(dev)
+    dst = torch.zeros_like(src)
+    team.reduce(src, dst, root=0, stream=stream).run().finalize()
+    if rank == 0:
+        assert torch.equal(dst.cpu(), torch.stack([_vals(r, 5000, torch.float32, seed=32) for r in range(size)]).sum(0))
+    buf = _vals(1, 4099, torch.float32, seed=33).to(dev) if rank == 1 else torch.zeros(4099, device=dev)
+    team.bcast(buf, 1, stream=stream).run().finalize()
+    assert torch.equal(buf.cpu(), _vals(1, 4099, torch.float32, seed=33))
+    team.close(); ctx.close(); lib.close(); oob.close()
+    return "ok"
+
+
+@pytest.mark.xfail(reason="first hardware run of the host team on device buffers across GPUs is pending", strict=False)
+def test_host_team_serves_cuda_buffers():
+    if _ngpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    res = run_ranks(_host_team_cuda_main, 2, timeout=180, start_method="spawn")
+    assert res == ["ok", "ok"]
