@@ -32,11 +32,11 @@ struct Tile {
 };
 
 // Order in which a rank walks its output tiles.
-//  COMM_NONE            groups of 16 row blocks x all column blocks (L2 reuse of A and B)
+//  COMM_NONE            groups of group_rows row blocks x all column blocks (L2 reuse of A and B)
 //  COMM_ALLGATHER_A     row shard by row shard, starting with the local one (its A is already here)
 //  COMM_REDUCE_SCATTER  row shard by row shard, starting with the next rank's and ending with the
 //                       local one, so remote partial tiles leave early and local ones need no wire
-__device__ __forceinline__ Tile tile_of(const GemmParams &p, int rank, int t, int tiles_m, int tiles_n)
+__host__ __device__ __forceinline__ Tile tile_of(const GemmParams &p, int rank, int t, int tiles_m, int tiles_n)
 {
     Tile tl;
     if (p.comm == COMM_NONE) {

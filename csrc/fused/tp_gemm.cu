@@ -601,6 +601,26 @@ xccl_status_t xccl_gemm_swiglu_bf16(const void *A, const void *Wg, const void *W
     return launch_gemm(p, l, (cudaStream_t)stream);
 }
 
+// Host-side view of the tile order (tests): writes (row block, column block, shard) of tile t = 0 .. tiles-1 as
+// rank `rank` walks them and returns the number of tiles, or -1 when `max` is too small.
+int xccl_tp_tile_order(int tiles_m, int tiles_n, int tp, int rank, int comm, int group_rows, int *mb, int *nb, int *shard,
+                       int max)
+{
+    GemmParams p{};
+    p.comm       = comm;
+    p.tp_size    = tp;
+    p.group_rows = group_rows;
+    const int total = tiles_m * tiles_n;
+    if (total > max) return -1;
+    for (int t = 0; t < total; t++) {
+        const Tile tl = tile_of(p, rank, t, tiles_m, tiles_n);
+        mb[t] = tl.mb;
+        nb[t] = tl.nb;
+        shard[t] = tl.shard;
+    }
+    return total;
+}
+
 uint32_t xccl_gemm_last_error(void)
 {
     uint32_t *w = xccl::tp::error_word();
