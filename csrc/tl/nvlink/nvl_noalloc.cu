@@ -1,6 +1,7 @@
 // See nvl_noalloc.h. The scratch that EmuWorld::create obtains with cudaMalloc is replaced by a
 // file-scope device array; the kernel is the one-shot allreduce of nvl_kernels.cu, handed
 // pointers into that array.
+#include <atomic>
 #include <cstring>
 
 #include "../../cuda/cuda_common.h"
@@ -22,24 +23,25 @@ constexpr size_t kScratchBytes = kPadRegion + kStatusBytes + kWsBytes * XCCL_NOA
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kScratchBytes];
 
 constexpr int kMaxDevices = 64;
-void         *g_scratch_ptr[kMaxDevices] = {nullptr};
+std::atomic<void *> g_scratch_ptr[kMaxDevices];
 
-// Device address of the scratch on the current device; looked up once per device.
+// Device address of the scratch on the current device; looked up once per device. Two threads that make the
+// first call on one device at the same time both look it up and store the same address.
 xccl_status_t scratch_for_current_device(unsigned char **out)
 {
     int dev = 0;
     XCCL_CUDA_CHECK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= kMaxDevices) return XCCL_ERR_INVALID_PARAM;
-    if (g_scratch_ptr[dev] == nullptr) {
-        void       *p = nullptr;
+    void *p = g_scratch_ptr[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
         cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
         if (e != cudaSuccess || p == nullptr) {
             xccl_error("cudaGetSymbolAddress(no-alloc scratch) failed on device %d: %s", dev, cudaGetErrorString(e));
             return xccl::cuda_status(e != cudaSuccess ? e : cudaErrorUnknown);
         }
-        g_scratch_ptr[dev] = p;
+        g_scratch_ptr[dev].store(p, std::memory_order_release);
     }
-    *out = (unsigned char *)g_scratch_ptr[dev];
+    *out = (unsigned char *)p;
     return XCCL_OK;
 }
 

@@ -254,7 +254,6 @@ class _Guarded:
         return bool(torch.all(self.raw[:self.off] == self.fill)) and bool(torch.all(self.raw[self.off + self.n:] == self.fill))
 
 
-@pytest.mark.xfail(reason="guard-band checks: first hardware run pending", strict=False)
 def test_emu_byte_collectives_stay_inside_their_buffers(world4, dev):
     """bcast / allgather / alltoall on unaligned, odd-sized byte buffers: results exact, sources untouched,
     not one byte written outside the destination."""

@@ -210,7 +210,7 @@ def _tp_rank_main(rank, size, job):
         oob.close()
 
 
-@pytest.mark.parametrize("size", [2, 4])
+@pytest.mark.parametrize("size", [2, 4, 8])
 def test_tp_mlp_fused_across_gpus(size):
     if _ngpus() < size:
         pytest.skip(f"needs {size} GPUs")
@@ -249,7 +249,6 @@ def _host_team_cuda_main(rank, size, job):
     return "ok"
 
 
-@pytest.mark.xfail(reason="first hardware run of the host team on device buffers across GPUs is pending", strict=False)
 def test_host_team_serves_cuda_buffers():
     if _ngpus() < 2:
         pytest.skip("needs 2 GPUs")

@@ -50,7 +50,6 @@ def _stage_main(rank, size, job):
         oob.close()
 
 
-@pytest.mark.xfail(reason="first hardware run of the pipeline helpers is pending", strict=False)
 def test_pipeline_send_recv_two_stages():
     if _ngpus() < 2:
         pytest.skip("needs 2 GPUs")
@@ -89,7 +88,6 @@ def _torch_p2p_main(rank, size, job, port):
         dist.destroy_process_group()
 
 
-@pytest.mark.xfail(reason="first hardware run of the backend's send/recv is pending", strict=False)
 def test_torch_backend_send_recv():
     if _ngpus() < 2:
         pytest.skip("needs 2 GPUs")
