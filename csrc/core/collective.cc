@@ -4,6 +4,7 @@
 
 #include <nvtx3/nvToolsExt.h>  // header-only: resolves to no-ops unless a profiler injects itself
 
+#include "../cuda/mem_cuda.h"
 #include "../utils/mem.h"
 #include "core.h"
 
@@ -85,6 +86,92 @@ struct FanoutMemHandle final : xccl_mem_handle {
 
 }  // namespace
 
+namespace {
+
+// The scale/cast epilogue for a team library that cannot fuse it: the library reduces in the input datatype
+// (into the caller's dst when the output type is the same, else into a private buffer), and when its request
+// completes the result is scaled and converted into dst as a last local step - on the host for host memory,
+// with the reduction kernel (no vectors to add, only scale and cast) for device memory. The request reports
+// completion only after that step. Such libraries complete through test(), so a caller already has to see
+// XCCL_OK before it reads dst.
+struct EpilogueReq final : xccl_coll_req {
+    xccl_coll_req     *inner = nullptr;
+    xccl_memory_type_t mem   = XCCL_MEMORY_TYPE_HOST;
+    void              *tmp   = nullptr;   // owned; nullptr = scale in place in dst
+    void              *dst   = nullptr;
+    xccl_dt_t          dt = XCCL_DT_UNSUPPORTED, out_dt = XCCL_DT_UNSUPPORTED;
+    size_t             count  = 0;
+    float              scale  = 1.0f;
+    void              *stream = nullptr;  // cudaStream_t value, may be null
+    void              *event  = nullptr;
+    bool               local_result = true;  // false on the non-root ranks of a reduce
+    enum { IDLE, INNER, KERNEL, DONE } state = IDLE;
+
+    ~EpilogueReq() override
+    {
+        if (event != nullptr) cuda_event_release(event);
+        if (tmp != nullptr) mem_free(tmp, mem);
+        delete inner;
+    }
+    xccl_status_t post() override
+    {
+        if (state == INNER || state == KERNEL) return XCCL_ERR_INVALID_PARAM;  // still in flight
+        xccl_status_t st = inner->post();
+        if (st == XCCL_OK) state = INNER;
+        return st;
+    }
+    xccl_status_t test() override
+    {
+        if (state == INNER) {
+            xccl_status_t st = inner->test();
+            if (st != XCCL_OK) return st;
+            if (!local_result || count == 0) {
+                state = DONE;
+            } else if (mem == XCCL_MEMORY_TYPE_CUDA) {
+                st = cuda_reduce_multi(tmp != nullptr ? tmp : dst, nullptr, dst, 0, count, 0, dt, XCCL_OP_SUM, scale,
+                                       out_dt, stream != nullptr ? stream : cuda_internal_stream());
+                if (st != XCCL_OK) return st;
+                st = cuda_event_record(stream != nullptr ? stream : cuda_internal_stream(), &event);
+                if (st != XCCL_OK) return st;
+                state = KERNEL;
+            } else {
+                st = host_scale_cast(tmp != nullptr ? tmp : dst, dt, dst, out_dt, count, scale);
+                if (st != XCCL_OK) return st;
+                state = DONE;
+            }
+        }
+        if (state == KERNEL) {
+            xccl_status_t st = cuda_event_query(event);
+            if (st != XCCL_OK) return st;
+            cuda_event_release(event);
+            event = nullptr;
+            state = DONE;
+        }
+        return state == DONE ? XCCL_OK : XCCL_ERR_INVALID_PARAM;  // IDLE: never posted
+    }
+    xccl_status_t finalize() override
+    {
+        if (state == INNER || state == KERNEL) return XCCL_INPROGRESS;
+        return inner->finalize();
+    }
+    double elapsed_us() override { return inner->elapsed_us(); }
+};
+
+bool is_reduction(xccl_collective_type_t c) { return c == XCCL_ALLREDUCE || c == XCCL_REDUCE || c == XCCL_REDUCE_SCATTER; }
+
+// Elements of dt that the reduction leaves in dst on this rank.
+size_t result_count(const xccl_coll_op_args_t &a, int team_size)
+{
+    const size_t es = xccl_dt_size(a.reduce_info.dt);
+    if (es == 0) return 0;
+    if (a.coll_type == XCCL_REDUCE_SCATTER) {
+        return a.buffer_info.len != 0 ? a.buffer_info.len / (size_t)team_size / es : a.reduce_info.count;
+    }
+    return a.buffer_info.len != 0 ? a.buffer_info.len / es : a.reduce_info.count;
+}
+
+}  // namespace
+
 namespace xccl {
 // A region handle returned by xccl_global_mem_map_start bundles one handle per team library;
 // a team library finds its own part with this.
@@ -100,6 +187,58 @@ xccl_mem_handle *find_mem_part(xccl_mem_handle *h, bool (*match)(xccl_mem_handle
     return match(h) ? h : nullptr;
 }
 }  // namespace xccl
+
+namespace {
+
+xccl_status_t init_with_local_epilogue(xccl_team *team, TlTeam *tt, const xccl_coll_op_args_t &args,
+                                       xccl_memory_type_t mem, xccl_coll_req **out)
+{
+    const xccl_dt_t dt = args.reduce_info.dt;
+    xccl_dt_t       od = args.epilogue.out_dt;
+    if (od == XCCL_DT_UNSUPPORTED || od == XCCL_DT_LAST_PREDEFINED) od = dt;
+    xccl_coll_op_args_t inner = args;
+    inner.field_mask &= ~(uint64_t)XCCL_COLL_OP_ARGS_FIELD_EPILOGUE;
+    if (args.epilogue.scale == 1.0f && od == dt) return tt->collective_init(inner, mem, out);
+
+    // the conversion has to exist; probe it on the host, where both sides implement the same pairs
+    char pin[16] = {0}, pout[16] = {0};
+    if (host_scale_cast(pin, dt, pout, od, 1, 1.0f) != XCCL_OK) return XCCL_ERR_UNSUPPORTED;
+
+    int rank = 0, size = 1;
+    xccl_team_query(team, &rank, &size);
+    auto *req         = new EpilogueReq;
+    req->mem          = mem;
+    req->dt           = dt;
+    req->out_dt       = od;
+    req->scale        = args.epilogue.scale;
+    req->count        = result_count(args, size);
+    req->dst          = args.buffer_info.dst_buffer;
+    req->local_result = (args.coll_type != XCCL_REDUCE) || (args.root == rank);
+    if ((args.field_mask & XCCL_COLL_OP_ARGS_FIELD_STREAM) && args.stream.stream != nullptr) {
+        req->stream = *(void **)args.stream.stream;
+    }
+    if (od != dt && req->local_result) {
+        xccl_status_t st = mem_alloc(&req->tmp, req->count * xccl_dt_size(dt), mem);
+        if (st != XCCL_OK) {
+            delete req;
+            return st;
+        }
+        // in place: dst holds the input and receives the converted output; the library reads it, writes tmp
+        if (inner.buffer_info.src_buffer == XCCL_IN_PLACE || inner.buffer_info.src_buffer == nullptr) {
+            inner.buffer_info.src_buffer = args.buffer_info.dst_buffer;
+        }
+        inner.buffer_info.dst_buffer = req->tmp;
+    }
+    xccl_status_t st = tt->collective_init(inner, mem, &req->inner);
+    if (st != XCCL_OK) {
+        delete req;
+        return st;
+    }
+    *out = req;
+    return XCCL_OK;
+}
+
+}  // namespace
 
 extern "C" {
 
@@ -127,15 +266,39 @@ xccl_status_t xccl_collective_init(xccl_coll_op_args_t *args, xccl_coll_req_h *r
         xccl_debug("no team library serves collective %d on memory type %d", (int)args->coll_type, (int)mem);
         return XCCL_ERR_UNSUPPORTED;
     }
-    TlTeam *tt = team->tl_teams[(size_t)id].get();
-    if (tt->poisoned) return XCCL_ERR_NO_PROGRESS;
-    xccl_coll_req *req = nullptr;
-    xccl_status_t  st  = tt->collective_init(*args, mem, &req);
-    if (st != XCCL_OK) return st;
-    req->core_team = team;
-    req->coll_type = (int)args->coll_type;
-    *request       = req;
-    return XCCL_OK;
+    // The table names the first team library by priority. When that one answers XCCL_ERR_UNSUPPORTED for
+    // these arguments (a datatype, operation or layout it does not handle - facts every rank sees alike),
+    // the next one that serves the collective on this memory type is asked.
+    const bool want_epi = is_reduction(args->coll_type) && (args->field_mask & XCCL_COLL_OP_ARGS_FIELD_EPILOGUE);
+    xccl_status_t st = XCCL_ERR_UNSUPPORTED;
+    for (size_t i = (size_t)id; i < team->tl_teams.size(); i++) {
+        TlTeam       *tt   = team->tl_teams[i].get();
+        const TlCaps &caps = tt->ctx->tl->caps;
+        if (i != (size_t)id) {
+            const bool     sync = (args->coll_type == XCCL_BARRIER || args->coll_type == XCCL_FANIN ||
+                               args->coll_type == XCCL_FANOUT);
+            const uint64_t mems = (sync && caps.sync_mem_types != ~0ull) ? caps.sync_mem_types : caps.mem_types;
+            if (!(caps.coll_types & XCCL_BIT(args->coll_type)) || !(mems & XCCL_BIT(mem))) continue;
+        }
+        if (tt->poisoned) return XCCL_ERR_NO_PROGRESS;
+        xccl_coll_req *req = nullptr;
+        if (want_epi && !caps.epilogue) {
+            st = init_with_local_epilogue(team, tt, *args, mem, &req);
+        } else {
+            st = tt->collective_init(*args, mem, &req);
+        }
+        if (st == XCCL_ERR_UNSUPPORTED) {
+            xccl_debug("team library %s does not take this %s, trying the next one", tt->ctx->tl->name,
+                       coll_name((int)args->coll_type));
+            continue;
+        }
+        if (st != XCCL_OK) return st;
+        req->core_team = team;
+        req->coll_type = (int)args->coll_type;
+        *request       = req;
+        return XCCL_OK;
+    }
+    return st;
 }
 
 xccl_status_t xccl_collective_post(xccl_coll_req_h request)

@@ -11,6 +11,7 @@
 #include <mutex>
 #include <unistd.h>
 
+#include "../utils/mem.h"
 #include "../utils/topo.h"
 #include "core.h"
 
@@ -100,6 +101,39 @@ TeamLib *find_team_lib(xccl_tl_id_t id)
     return nullptr;
 }
 
+namespace {
+struct Plugin {
+    void    *handle;
+    TeamLib *tl;
+};
+std::vector<Plugin> &plugins()
+{
+    static std::vector<Plugin> p;
+    return p;
+}
+
+// End of the process (reference: the library destructor, src/core/xccl_finalize.c:18-42): every team library
+// that was opened is closed, newest first, the scratch cache of the memory component is dropped and plugin
+// objects are unloaded. Registered with atexit when the team libraries are opened, so it runs before the
+// destructors of the statically registered team-library objects, which were constructed earlier.
+void close_all_team_libs()
+{
+    auto &reg = team_lib_registry();
+    for (auto it = reg.rbegin(); it != reg.rend(); ++it) {
+        if ((*it)->opened) {
+            (*it)->close();
+            (*it)->opened = false;
+        }
+    }
+    mem_cache_release();
+    for (auto it = plugins().rbegin(); it != plugins().rend(); ++it) {
+        reg.erase(std::remove(reg.begin(), reg.end(), it->tl), reg.end());
+        dlclose(it->handle);
+    }
+    plugins().clear();
+}
+}  // namespace
+
 static void load_plugins(const std::string &dir)
 {
     glob_t      g{};
@@ -121,7 +155,14 @@ static void load_plugins(const std::string &dir)
             dlclose(h);
             continue;
         }
-        register_team_lib(fn());
+        TeamLib *tl = fn();
+        if (tl == nullptr || find_team_lib(tl->id) != nullptr) {
+            xccl_warn("plugin %s offers no team library, or one whose id is already registered", g.gl_pathv[i]);
+            dlclose(h);
+            continue;
+        }
+        register_team_lib(tl);
+        plugins().push_back(Plugin{h, tl});
     }
     globfree(&g);
 }
@@ -153,6 +194,7 @@ void open_all_team_libs()
                 xccl_debug("team library %s not available (%s)", tl->name, xccl_status_str(st));
             }
         }
+        std::atexit(close_all_team_libs);
     });
 }
 

@@ -75,6 +75,10 @@ struct TlCaps {
     unsigned                   thread_mode  = XCCL_THREAD_MODE_SINGLE | XCCL_THREAD_MODE_MULTIPLE;
     uint64_t                   team_usage   = XCCL_LIB_PARAMS_TEAM_USAGE_SW_COLLECTIVES;
     xccl_context_create_mode_t ctx_mode     = XCCL_TEAM_LIB_CONTEXT_CREATE_MODE_LOCAL;
+    // true: the TL applies xccl_coll_epilogue_t (scale, output cast) itself, fused into its last pass.
+    // false: the core strips the epilogue from the arguments the TL sees and applies it as a local last
+    // step when the TL's collective has completed (csrc/core/collective.cc, EpilogueReq).
+    bool                       epilogue     = false;
 };
 
 class TeamLib {

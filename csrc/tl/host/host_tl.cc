@@ -395,6 +395,7 @@ public:
                           XCCL_COLL_CAP_FANIN | XCCL_COLL_CAP_FANOUT | XCCL_COLL_CAP_REDUCE_SCATTER;
         caps.mem_types    = XCCL_BIT(XCCL_MEMORY_TYPE_HOST) | XCCL_BIT(XCCL_MEMORY_TYPE_CUDA);
         caps.reproducible = XCCL_REPRODUCIBILITY_MODE_REPRODUCIBLE | XCCL_REPRODUCIBILITY_MODE_NON_REPRODUCIBLE;
+        caps.epilogue     = true;
     }
 
     std::vector<OptField> context_options() const override

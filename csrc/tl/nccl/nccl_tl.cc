@@ -6,12 +6,15 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <algorithm>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
 
 #include "../../core/core.h"
 #include "../../cuda/cuda_common.h"
+#include "../../cuda/mem_cuda.h"
+#include "../../utils/mem.h"
 #include "nccl_tl.h"
 
 namespace xccl {
@@ -108,6 +111,7 @@ public:
     {
         if (done_ != nullptr) cudaEventDestroy(done_);
         if (start_ != nullptr) cudaEventDestroy(start_);
+        if (epi_tmp_ != nullptr) cuda_free(epi_tmp_);
     }
     xccl_status_t prepare();
     xccl_status_t post() override;
@@ -145,6 +149,13 @@ private:
     bool                in_flight_ = false;
     xccl_status_t       last_ = XCCL_OK;
     double              elapsed_us_ = -1.0;
+    // scale / cast epilogue: NCCL reduces in the input datatype (into epi_tmp_ when the output datatype
+    // differs, so that it never writes count * sizeof(dt) bytes into a destination sized for out_dt), then
+    // one kernel on the same stream scales and converts into dst
+    bool      epi_       = false;
+    void     *epi_tmp_   = nullptr;
+    size_t    epi_count_ = 0;
+    xccl_dt_t epi_out_   = XCCL_DT_UNSUPPORTED;
 };
 
 class NcclTeam final : public TlTeam {
@@ -201,6 +212,25 @@ xccl_status_t NcclReq::prepare()
     case XCCL_REDUCE:
     case XCCL_REDUCE_SCATTER:
         if (!to_nccl_dt(args_.reduce_info.dt, &dt) || !to_nccl_op(args_.reduce_info.op, &op)) return XCCL_ERR_UNSUPPORTED;
+        if (args_.field_mask & XCCL_COLL_OP_ARGS_FIELD_EPILOGUE) {
+            const xccl_dt_t in = args_.reduce_info.dt;
+            epi_out_           = args_.epilogue.out_dt;
+            if (epi_out_ == XCCL_DT_UNSUPPORTED || epi_out_ == XCCL_DT_LAST_PREDEFINED) epi_out_ = in;
+            epi_       = (args_.epilogue.scale != 1.0f) || (epi_out_ != in);
+            epi_count_ = args_.reduce_info.count;
+            if (epi_count_ == 0) {
+                epi_count_ = bi.len / xccl_dt_size(in) / (args_.coll_type == XCCL_REDUCE_SCATTER ? (size_t)team_->size : 1);
+            }
+            if (args_.coll_type == XCCL_REDUCE && args_.root != team_->rank) epi_ = false;  // no result here
+            if (epi_) {
+                char pin[16] = {0}, pout[16] = {0};
+                if (host_scale_cast(pin, in, pout, epi_out_, 1, 1.0f) != XCCL_OK) return XCCL_ERR_UNSUPPORTED;
+                if (epi_out_ != in) {
+                    xccl_status_t st = cuda_alloc(&epi_tmp_, std::max<size_t>(epi_count_ * xccl_dt_size(in), 16));
+                    if (st != XCCL_OK) return st;
+                }
+            }
+        }
         break;
     case XCCL_ALLTOALLV:
         if (bi.src_counts == nullptr || bi.dst_counts == nullptr || bi.src_displacements == nullptr ||
@@ -229,6 +259,8 @@ xccl_status_t NcclReq::start(cudaStream_t s)
     ncclComm_t  comm = team_->comm;
     void       *src = bi.src_buffer, *dst = bi.dst_buffer;
     if (src == XCCL_IN_PLACE || src == nullptr) src = dst;
+    void *const user_dst = dst;
+    if (epi_tmp_ != nullptr) dst = epi_tmp_;
     ncclDataType_t dt = ncclChar;
     ncclRedOp_t    op = ncclSum;
     switch (args_.coll_type) {
@@ -277,6 +309,10 @@ xccl_status_t NcclReq::start(cudaStream_t s)
     case XCCL_BCAST: NCCL_TRY(team_->tl_, api().Broadcast(src, dst, bi.len, ncclChar, args_.root, comm, s)); break;
     default: return XCCL_ERR_UNSUPPORTED;
     }
+    if (epi_) {
+        return cuda_reduce_multi(dst, nullptr, user_dst, 0, epi_count_, 0, args_.reduce_info.dt, XCCL_OP_SUM,
+                                 args_.epilogue.scale, epi_out_, s);
+    }
     return XCCL_OK;
 }
 
@@ -323,6 +359,7 @@ public:
     {
         caps.mem_types  = XCCL_BIT(XCCL_MEMORY_TYPE_CUDA);
         caps.team_usage = XCCL_LIB_PARAMS_TEAM_USAGE_SW_COLLECTIVES | XCCL_LIB_PARAMS_TEAM_USAGE_HW_COLLECTIVES;
+        caps.epilogue   = true;  // one scale/cast kernel on the same stream after the library call
     }
     std::vector<OptField> lib_options() const override
     {

@@ -476,53 +476,97 @@ template <int KIND, bool kMc> __global__ void __launch_bounds__(512) mover_kerne
     self_end(w, s);
 }
 
-// alltoallv: one chunk; a header per block index publishes the sender's per-destination bytes.
+// alltoallv: any counts. A rank's outgoing segments, each rounded up to a 16-byte pack and laid end to end in
+// destination order, form its "stream". Round k stages window k of that stream (cap bytes) in the workspace half
+// of alternating parity, the ranks meet at a barrier, and every receiver pulls the part of its segment that lies
+// inside the window. A header per block index, written in round 0, publishes the sender's per-destination bytes;
+// after the first barrier every block reads all N headers and so knows every stream's length: the number of
+// rounds (the longest stream divided by the window) is the same on all ranks without any host exchange.
+// Whatever the number of rounds, the launch counts as ONE workspace half for the caller's parity bookkeeping: a
+// closing barrier after a multi-round exchange makes sure no peer still reads either half when the next
+// collective begins.
 constexpr size_t kVHeaderBytes = (size_t)kMaxBlocks * kMaxRanks * 4;
 
 __global__ void __launch_bounds__(512) alltoallv_kernel(World w, Call c)
 {
+    __shared__ uint32_t sh_hdr[kMaxRanks * kMaxRanks];  // [sender][destination] bytes
     Self            s    = self_begin(w);
     const Byte     *src  = (const Byte *)c.src[s.local];
     Byte           *dst  = (Byte *)c.dst[s.local];
     const uint32_t *meta = c.vmeta[s.local];
     const uint32_t *sc = meta, *sd = meta + w.size, *dc = meta + 2 * w.size, *dd = meta + 3 * w.size;
-    const size_t    hoff = (size_t)c.parity * (w.ws_bytes / 2);
-    char           *mine = w.ws[s.rank] + hoff;
-    uint32_t       *hdr  = reinterpret_cast<uint32_t *>(mine) + (size_t)blockIdx.x * kMaxRanks;
+    const size_t    half = w.ws_bytes / 2;
+    const size_t    cap  = (half - kVHeaderBytes) & ~(size_t)15;  // stream bytes per round
+    int             parity = c.parity;
+    size_t          rounds = 1;
 
-    if ((int)threadIdx.x < w.size) hdr[threadIdx.x] = sc[threadIdx.x] * (uint32_t)c.src_es;
-    size_t off = kVHeaderBytes;
-    for (int q = 0; q < w.size; q++) {
-        const size_t bytes = (size_t)sc[q] * c.src_es;
-        const size_t n     = (bytes + 15) / 16;
-        const Byte  *seg   = src + (size_t)sd[q] * c.src_es;
-        const bool   al    = ((uintptr_t)seg & 15) == 0;
-        const Range  r     = block_range(n);
-        stream_packs<4>(
-            r.lo, r.hi, [&](size_t i) { return load_pack<Byte>(seg, i, bytes, al); },
-            [&](size_t i, uint4 v) { st_16(mine + off + i * 16, v); });
-        off += n * 16;
-    }
-    block_barrier(w, s);
-    if (!s.failed) {
+    for (size_t k = 0; k < rounds; k++, parity ^= 1) {
+        const size_t hoff = (size_t)parity * half;
+        char        *mine = w.ws[s.rank] + hoff;
+        const size_t w0 = k * cap, w1 = w0 + cap;
+        if (k == 0) {
+            uint32_t *hdr = reinterpret_cast<uint32_t *>(mine) + (size_t)blockIdx.x * kMaxRanks;
+            if ((int)threadIdx.x < w.size) hdr[threadIdx.x] = sc[threadIdx.x] * (uint32_t)c.src_es;
+        }
+        // stage the part of each outgoing segment that lies in [w0, w1)
+        size_t off = 0;
+        for (int q = 0; q < w.size; q++) {
+            const size_t bytes = (size_t)sc[q] * c.src_es;
+            const size_t n     = (bytes + 15) / 16;
+            const size_t lo = max(off, w0), hi = min(off + n * 16, w1);
+            if (lo < hi) {
+                const Byte *seg = src + (size_t)sd[q] * c.src_es;
+                const bool  al  = ((uintptr_t)seg & 15) == 0;
+                const size_t p0 = (lo - off) / 16;
+                const Range  r  = block_range((hi - lo) / 16);
+                char        *to = mine + kVHeaderBytes + (off - w0);  // may point before the data area; indexed from p0 on
+                stream_packs<4>(
+                    p0 + r.lo, p0 + r.hi, [&](size_t i) { return load_pack<Byte>(seg, i, bytes, al); },
+                    [&](size_t i, uint4 v) { st_16(to + i * 16, v); });
+            }
+            off += n * 16;
+        }
+        block_barrier(w, s);
+        if (s.failed) break;
+        if (k == 0) {
+            // every sender's header -> shared memory; the longest stream fixes the number of rounds
+            for (int t = threadIdx.x; t < w.size * w.size; t += blockDim.x) {
+                const int       p  = t / w.size, j = t % w.size;
+                const uint32_t *ph = reinterpret_cast<const uint32_t *>(w.ws[p] + hoff) + (size_t)blockIdx.x * kMaxRanks;
+                sh_hdr[p * kMaxRanks + j] = ld_relaxed_sys(ph + j);
+            }
+            __syncthreads();
+            size_t longest = 0;
+            for (int p = 0; p < w.size; p++) {
+                size_t tot = 0;
+                for (int j = 0; j < w.size; j++) tot += (((size_t)sh_hdr[p * kMaxRanks + j] + 15) / 16) * 16;
+                longest = max(longest, tot);
+            }
+            rounds = max((size_t)1, (longest + cap - 1) / cap);
+        }
         for (int q = 0; q < w.size; q++) {
             const int       p    = (s.rank + q) % w.size;
             const char     *peer = w.ws[p] + hoff;
-            const uint32_t *ph   = reinterpret_cast<const uint32_t *>(peer) + (size_t)blockIdx.x * kMaxRanks;
-            size_t          poff = kVHeaderBytes;
-            for (int j = 0; j < s.rank; j++) poff += (((size_t)ld_relaxed_sys(ph + j) + 15) / 16) * 16;
-            const size_t sent  = ld_relaxed_sys(ph + s.rank);
+            const uint32_t *ph   = sh_hdr + p * kMaxRanks;
+            size_t          poff = 0;
+            for (int j = 0; j < s.rank; j++) poff += (((size_t)ph[j] + 15) / 16) * 16;
+            const size_t sent  = ph[s.rank];
             const size_t want  = (size_t)dc[p] * c.dst_es;
             const size_t bytes = min(sent, want);
             const size_t n     = (sent + 15) / 16;  // the sender's partition
-            Byte        *out   = dst + (size_t)dd[p] * c.dst_es;
-            const bool   al    = ((uintptr_t)out & 15) == 0;
-            const Range  r     = block_range(n);
+            const size_t lo = max(poff, w0), hi = min(poff + n * 16, w1);
+            if (lo >= hi) continue;
+            Byte        *out  = dst + (size_t)dd[p] * c.dst_es;
+            const bool   al   = ((uintptr_t)out & 15) == 0;
+            const size_t p0   = (lo - poff) / 16;
+            const Range  r    = block_range((hi - lo) / 16);
+            const char  *from = peer + kVHeaderBytes + (poff - w0);
             stream_packs<4>(
-                r.lo, r.hi, [&](size_t i) { return ld_nc16(peer + poff + i * 16); },
+                p0 + r.lo, p0 + r.hi, [&](size_t i) { return ld_nc16(from + i * 16); },
                 [&](size_t i, uint4 v) { store_bytes(out, i, bytes, al, v); });
         }
     }
+    if (rounds > 1) block_barrier(w, s);
     self_end(w, s);
 }
 
@@ -859,11 +903,15 @@ xccl_status_t launch_alltoall(const World &w, const Call &c, const LaunchCfg &cf
 xccl_status_t launch_alltoallv(const World &w, const Call &c, size_t max_src_bytes, const LaunchCfg &cfg,
                                cudaStream_t stream)
 {
-    // every segment is rounded up to a pack; the whole exchange must fit one workspace half
-    size_t need = kVHeaderBytes + max_src_bytes + (size_t)w.size * 16;
-    if (need > w.ws_bytes / 2) return XCCL_ERR_BUFFER_TOO_SMALL;
-    auto k      = alltoallv_kernel;
-    int  blocks = pick_blocks(k, w, cfg, (max_src_bytes + 15) / 16, 2);
+    // The kernel walks the exchange in windows of one workspace half, so any counts are served. Block b of a rank
+    // meets block b of every peer, so all ranks must launch the same grid although their byte counts differ:
+    // the grid never depends on the counts.
+    (void)max_src_bytes;
+    if (w.ws_bytes / 2 < kVHeaderBytes + 4096) return XCCL_ERR_BUFFER_TOO_SMALL;
+    auto      k = alltoallv_kernel;
+    LaunchCfg fixed = cfg;
+    if (fixed.blocks <= 0) fixed.blocks = cfg.max_blocks;
+    int blocks = pick_blocks(k, w, fixed, 0, 2);
     return launch(k, dim3((unsigned)blocks, (unsigned)w.n_local), dim3((unsigned)cfg.threads), cfg.cooperative, stream,
                   w, c);
 }

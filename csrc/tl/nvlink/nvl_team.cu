@@ -81,6 +81,8 @@ public:
     xccl_status_t wait() override;
     xccl_status_t finalize() override { return in_flight_ ? XCCL_INPROGRESS : XCCL_OK; }
     double        elapsed_us() override { return elapsed_us_; }
+    bool          in_flight() const { return in_flight_; }
+    cudaEvent_t   done_event() const { return done_; }
 
 private:
     xccl_status_t complete();
@@ -206,10 +208,33 @@ public:
     HostStatus      *status_host = nullptr;
     cudaStream_t     stream = nullptr;
     int              phase  = 0;  // workspace halves consumed so far
+    // All requests of the team share the workspace, the signal pads and the epoch counters, so their kernels
+    // must run in post order. Posts on one stream are ordered by it; when a post arrives on another stream it
+    // first waits for the event of the last post that may still be running.
+    NvlReq          *last_req    = nullptr;
+    cudaStream_t     last_stream = nullptr;
+    xccl_status_t    order_after_last_post(cudaStream_t s);
+    void             posted(NvlReq *r, cudaStream_t s)
+    {
+        last_req    = r;
+        last_stream = s;
+    }
 };
+
+xccl_status_t NvlTeam::order_after_last_post(cudaStream_t s)
+{
+    if (last_req != nullptr && last_stream != s && last_req->in_flight()) {
+        XCCL_CUDA_CHECK(cudaStreamWaitEvent(s, last_req->done_event(), 0));
+    }
+    return XCCL_OK;
+}
 
 NvlReq::~NvlReq()
 {
+    if (team_->last_req == this) {
+        // a request is only finalized when it is no longer in flight, so nothing is left to order after
+        team_->last_req = nullptr;
+    }
     if (done_ != nullptr) cudaEventDestroy(done_);
     if (start_ != nullptr) cudaEventDestroy(start_);
     if (vmeta_ != nullptr) cudaFree(vmeta_);
@@ -396,8 +421,9 @@ xccl_status_t NvlReq::post()
     cfg.threads    = team_->cfg.threads;
     cfg.max_blocks = team_->cfg.max_blocks;
     const xccl_dt_t dt = args_.reduce_info.dt;
+    xccl_status_t st = team_->order_after_last_post(s);
+    if (st != XCCL_OK) return st;
     if (start_ != nullptr) XCCL_CUDA_CHECK(cudaEventRecord(start_, s));
-    xccl_status_t st;
     if (direct_) {
         for (int p = 0; p < team_->size; p++) {
             c.peer_src[p] = peer_src_[p];
@@ -412,6 +438,7 @@ xccl_status_t NvlReq::post()
                 (args_.coll_type == XCCL_ALLREDUCE ? team_->stats.direct_allreduce : team_->stats.direct_other)++;
                 XCCL_CUDA_CHECK(cudaEventRecord(done_, s));
                 in_flight_ = true;
+                team_->posted(this, s);
                 return XCCL_OK;
             }
             if (st != XCCL_ERR_UNSUPPORTED) return st;
@@ -473,6 +500,7 @@ xccl_status_t NvlReq::post()
     if (args_.coll_type != XCCL_ALLREDUCE) team_->stats.other++;
     XCCL_CUDA_CHECK(cudaEventRecord(done_, s));
     in_flight_ = true;
+    team_->posted(this, s);
     return XCCL_OK;
 }
 
@@ -552,6 +580,7 @@ public:
         caps.sync_mem_types = XCCL_BIT(XCCL_MEMORY_TYPE_HOST);
         caps.team_usage     = XCCL_LIB_PARAMS_TEAM_USAGE_HW_COLLECTIVES | XCCL_LIB_PARAMS_TEAM_USAGE_SW_COLLECTIVES;
         caps.reproducible   = XCCL_REPRODUCIBILITY_MODE_REPRODUCIBLE | XCCL_REPRODUCIBILITY_MODE_NON_REPRODUCIBLE;
+        caps.epilogue       = true;  // fused into the kernels' last pass
     }
 
     xccl_status_t open() override { return cuda_available() ? XCCL_OK : XCCL_ERR_NO_RESOURCE; }

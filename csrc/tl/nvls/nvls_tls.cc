@@ -109,6 +109,7 @@ public:
         caps.sync_mem_types = XCCL_BIT(XCCL_MEMORY_TYPE_HOST);
         caps.team_usage     = XCCL_LIB_PARAMS_TEAM_USAGE_HW_COLLECTIVES;
         caps.ctx_mode       = XCCL_TEAM_LIB_CONTEXT_CREATE_MODE_GLOBAL;
+        caps.epilogue       = true;  // the arguments reach the NVLink team unchanged
     }
     xccl_status_t open() override { return cuda_available() ? XCCL_OK : XCCL_ERR_NO_RESOURCE; }
     std::vector<OptField> context_options() const override

@@ -191,6 +191,14 @@ public:
 
     const std::string getBackendName() const override { return "b200xccl"; }
 
+    // True when the team library that serves `coll` on device memory enqueues all of its work on the stream
+    // it is given, so that a later event on that stream stands for completion.
+    bool stream_ordered(xccl_collective_type_t coll) const
+    {
+        xccl_tl_id_t id = xccl_team_coll_tl(team_, coll, XCCL_MEMORY_TYPE_CUDA);
+        return id == XCCL_TL_NVLINK || id == XCCL_TL_NCCL || id == XCCL_TL_SHARP || id == XCCL_TL_HMC;
+    }
+
     // Which team library serves a collective for a memory type (for tests and logs).
     std::string coll_tl(int coll, bool cuda) const
     {
@@ -220,8 +228,15 @@ public:
             xccl_coll_req_h req = nullptr;
             check(xccl_collective_init(&args, &req, team_), "xccl_collective_init");
             check(xccl_collective_post(req), "xccl_collective_post");
-            pending_.push_back(req);
-            reap(false);
+            if (stream_ordered(args.coll_type)) {
+                pending_.push_back(req);
+                reap(false);
+            } else {
+                // a host-progressed team library (the host team staging device buffers, or a composite one):
+                // its result is complete only when test says so, nothing on the stream stands for it
+                check(xccl_collective_wait(req), "xccl_collective_wait");
+                check(xccl_collective_finalize(req), "xccl_collective_finalize");
+            }
             c10::cuda::CUDAStreamGuard guard(comm);
             work->complete();
         } else {
@@ -381,6 +396,143 @@ public:
         return run(a, c10d::OpType::ALLTOALL_BASE, {out}, {in, out});
     }
 
+    // ---- list and coalesced forms, built on the flat ones above. Packing and unpacking copies run on the
+    // caller's current stream; Work::wait orders that stream after the collective.
+    c10::intrusive_ptr<c10d::Work> allreduce_coalesced(std::vector<at::Tensor> &tensors,
+                                                       const c10d::AllreduceCoalescedOptions &opts) override
+    {
+        TORCH_CHECK(!tensors.empty(), "xccl: empty tensor list");
+        c10::intrusive_ptr<c10d::Work> w;
+        for (auto &t : tensors) {
+            std::vector<at::Tensor> one{t};
+            w = allreduce(one, opts);
+        }
+        return w;  // one communication stream: the last one finishing means all have
+    }
+
+    c10::intrusive_ptr<c10d::Work> allgather_into_tensor_coalesced(std::vector<at::Tensor> &outs, std::vector<at::Tensor> &ins,
+                                                                   const c10d::AllgatherOptions &opts) override
+    {
+        TORCH_CHECK(!ins.empty() && outs.size() == ins.size(), "xccl: bad coalesced allgather lists");
+        c10::intrusive_ptr<c10d::Work> w;
+        for (size_t i = 0; i < ins.size(); i++) w = _allgather_base(outs[i], ins[i], opts);
+        return w;
+    }
+
+    c10::intrusive_ptr<c10d::Work> reduce_scatter_tensor_coalesced(std::vector<at::Tensor> &outs, std::vector<at::Tensor> &ins,
+                                                                   const c10d::ReduceScatterOptions &opts) override
+    {
+        TORCH_CHECK(!ins.empty() && outs.size() == ins.size(), "xccl: bad coalesced reduce_scatter lists");
+        c10::intrusive_ptr<c10d::Work> w;
+        for (size_t i = 0; i < ins.size(); i++) w = _reduce_scatter_base(outs[i], ins[i], opts);
+        return w;
+    }
+
+    c10::intrusive_ptr<c10d::Work> reduce_scatter(std::vector<at::Tensor> &outs, std::vector<std::vector<at::Tensor>> &ins,
+                                                  const c10d::ReduceScatterOptions &opts) override
+    {
+        TORCH_CHECK(outs.size() == 1 && ins.size() == 1 && static_cast<int>(ins[0].size()) == getSize(),
+                    "xccl: bad reduce_scatter lists");
+        std::vector<at::Tensor> flat_parts;
+        for (auto &t : ins[0]) flat_parts.push_back(t.reshape({-1}));
+        at::Tensor flat = at::cat(flat_parts);
+        at::Tensor out  = outs[0].is_contiguous() ? outs[0] : at::empty_like(outs[0], at::MemoryFormat::Contiguous);
+        auto       w    = _reduce_scatter_base(out, flat, opts);
+        if (!out.is_same(outs[0])) {
+            w->wait();
+            outs[0].copy_(out);
+        }
+        return w;
+    }
+
+    // gather / scatter as an alltoallv in which only the root receives / sends
+    c10::intrusive_ptr<c10d::Work> gather(std::vector<std::vector<at::Tensor>> &outs, std::vector<at::Tensor> &ins,
+                                          const c10d::GatherOptions &opts) override
+    {
+        TORCH_CHECK(ins.size() == 1, "xccl: one input tensor per gather");
+        const int  n = getSize(), root = static_cast<int>(opts.rootRank);
+        const bool is_root = getRank() == root;
+        TORCH_CHECK(is_root ? (outs.size() == 1 && static_cast<int>(outs[0].size()) == n) : outs.empty(),
+                    "xccl: gather output list must have one tensor per rank on the root and be empty elsewhere");
+        at::Tensor in   = ins[0].contiguous();
+        at::Tensor flat = at::empty({is_root ? static_cast<int64_t>(n) * in.numel() : 1}, in.options());
+        std::vector<int64_t> in_splits(static_cast<size_t>(n), 0), out_splits(static_cast<size_t>(n), 0);
+        in_splits[static_cast<size_t>(root)] = in.numel();
+        if (is_root) std::fill(out_splits.begin(), out_splits.end(), in.numel());
+        at::Tensor src = in.reshape({-1});
+        auto       w   = alltoallv_flat(flat, src, out_splits, in_splits);
+        if (is_root) {
+            w->wait();
+            for (int r = 0; r < n; r++) {
+                at::Tensor &o = outs[0][static_cast<size_t>(r)];
+                o.copy_(flat.narrow(0, r * in.numel(), in.numel()).view_as(o));
+            }
+        }
+        return w;
+    }
+
+    c10::intrusive_ptr<c10d::Work> scatter(std::vector<at::Tensor> &outs, std::vector<std::vector<at::Tensor>> &ins,
+                                           const c10d::ScatterOptions &opts) override
+    {
+        TORCH_CHECK(outs.size() == 1, "xccl: one output tensor per scatter");
+        const int  n = getSize(), root = static_cast<int>(opts.rootRank);
+        const bool is_root = getRank() == root;
+        TORCH_CHECK(is_root ? (ins.size() == 1 && static_cast<int>(ins[0].size()) == n) : ins.empty(),
+                    "xccl: scatter input list must have one tensor per rank on the root and be empty elsewhere");
+        at::Tensor out = outs[0].is_contiguous() ? outs[0] : at::empty_like(outs[0], at::MemoryFormat::Contiguous);
+        at::Tensor flat;
+        if (is_root) {
+            std::vector<at::Tensor> parts;
+            for (auto &t : ins[0]) {
+                TORCH_CHECK(t.numel() == out.numel(), "xccl: scatter tensors must have the output's size");
+                parts.push_back(t.reshape({-1}));
+            }
+            flat = at::cat(parts);
+        } else {
+            flat = at::empty({1}, out.options());
+        }
+        std::vector<int64_t> in_splits(static_cast<size_t>(n), 0), out_splits(static_cast<size_t>(n), 0);
+        out_splits[static_cast<size_t>(root)] = out.numel();
+        if (is_root) std::fill(in_splits.begin(), in_splits.end(), out.numel());
+        at::Tensor dst = out.view({-1});
+        auto       w   = alltoallv_flat(dst, flat, out_splits, in_splits);
+        if (!out.is_same(outs[0])) {
+            w->wait();
+            outs[0].copy_(out);
+        }
+        return w;
+    }
+
+    c10::intrusive_ptr<c10d::Work> alltoall(std::vector<at::Tensor> &outs, std::vector<at::Tensor> &ins,
+                                            const c10d::AllToAllOptions &) override
+    {
+        const int n = getSize();
+        TORCH_CHECK(static_cast<int>(outs.size()) == n && static_cast<int>(ins.size()) == n, "xccl: alltoall lists need one tensor per rank");
+        std::vector<int64_t>    in_splits, out_splits;
+        std::vector<at::Tensor> parts;
+        int64_t                 out_total = 0;
+        for (int r = 0; r < n; r++) {
+            TORCH_CHECK(ins[static_cast<size_t>(r)].scalar_type() == ins[0].scalar_type() &&
+                        outs[static_cast<size_t>(r)].scalar_type() == ins[0].scalar_type(), "xccl: alltoall tensors must share a dtype");
+            in_splits.push_back(ins[static_cast<size_t>(r)].numel());
+            out_splits.push_back(outs[static_cast<size_t>(r)].numel());
+            parts.push_back(ins[static_cast<size_t>(r)].reshape({-1}));
+            out_total += out_splits.back();
+        }
+        at::Tensor src = at::cat(parts);
+        if (src.numel() == 0) src = at::empty({1}, ins[0].options());
+        at::Tensor dst = at::empty({std::max<int64_t>(out_total, 1)}, outs[0].options());
+        auto       w   = alltoallv_flat(dst, src, out_splits, in_splits);
+        w->wait();
+        int64_t off = 0;
+        for (int r = 0; r < n; r++) {
+            at::Tensor &o = outs[static_cast<size_t>(r)];
+            if (o.numel() > 0) o.copy_(dst.narrow(0, off, o.numel()).view_as(o));
+            off += o.numel();
+        }
+        return w;
+    }
+
     c10::intrusive_ptr<c10d::Work> barrier(const c10d::BarrierOptions &) override
     {
         xccl_coll_op_args_t a{};
@@ -409,6 +561,33 @@ public:
     }
 
 private:
+    // element-count splits over flat 1-D tensors
+    c10::intrusive_ptr<c10d::Work> alltoallv_flat(at::Tensor &out, at::Tensor &in, std::vector<int64_t> &out_splits,
+                                                  std::vector<int64_t> &in_splits)
+    {
+        xccl_coll_op_args_t a{};
+        a.buffer_info.src_buffer = in.data_ptr();
+        a.buffer_info.dst_buffer = out.data_ptr();
+        std::vector<uint32_t> sc, sd, dc, dd;
+        uint32_t              so = 0, dof = 0;
+        for (int r = 0; r < getSize(); r++) {
+            sc.push_back(static_cast<uint32_t>(in_splits[static_cast<size_t>(r)]));
+            sd.push_back(so);
+            so += sc.back();
+            dc.push_back(static_cast<uint32_t>(out_splits[static_cast<size_t>(r)]));
+            dd.push_back(dof);
+            dof += dc.back();
+        }
+        a.coll_type                     = XCCL_ALLTOALLV;
+        a.buffer_info.src_counts        = sc.data();
+        a.buffer_info.src_displacements = sd.data();
+        a.buffer_info.dst_counts        = dc.data();
+        a.buffer_info.dst_displacements = dd.data();
+        a.buffer_info.src_datatype      = to_dt(in.scalar_type());
+        a.buffer_info.dst_datatype      = to_dt(out.scalar_type());
+        return run(a, c10d::OpType::ALLTOALL, {out}, {in, out});
+    }
+
     struct PairComm {
         StoreOob               state;
         xccl_oob_collectives_t oob{};

@@ -304,6 +304,45 @@ def test_emu_alltoallv(world4, dev):
         assert torch.equal(dsts[r], want)
 
 
+def test_emu_alltoallv_larger_than_the_workspace(dev):
+    """Uneven counts whose streams are several workspace halves long (and of different length per rank, one rank
+    sending nothing): the kernel walks the exchange in windows and agrees on the number of rounds from the headers."""
+    from xccl_b200.ops.emu import EmuWorld
+    n = 4
+    w = EmuWorld(n, 256 << 10)   # halves of 128 KiB, 8 KiB of it header
+    try:
+        for trial in range(2):   # the second exchange starts on the other workspace half
+            sc = [[(7919 * (s + 1) + 15013 * d + 3 + trial) * (0 if s == 2 else 1) for d in range(n)] for s in range(n)]
+            sc[1][3] = 0
+            srcs, dsts, metas = [], [], []
+            g = torch.Generator(device=dev).manual_seed(5 + trial)
+            for r in range(n):
+                scounts = sc[r]
+                sdispl = [sum(scounts[:d]) for d in range(n)]
+                rcounts = [sc[s][r] for s in range(n)]
+                rdispl = [sum(rcounts[:s]) for s in range(n)]
+                srcs.append(torch.randn(max(sum(scounts), 1), device=dev, generator=g))
+                dsts.append(torch.full((max(sum(rcounts), 1) + 4,), -1.0, device=dev))
+                metas.append(torch.tensor(scounts + sdispl + rcounts + rdispl, dtype=torch.int32, device=dev))
+            assert max(sum(x) for x in sc) * 4 > 3 * (128 << 10)
+            w.alltoallv(srcs, dsts, metas, max(sum(x) for x in sc) * 4)
+            for r in range(n):
+                parts = []
+                for s_ in range(n):
+                    o = sum(sc[s_][:r])
+                    parts.append(srcs[s_][o:o + sc[s_][r]])
+                want = torch.cat(parts)
+                assert torch.equal(dsts[r][:want.numel()], want), (trial, r)
+                assert torch.all(dsts[r][want.numel():] == -1.0)
+            # the workspace parity bookkeeping still holds for what follows
+            a = _ints(n, 3000, torch.float32, dev, seed=trial)
+            b = [torch.empty_like(x) for x in a]
+            w.allreduce(a, b, alg=K.NVLINK_ALG_TWO_SHOT)
+            assert torch.equal(b[3], torch.stack(a).sum(0))
+    finally:
+        w.close()
+
+
 def test_emu_sync_collectives_and_bounded_wait(world4, dev):
     for _ in range(3):
         world4.barrier()

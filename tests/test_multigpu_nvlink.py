@@ -67,15 +67,22 @@ def _rank_main(rank, size, job, tls, nvls):
     # fused scale + cast (gradient averaging), persistent request posted 3 times
     src = torch.randn(100000, device=dev, generator=torch.Generator(device=dev).manual_seed(rank))
     dst = torch.empty(100000, device=dev, dtype=torch.bfloat16)
-    if tls & K.TL_NVLINK:
-        req = team.allreduce(src, dst, scale=1.0 / size, out_dt=K.DT_BFLOAT16, stream=stream)
-        for _ in range(3):
-            req.post().wait()
-        allv = [torch.randn(100000, device=dev, generator=torch.Generator(device=dev).manual_seed(r)) for r in range(size)]
-        want = (torch.stack(allv).double().sum(0) / size).float()
-        torch.testing.assert_close(dst.float(), want, rtol=1e-2, atol=2e-2)
-        out["elapsed_us"] = req.elapsed_us
-        req.finalize()
+    # (the NCCL team applies it with one kernel on the same stream after the library call; a guard band
+    # behind dst shows that nothing wider than the output type was written there)
+    guard = torch.full((100000 + 64,), 7.0, device=dev, dtype=torch.bfloat16)
+    dst = guard[:100000]
+    req = team.allreduce(src, dst, scale=1.0 / size, out_dt=K.DT_BFLOAT16, stream=stream)
+    for _ in range(3):
+        req.post().wait()
+    allv = [torch.randn(100000, device=dev, generator=torch.Generator(device=dev).manual_seed(r)) for r in range(size)]
+    want = (torch.stack(allv).double().sum(0) / size).float()
+    torch.testing.assert_close(dst.float(), want, rtol=1e-2, atol=2e-2)
+    assert torch.all(guard[100000:] == 7.0)
+    out["elapsed_us"] = req.elapsed_us
+    req.finalize()
+    buf = src.clone()
+    team.allreduce("in_place", buf, scale=1.0 / size, stream=stream).run().finalize()
+    torch.testing.assert_close(buf, want, rtol=1e-5, atol=1e-5)
     # the other collectives
     per = 4099
     src = _vals(rank, per, torch.int32, seed=3).to(dev)
@@ -156,6 +163,36 @@ def _rank_main(rank, size, job, tls, nvls):
         assert team.coll_tl(K.BARRIER, K.MEM_HOST) == K.TL_NVLINK
         for _ in range(3):
             team.barrier().run().finalize()
+    if tls & K.TL_NVLINK:
+        # posts that alternate between two streams without a host wait in between: the team orders them, so every
+        # rank runs the same sequence of kernels on the shared workspace and pads
+        s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+        torch.cuda.synchronize()
+        xs = [_vals(rank, 50000 + i, torch.float32, seed=40 + i).to(dev) for i in range(6)]
+        ys = [torch.zeros_like(x) for x in xs]
+        reqs = [team.allreduce(xs[i], ys[i], stream=(s1 if i % 2 == 0 else s2).cuda_stream,
+                               alg=(K.NVLINK_ALG_ONE_SHOT if i % 3 == 0 else K.NVLINK_ALG_TWO_SHOT)) for i in range(6)]
+        for _ in range(3):
+            for r_ in reqs:
+                r_.post()
+        for r_ in reqs:
+            r_.wait()
+        for i in range(6):
+            want = torch.stack([_vals(r, 50000 + i, torch.float32, seed=40 + i) for r in range(size)]).sum(0)
+            assert torch.equal(ys[i].cpu(), want), ("two streams", i)
+            reqs[i].finalize()
+        out["two_streams"] = "ok"
+        # alltoallv several times larger than the workspace (32 MiB: halves of 16 MiB), uneven counts
+        cnt = [(3 << 20) + 1001 * ((rank + 2 * d) % size) for d in range(size)]   # fp32 elements to each peer
+        rcnt = [(3 << 20) + 1001 * ((s_ + 2 * rank) % size) for s_ in range(size)]
+        src = torch.cat([torch.full((cnt[d],), float(100 * rank + d), device=dev) for d in range(size)])
+        dst = torch.zeros(sum(rcnt), device=dev)
+        sd = [sum(cnt[:d]) for d in range(size)]
+        rd = [sum(rcnt[:s_]) for s_ in range(size)]
+        team.alltoallv(src, cnt, sd, dst, rcnt, rd, stream=stream).run().finalize()
+        for s_ in range(size):
+            assert torch.all(dst[rd[s_]:rd[s_] + rcnt[s_]] == float(100 * s_ + rank)), ("alltoallv", s_)
+        out["big_alltoallv"] = "ok"
     torch.cuda.synchronize()
     team.close()
     ctx.close()

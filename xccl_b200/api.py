@@ -287,29 +287,37 @@ class Team:
         count = numel_of(dst if isinstance(src, str) else src) if count is None else count
         a = self._args(K.ALLREDUCE, src, dst, count * K.DT_SIZE[dt], alg, stream, keep)
         a.reduce_info.dt, a.reduce_info.op, a.reduce_info.count = dt, op, count
+        self._epilogue(a, scale, out_dt)
+        return Request(self, a, tuple(keep))
+
+    @staticmethod
+    def _epilogue(a, scale: Optional[float], out_dt: Optional[int]) -> None:
         if scale is not None or out_dt is not None:
             a.field_mask |= K.ARGS_FIELD_EPILOGUE
             a.epilogue.scale = 1.0 if scale is None else scale
             a.epilogue.out_dt = K.DT_UNSUPPORTED if out_dt is None else out_dt
-        return Request(self, a, tuple(keep))
 
     def reduce(self, src: Any, dst: Any, root: int, op: int = K.OP_SUM, count: Optional[int] = None,
-               dt: Optional[int] = None, alg: Optional[int] = None, stream: Any = None) -> Request:
+               dt: Optional[int] = None, alg: Optional[int] = None, stream: Any = None,
+               scale: Optional[float] = None, out_dt: Optional[int] = None) -> Request:
         keep: list = []
         dt = dtype_of(src) if dt is None else dt
         count = numel_of(src) if count is None else count
         a = self._args(K.REDUCE, src, dst, count * K.DT_SIZE[dt], alg, stream, keep)
         a.reduce_info.dt, a.reduce_info.op, a.reduce_info.count = dt, op, count
         a.root = root
+        self._epilogue(a, scale, out_dt)
         return Request(self, a, tuple(keep))
 
     def reduce_scatter(self, src: Any, dst: Any, op: int = K.OP_SUM, dt: Optional[int] = None,
-                       stream: Any = None, alg: Optional[int] = None) -> Request:
+                       stream: Any = None, alg: Optional[int] = None,
+                       scale: Optional[float] = None, out_dt: Optional[int] = None) -> Request:
         keep: list = []
         dt = dtype_of(src) if dt is None else dt
         a = self._args(K.REDUCE_SCATTER, src, dst, nbytes_of(src), alg, stream, keep)
         a.reduce_info.dt, a.reduce_info.op = dt, op
         a.reduce_info.count = numel_of(src) // self.size
+        self._epilogue(a, scale, out_dt)
         return Request(self, a, tuple(keep))
 
     def bcast(self, buf: Any, root: int, nbytes: Optional[int] = None, alg: Optional[int] = None,
