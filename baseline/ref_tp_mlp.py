@@ -32,6 +32,8 @@ class RefTpMlp:
         self._stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
         sp = C.addressof(self._stream)
         self.req_ag = self.req_a2a = None
+        self._stage = self._rd_stream = None
+        self._steps = 0
         if tp > 1:
             self.req_ag = session.collective(R.ALLGATHER, self.x_shard.data_ptr(), self.xg.data_ptr(),
                                              length=tokens * hidden * 2, stream_handle_ptr=sp)
@@ -57,6 +59,31 @@ class RefTpMlp:
         self.x_shard.copy_(x_pinned, non_blocking=True)
         y = self.forward()
         return torch.linalg.vector_norm(y, dtype=torch.float32).cpu().square() / y.numel()
+
+    def forward_from_host_full(self, x_pinned: torch.Tensor, y_pinned: list) -> None:
+        """The step with the whole output shard read back to pinned memory (two buffers, the read of step i on a
+        copy stream under the kernels of step i+1: the same overlap every arm of the benchmark uses)."""
+        if self._stage is None:
+            like = torch.empty(self.tokens // self.tp, self.hidden, dtype=torch.bfloat16, device=self.x_shard.device)
+            self._stage = [like, torch.empty_like(like)]
+            self._rd_stream = torch.cuda.Stream()
+            self._free = [torch.cuda.Event(), torch.cuda.Event()]
+        k = self._steps & 1
+        self._steps += 1
+        main = torch.cuda.current_stream()
+        main.wait_event(self._free[k])
+        self.x_shard.copy_(x_pinned, non_blocking=True)
+        self._stage[k].copy_(self.forward(), non_blocking=True)
+        done = torch.cuda.Event()
+        done.record(main)
+        with torch.cuda.stream(self._rd_stream):
+            self._rd_stream.wait_event(done)
+            y_pinned[k].copy_(self._stage[k], non_blocking=True)
+            self._free[k].record(self._rd_stream)
+
+    def wait_outputs(self) -> None:
+        if self._rd_stream is not None:
+            self._rd_stream.synchronize()
 
     def close(self) -> None:
         torch.cuda.synchronize()

@@ -20,9 +20,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
-import statistics
 import sys
-import threading
 import time
 import uuid
 
@@ -30,84 +28,17 @@ TOKENS, HIDDEN, FFN = 8192, 8192, 28672
 METRIC = "tp_mlp_step_tokens_per_s"
 
 
-class ClockSampler:
-    """Samples SM clocks and throttle reasons of one GPU through NVML (read-only queries) from a
-    thread of this process, every few milliseconds, while a region runs."""
+try:
+    from xccl_b200.bench.clocks import ClockSampler
+except Exception:  # the reference arm runs even where the package cannot be imported
+    ClockSampler = None
 
-    PERIOD_S = 0.004
 
-    def __init__(self, index: int):
-        self.index, self.samples, self.handle, self.nv = index, [], None, None
-        self._stop = threading.Event()
-        self.thread = None
-
-    def start(self) -> None:
-        try:
-            import pynvml as nv
-            nv.nvmlInit()
-            try:
-                import torch
-                uuid = str(torch.cuda.get_device_properties(self.index).uuid)
-                self.handle = nv.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
-            except Exception:
-                self.handle = nv.nvmlDeviceGetHandleByIndex(self.index)
-            self.nv = nv
-        except Exception:
-            self.nv = None
-            return
-        self.thread = threading.Thread(target=self._run, daemon=True)
-        self.thread.start()
-
-    def _sample(self) -> None:
-        nv = self.nv
-        try:
-            sm = nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)
-            reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle) if hasattr(
-                nv, "nvmlDeviceGetCurrentClocksEventReasons") else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
-            try:
-                watts = nv.nvmlDeviceGetPowerUsage(self.handle) / 1000.0
-            except Exception:
-                watts = None
-            self.samples.append((time.monotonic(), sm, int(reasons), watts))
-        except Exception:
-            pass
-
-    def _run(self) -> None:
-        while not self._stop.is_set():
-            self._sample()
-            time.sleep(self.PERIOD_S)
-
-    def mark_begin(self) -> None:
-        self.t0 = time.monotonic()
-
-    def mark_end(self) -> None:
-        self.t1 = time.monotonic()
-
-    def stop(self) -> dict:
-        if self.nv is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml unavailable"]}
-        self._stop.set()
-        self.thread.join(timeout=2)
-        nv = self.nv
-        try:
-            smax = nv.nvmlDeviceGetMaxClockInfo(self.handle, nv.NVML_CLOCK_SM)
-        except Exception:
-            smax = None
-        masks = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
-        t0, t1 = getattr(self, "t0", 0.0), getattr(self, "t1", float("inf"))
-        sm, reasons, watts = [], set(), []
-        for ts, mhz, bits, w in self.samples:
-            if ts < t0 or ts > t1:
-                continue
-            sm.append(mhz)
-            if w is not None:
-                watts.append(w)
-            for name, m in masks.items():
-                if bits & m:
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_min_mhz": min(sm) if sm else None,
-                "sm_max_mhz": smax, "samples": len(sm), "power_w": statistics.median(watts) if watts else None,
-                "reasons": sorted(reasons)}
+class _NoClocks:
+    def start(self): pass
+    def mark_begin(self): pass
+    def mark_end(self): pass
+    def stop(self): return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["clock sampler unavailable"]}
 
 
 def reference_unavailable(why: str) -> None:
@@ -182,8 +113,10 @@ def main() -> None:
         model = RefTpMlp(TOKENS, HIDDEN, FFN, tp=world, rank=rank, session=ref_session)
         model.x_shard.copy_(torch.randn(TOKENS // world, HIDDEN, device=dev).to(torch.bfloat16))
         xp = torch.randn(TOKENS // world, HIDDEN).to(torch.bfloat16).pin_memory()
+        yp = [torch.empty(TOKENS // world, HIDDEN, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
         step = lambda: model.forward()                 # noqa: E731
         e2e_step = lambda: model.forward_from_host(xp)  # noqa: E731
+        full_step = lambda: model.forward_from_host_full(xp, yp)  # noqa: E731
         launches_per_step = 0
     elif args.impl == "xccl":
         from xccl_b200.models.tp_mlp import TpMlp, TpMlpFp8
@@ -195,29 +128,76 @@ def main() -> None:
         model = (TpMlpFp8 if args.dtype == "fp8" else TpMlp)(TOKENS, HIDDEN, FFN, tp=world, rank=rank, oob=oob)
         x_dev = [torch.randn(TOKENS // world, HIDDEN, device=dev).to(torch.bfloat16)]
         x_pin = [torch.randn(TOKENS // world, HIDDEN).to(torch.bfloat16).pin_memory()]
+        y_pin = [[torch.empty(TOKENS // world, HIDDEN, dtype=torch.bfloat16).pin_memory()] for _ in range(2)]
         step = lambda: model.forward(x_dev)           # noqa: E731
         e2e_step = lambda: model.forward_from_host(x_pin)  # noqa: E731
+        full_step = lambda: model.forward_from_host_full(x_pin, y_pin)  # noqa: E731
         launches_per_step = 4 if args.dtype == "fp8" else 2
     else:
         from xccl_b200.models.tp_mlp import TorchTpMlp
         model = TorchTpMlp(TOKENS, HIDDEN, FFN, tp=world, rank=rank)
         xd = torch.randn(TOKENS // world, HIDDEN, device=dev).to(torch.bfloat16)
         xp = torch.randn(TOKENS // world, HIDDEN).to(torch.bfloat16).pin_memory()
+        yp = [torch.empty(TOKENS // world, HIDDEN, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
         step = lambda: model.forward(xd)               # noqa: E731
         e2e_step = lambda: model.forward_from_host(xp)  # noqa: E731
+        full_step = lambda: model.forward_from_host_full(xp, yp)  # noqa: E731
         launches_per_step = 0
 
-    def timed(fn, n: int) -> float:
+    def timed(fn, n: int, after=None) -> float:
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(n):
             fn()
+        if after is not None:
+            after()    # work the steps left on other streams joins the timed stream before the closing event
         e1.record()
         barrier()
         return max_over_ranks(e0.elapsed_time(e1))
 
-    sampler = ClockSampler(local_rank)
+    def numerics_check() -> bool:
+        """One output shard against the plain fp32 statement of the block on a sample of its rows (the block is
+        row-wise, so a rank's output rows depend on its own input rows and on the full weights, which every rank
+        can rebuild from the seeds). Outside every timed region."""
+        from xccl_b200.models.tp_mlp import _init_weights
+        y = model.forward(x_dev)[0]
+        torch.cuda.synchronize()
+        model.check_error()
+        rows = torch.arange(0, TOKENS // world, max(1, TOKENS // world // 48), device=dev)[:48]
+        xs = x_dev[0][rows].float()
+        want = torch.zeros(rows.numel(), HIDDEN, device=dev, dtype=torch.float32)
+        for r in range(world):
+            wg, wu, wd = _init_weights(TOKENS, HIDDEN, FFN, world, r, dev)
+            h = torch.nn.functional.silu(xs @ wg.float().t()) * (xs @ wu.float().t())
+            want += h.to(torch.bfloat16).float() @ wd.float().t()
+            del wg, wu, wd, h
+        err = float((y[rows].float() - want).abs().max())
+        tol = 3e-2 if args.dtype == "bf16" else 1.5e-1
+        ok = torch.tensor([1.0 if err <= tol + tol * float(want.abs().max()) else 0.0], device=dev)
+        if world > 1:
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        return bool(ok.item() == 1.0), err
+
+    def split_times(n: int = 10) -> dict:
+        """Device time of each of the two launches of a step, and of the same two GEMM shapes without
+        communication, each timed alone over n launches (max over ranks). Outside the headline region."""
+        from xccl_b200.ops import gemm as G
+        f_local = FFN // world
+        out = {}
+        model.forward(x_dev)
+        out["ag_gemm_swiglu_ms"] = timed(lambda: model.ws.ag_gemm_swiglu(model.w_gate, model.w_up, model.h), n) / n
+        out["gemm_rs_ms"] = timed(lambda: model.ws.gemm_rs(model.h, model.w_down, model.y), n) / n
+        xa = torch.randn(TOKENS, HIDDEN, device=dev).to(torch.bfloat16)
+        hh = torch.empty(TOKENS, f_local, device=dev, dtype=torch.bfloat16)
+        yy = torch.empty(TOKENS, HIDDEN, device=dev, dtype=torch.bfloat16)
+        G.gemm_swiglu(xa, model.w_gate[0], model.w_up[0], out=hh)
+        out["gemm_swiglu_no_comm_ms"] = timed(lambda: G.gemm_swiglu(xa, model.w_gate[0], model.w_up[0], out=hh), n) / n
+        G.gemm_bf16(hh, model.w_down[0], out=yy)
+        out["gemm_down_no_comm_ms"] = timed(lambda: G.gemm_bf16(hh, model.w_down[0], out=yy), n) / n
+        return out
+
+    sampler = ClockSampler(local_rank) if ClockSampler is not None else _NoClocks()
     sampler.start()  # nvidia-smi needs a moment to start: launch it before the warm-up
     for _ in range(args.warmup):
         step()
@@ -237,6 +217,23 @@ def main() -> None:
     if args.impl == "xccl":
         model.check_error()
 
+    # second end-to-end figure: the same step with the whole output shard read back to pinned host memory
+    for _ in range(3):
+        full_step()
+    model.wait_outputs()
+    full_ms = timed(full_step, args.steps, after=lambda: torch.cuda.current_stream().wait_stream(
+        model._d2h_stream if args.impl == "xccl" else (model._reader.stream if args.impl == "torch" else model._rd_stream)))
+    model.wait_outputs()
+    if args.impl == "xccl":
+        model.check_error()
+    extra = {}
+    if args.impl == "xccl" and args.dtype == "bf16":
+        ok, err = numerics_check()
+        extra["numerics_ok"] = ok
+        extra["numerics_max_abs_err"] = err
+        extra["split"] = split_times()
+        model.check_error()
+
     ms_per_step = ms_total / args.steps
     value = TOKENS / (ms_per_step * 1e-3)
     e2e_value = TOKENS / (max(e2e_ms, 1e-9) / args.steps * 1e-3)
@@ -252,7 +249,14 @@ def main() -> None:
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                     "wall_ms_per_step": wall_ms / args.steps,
-                    "h2d_bytes_per_step": TOKENS // world * HIDDEN * 2, "d2h_bytes_per_step": 4},
+                    "h2d_bytes_per_step": TOKENS // world * HIDDEN * 2, "d2h_bytes_per_step": 4,
+                    "result": "scalar metric of the output shard (mean of squares)"},
+            "e2e_full_output": {"value": TOKENS / (max(full_ms, 1e-9) / args.steps * 1e-3), "unit": "tokens/s",
+                                "ms_per_step": full_ms / args.steps,
+                                "h2d_bytes_per_step": TOKENS // world * HIDDEN * 2,
+                                "d2h_bytes_per_step": TOKENS // world * HIDDEN * 2,
+                                "result": "the whole output shard, read to pinned memory under the next step's kernels"},
+            **extra,
             "gpu_launches": launches_per_step * args.steps,
             "tflops_per_gpu": 6.0 * TOKENS * HIDDEN * FFN / world / (ms_per_step * 1e-3) / 1e12,
         }

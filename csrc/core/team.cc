@@ -175,6 +175,26 @@ xccl_status_t xccl_team_query(xccl_team_h team, int *rank, int *size)
     return XCCL_OK;
 }
 
+xccl_status_t xccl_team_mem_alloc(xccl_team_h team, size_t bytes, void **ptr)
+{
+    if (team == nullptr || ptr == nullptr || bytes == 0 || !team->created) return XCCL_ERR_INVALID_PARAM;
+    for (auto &tt : team->tl_teams) {
+        xccl_status_t st = tt->sym_alloc(bytes, ptr);
+        if (st != XCCL_ERR_NOT_IMPLEMENTED) return st;
+    }
+    return XCCL_ERR_NOT_IMPLEMENTED;
+}
+
+xccl_status_t xccl_team_mem_free(xccl_team_h team, void *ptr)
+{
+    if (team == nullptr || ptr == nullptr) return XCCL_ERR_INVALID_PARAM;
+    for (auto &tt : team->tl_teams) {
+        xccl_status_t st = tt->sym_free(ptr);
+        if (st != XCCL_ERR_NOT_IMPLEMENTED && st != XCCL_ERR_NO_ELEM) return st;
+    }
+    return XCCL_ERR_NO_ELEM;
+}
+
 xccl_tl_id_t xccl_team_coll_tl(xccl_team_h team, xccl_collective_type_t coll, xccl_memory_type_t mem)
 {
     if (team == nullptr || !team->created || coll >= XCCL_COLL_LAST || mem >= XCCL_MEMORY_TYPE_LAST) return XCCL_TL_NULL;

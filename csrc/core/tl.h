@@ -48,6 +48,9 @@ public:
     virtual xccl_status_t collective_init(const xccl_coll_op_args_t &args, xccl_memory_type_t mem,
                                           xccl_coll_req **req) = 0;
     virtual xccl_status_t mem_map_start(const xccl_mem_map_params_t &, xccl_mem_handle **) { return XCCL_ERR_NOT_IMPLEMENTED; }
+    // symmetric device memory (xccl_team_mem_alloc / xccl_team_mem_free), collective over the team
+    virtual xccl_status_t sym_alloc(size_t, void **) { return XCCL_ERR_NOT_IMPLEMENTED; }
+    virtual xccl_status_t sym_free(void *) { return XCCL_ERR_NOT_IMPLEMENTED; }
     // false until the TL team can no longer make progress after an error (bounded wait expired)
     bool       poisoned = false;
     TlContext *ctx      = nullptr;

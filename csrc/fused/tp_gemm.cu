@@ -267,7 +267,28 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
             __nv_bfloat16 *out;
             size_t         ld;
             int            row0;
-            if (p.comm == COMM_REDUCE_SCATTER_C) {
+            // reduce-scatter, tiles of my own rows (walked last): the partial tiles of the other ranks for these
+            // rows are already in my partial buffer, so the epilogue adds them to the accumulator and writes the
+            // final value - no pass over the partials after the last tile
+            const bool     own_rs = (p.comm == COMM_REDUCE_SCATTER_C) && p.rs_fused != 0 && tl.shard == rank;
+            const __nv_bfloat16 *rs_parts = nullptr;
+            size_t               rs_slot  = 0;
+            if (own_rs) {
+                const size_t shard_rows = (size_t)mbs * kBM;
+                rs_slot  = shard_rows * (size_t)p.N;
+                rs_parts = p.part[rank] + (size_t)(p.seq & 1) * p.tp_size * rs_slot;
+                out      = p.C[local];
+                ld       = (size_t)p.ldc;
+                row0     = (tl.mb - tl.shard * mbs) * kBM;
+                // every other rank has sent all column tiles of this row block (bounded wait, one source per lane)
+                int good = 1;
+                if (lane < p.tp_size && lane != rank) {
+                    const uint32_t *ctr = p.pad[rank] + nvl::kPadCounterOff + ((p.seq & 1) * p.tp_size + lane) * 64 +
+                                          (tl.mb - tl.shard * mbs);
+                    good = wait_counter(ctr, p.rs_target, true, ab, 6) ? 1 : 0;
+                }
+                if (!__all_sync(0xffffffffu, good)) break;
+            } else if (p.comm == COMM_REDUCE_SCATTER_C) {
                 // slot `rank` of the owner's partial buffer, parity by launch sequence
                 const size_t shard_rows = (size_t)mbs * kBM;
                 out  = p.part[tl.shard] + ((size_t)(p.seq & 1) * p.tp_size + rank) * shard_rows * (size_t)p.N;
@@ -317,6 +338,34 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
                     const int grow = quarter * 32 + r, gcol = col0 + chunk * 8;
                     if (grow < rows_valid && gcol < n_out) {
                         uint4 v = *reinterpret_cast<const uint4 *>(stage + r * kStageRowBytes + chunk * 16);
+                        if (own_rs) {
+                            // sum of the tp partials in rank order, every one rounded to bf16 exactly as it would
+                            // have travelled; all loads are issued before the first add
+                            const size_t off = (size_t)(row0 + grow) * (size_t)p.N + gcol;
+                            uint4        raw[kMaxTpRanks];
+#pragma unroll
+                            for (int src = 0; src < kMaxTpRanks; src++) {
+                                if (src < p.tp_size && src != rank) raw[src] = nvl::ld_nc16(rs_parts + (size_t)src * rs_slot + off);
+                            }
+                            float acc[8];
+#pragma unroll
+                            for (int e = 0; e < 8; e++) acc[e] = 0.0f;
+#pragma unroll
+                            for (int src = 0; src < kMaxTpRanks; src++) {
+                                if (src < p.tp_size) {
+                                    const uint4           x = (src == rank) ? v : raw[src];
+                                    const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&x);
+#pragma unroll
+                                    for (int e = 0; e < 4; e++) {
+                                        const float2 f = __bfloat1622float2(h2[e]);
+                                        acc[2 * e] += f.x;
+                                        acc[2 * e + 1] += f.y;
+                                    }
+                                }
+                            }
+                            v = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                                           pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+                        }
                         uint4 *dstp = reinterpret_cast<uint4 *>(out + (size_t)(row0 + grow) * ld + gcol);
                         if (p.st_stream) {
                             __stcs(dstp, v);
@@ -336,7 +385,7 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
                     mbar_arrive(tmem_empty_bar(a));
                 }
             }
-            if (p.comm == COMM_REDUCE_SCATTER_C) {
+            if (p.comm == COMM_REDUCE_SCATTER_C && !own_rs) {
                 // all four epilogue warps have stored their rows: tell the owner one more tile arrived
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (warp == 2 && lane == 0) {
@@ -364,7 +413,8 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
     }
 
     // ---- reduce-scatter: add up the partial tiles that every rank stored for my rows
-    if (p.comm == COMM_REDUCE_SCATTER_C && *abort_slot == 0) rs_reduce_phase(p, rank, local, tiles_m128, ab);
+    // (only when the reduce is not fused into the epilogue of the local tiles)
+    if (p.comm == COMM_REDUCE_SCATTER_C && p.rs_fused == 0 && *abort_slot == 0) rs_reduce_phase(p, rank, local, tiles_m128, ab);
 }
 
 }  // namespace

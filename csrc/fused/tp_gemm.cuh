@@ -49,6 +49,8 @@ struct GemmParams {
     unsigned  sync_budget_ns;
     uint32_t seq;         // launch sequence number (starts at 1): readiness counters and buffer parity follow it
     uint32_t rs_target;   // reduce-scatter: running total of tiles per (source, row block) for this parity
+    int      rs_fused;    // reduce-scatter: 1 = the tiles of the local rows (walked last) add the other ranks' partial
+                          // tiles in their epilogue and write the result; 0 = a reduce phase after the last tile
     unsigned long long budget_ns;
     uint32_t *error;      // device word, 0 = fine
     int ldc;              // leading dimension of the output in elements

@@ -34,6 +34,7 @@ struct TpWorkspace {
     size_t    off_xg = 0, off_part = 0, total = 0;
     uint32_t  seq_ag = 0, seq_rs = 0, rs_count[2] = {0, 0};
     int       copy_ctas = 16;
+    bool      rs_fused  = true;   // XCCL_TP_RS_FUSED=0: separate reduce phase after the last tile
     // input rows arriving from the host while the allgather->GEMM kernel already runs
     uint32_t   *in_flags[kMaxTpRanks] = {nullptr};  // per LOCAL rank: one word per chunk of in_rows rows
     uint32_t    in_seq = 0;
@@ -106,6 +107,8 @@ xccl_status_t xccl_tp_ws_create(const xccl_oob_collectives_t *oob, int emu_ranks
     w->N_rs = N_rs;
     const char *cc = std::getenv("XCCL_TP_COPY_CTAS");
     if (cc != nullptr && std::atoi(cc) > 0) w->copy_ctas = std::atoi(cc);
+    const char *rf = std::getenv("XCCL_TP_RS_FUSED");
+    if (rf != nullptr) w->rs_fused = std::atoi(rf) != 0;
     layout(w);
     xccl_status_t st = XCCL_OK;
     if (oob == nullptr) {
@@ -312,6 +315,7 @@ xccl_status_t xccl_tp_gemm_rs(xccl_tp_ws_h w, const void *const *Hin, const void
     const int tiles_n = (p.N + kBN - 1) / kBN;
     w->rs_count[p.seq & 1] += (uint32_t)tiles_n;
     p.rs_target = w->rs_count[p.seq & 1];
+    p.rs_fused  = w->rs_fused ? 1 : 0;
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

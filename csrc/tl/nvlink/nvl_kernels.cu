@@ -641,6 +641,60 @@ template <int KIND> __global__ void __launch_bounds__(512) direct_mover_kernel(W
     self_end(w, s);
 }
 
+// ------------------------------------------------------------------ symmetric memory: NVLS in place
+// The buffers live in allocations of xccl_team_mem_alloc, at the same offset on every rank, and are addressed
+// through the multicast mapping. allreduce: rank r owns 1/N of the packs; one multimem.ld_reduce per pack makes the
+// switch fetch and add that pack from all N source buffers, one multimem.st writes the (scaled) sum into all N
+// destination buffers. Every byte crosses each GPU's links once in each direction and nothing is staged. In place is
+// safe: a pack is read and written by one thread of one rank. bcast: the root streams its source through
+// multimem.st into every destination.
+template <typename T> __global__ void __launch_bounds__(512) symmetric_allreduce_kernel(World w, Call c)
+{
+    constexpr int E = Epp<T>::value;
+    Self          s = self_begin(w);
+    const size_t  npacks = c.count / E;
+    const char   *src = (const char *)c.mc_src[s.local];
+    char         *dst = (char *)c.mc_dst[s.local];
+    block_barrier(w, s);  // the same block of every peer has started: the peers' streams have produced their sources
+    if (!s.failed) {
+        const size_t per = (npacks + w.size - 1) / w.size;
+        const size_t lo  = min((size_t)s.rank * per, npacks), hi = min(lo + per, npacks);
+        const Range  r   = sub_range(Range{lo, hi}, gridDim.x, blockIdx.x);
+        stream_packs<8>(
+            r.lo, r.hi, [&](size_t i) { return nvls_reduce<T>(src + i * 16); },
+            [&](size_t i, uint4 v) {
+                if (c.do_scale) {
+                    auto x = from_raw<T>(v);
+#pragma unroll
+                    for (int e = 0; e < E; e++) x.v[e] = Traits<T>::down(dev::scaled(Traits<T>::up(x.v[e]), c.scale, true));
+                    v = as_raw<T>(x);
+                }
+                mm_st_16(dst + i * 16, v);
+            });
+        block_barrier(w, s);  // every share has been written everywhere; nobody reads a source any more
+    }
+    self_end(w, s);
+}
+
+__global__ void __launch_bounds__(512) symmetric_bcast_kernel(World w, Call c)
+{
+    Self         s = self_begin(w);
+    const size_t npacks = c.len / 16;
+    block_barrier(w, s);  // the destinations may be overwritten: every peer has reached this call
+    if (!s.failed) {
+        if (s.rank == c.root) {
+            const char *src = (const char *)c.src[s.local];
+            char       *dst = (char *)c.mc_dst[s.local];
+            const Range r   = block_range(npacks);
+            stream_packs<8>(
+                r.lo, r.hi, [&](size_t i) { return *reinterpret_cast<const uint4 *>(src + i * 16); },
+                [&](size_t i, uint4 v) { mm_st_16(dst + i * 16, v); });
+        }
+        block_barrier(w, s);
+    }
+    self_end(w, s);
+}
+
 // ------------------------------------------------------------------ synchronisation only
 
 __global__ void sync_kernel(World w, Call c, int kind)
@@ -838,6 +892,39 @@ xccl_status_t launch_direct(const World &w, const Call &c, int coll, xccl_dt_t d
     }
     default: return XCCL_ERR_UNSUPPORTED;
     }
+}
+
+xccl_status_t launch_symmetric(const World &w, const Call &c, int coll, xccl_dt_t dt, const LaunchCfg &cfg, cudaStream_t stream)
+{
+    auto al = [](const void *p) { return ((uintptr_t)p & 15) == 0; };
+    dim3 block((unsigned)cfg.threads);
+    if (coll == XCCL_BCAST) {
+        if (c.len == 0) return XCCL_OK;
+        if (c.len % 16 != 0) return XCCL_ERR_INVALID_PARAM;
+        for (int i = 0; i < w.n_local; i++) {
+            if (c.mc_dst[i] == nullptr || !al(c.mc_dst[i]) || !al(c.src[i])) return XCCL_ERR_INVALID_PARAM;
+        }
+        auto k      = symmetric_bcast_kernel;
+        int  blocks = pick_blocks(k, w, cfg, c.len / 16, 8);
+        return launch(k, dim3((unsigned)blocks, (unsigned)w.n_local), block, cfg.cooperative, stream, w, c);
+    }
+    if (coll != XCCL_ALLREDUCE || !nvls_supported(dt, (xccl_op_t)c.op)) return XCCL_ERR_UNSUPPORTED;
+    if (c.count == 0) return XCCL_OK;
+    if ((c.count * xccl_dt_size(dt)) % 16 != 0) return XCCL_ERR_INVALID_PARAM;
+    for (int i = 0; i < w.n_local; i++) {
+        if (c.mc_src[i] == nullptr || c.mc_dst[i] == nullptr || !al(c.mc_src[i]) || !al(c.mc_dst[i])) return XCCL_ERR_INVALID_PARAM;
+    }
+    const size_t mine = (c.count * xccl_dt_size(dt) / 16 + w.size - 1) / w.size;
+    if (dt == XCCL_DT_FLOAT32) {
+        auto k = symmetric_allreduce_kernel<float>;
+        return launch(k, dim3((unsigned)pick_blocks(k, w, cfg, mine, 8), (unsigned)w.n_local), block, cfg.cooperative, stream, w, c);
+    }
+    if (dt == XCCL_DT_BFLOAT16) {
+        auto k = symmetric_allreduce_kernel<__nv_bfloat16>;
+        return launch(k, dim3((unsigned)pick_blocks(k, w, cfg, mine, 8), (unsigned)w.n_local), block, cfg.cooperative, stream, w, c);
+    }
+    auto k = symmetric_allreduce_kernel<__half>;
+    return launch(k, dim3((unsigned)pick_blocks(k, w, cfg, mine, 8), (unsigned)w.n_local), block, cfg.cooperative, stream, w, c);
 }
 
 bool nvls_supported(xccl_dt_t dt, xccl_op_t op)

@@ -26,9 +26,13 @@ struct Call {
     // mappings of registered buffers in a real team, the plain pointers when ranks are emulated).
     const void     *peer_src[kMaxRanks];
     void           *peer_dst[kMaxRanks];
+    // Symmetric algorithms: the buffers of this call seen through the multicast mapping of the symmetric
+    // allocation they live in (same offset on every rank), by LOCAL rank.
+    const void     *mc_src[kMaxRanks];
+    void           *mc_dst[kMaxRanks];
 };
 
-enum Alg { ALG_AUTO = 0, ALG_ONE_SHOT = 1, ALG_TWO_SHOT = 2, ALG_NVLS = 3, ALG_DIRECT = 4 };
+enum Alg { ALG_AUTO = 0, ALG_ONE_SHOT = 1, ALG_TWO_SHOT = 2, ALG_NVLS = 3, ALG_DIRECT = 4, ALG_SYMMETRIC = 5 };
 
 struct LaunchCfg {
     int  blocks  = 0;      // 0 = choose from the message size
@@ -59,6 +63,10 @@ xccl_status_t launch_alltoallv(const World &w, const Call &c, size_t max_src_byt
 xccl_status_t launch_direct(const World &w, const Call &c, int coll, xccl_dt_t dt, xccl_dt_t out_dt, const LaunchCfg &cfg,
                             cudaStream_t stream);
 bool          direct_shape_ok(int coll, const Call &c, xccl_dt_t dt, int team_size);
+// Zero-copy NVLS on symmetric memory: c.mc_src / c.mc_dst are multicast addresses of the buffers (bcast: mc_dst only,
+// c.src is the root's plain source). coll: XCCL_ALLREDUCE (sum of fp32 / fp16 / bf16, same output type) or XCCL_BCAST.
+// Buffers 16-byte aligned, byte counts multiples of 16.
+xccl_status_t launch_symmetric(const World &w, const Call &c, int coll, xccl_dt_t dt, const LaunchCfg &cfg, cudaStream_t stream);
 // kind: XCCL_BARRIER, XCCL_FANIN or XCCL_FANOUT
 xccl_status_t launch_sync(const World &w, const Call &c, int kind, const LaunchCfg &cfg, cudaStream_t stream);
 // A barrier whose flags nobody sets, with a short budget: reports NVL_TIMEOUT in the status

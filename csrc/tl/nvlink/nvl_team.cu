@@ -34,6 +34,8 @@ struct NvlCfg {
     size_t direct_min    = ~(size_t)0;  // messages from this size register their buffers and skip the workspace
     bool   direct_min_set = false;      // given explicitly: a tuning file does not override it
     bool   direct        = true;
+    bool   symmetric     = true;        // zero-copy NVLS on buffers from xccl_team_mem_alloc
+    size_t symmetric_min = 32u << 10;
     std::string tuning_file;
     int    max_blocks    = 64;
     int    threads       = 512;
@@ -99,6 +101,10 @@ private:
     bool                direct_ = false;
     const void         *peer_src_[kMaxRanks] = {nullptr};
     void               *peer_dst_[kMaxRanks] = {nullptr};
+    // symmetric algorithms: the buffers lie in memory of xccl_team_mem_alloc; their multicast addresses
+    bool                sym_    = false;
+    const void         *mc_src_ = nullptr;
+    void               *mc_dst_ = nullptr;
 };
 
 class NvlTeam final : public TlTeam {
@@ -112,9 +118,10 @@ public:
         }
         // which algorithm served how many posts (log level info): the quickest check of a selection table
         tl_info(tl_, "nvlink team rank %d: allreduce posts one-shot %llu, two-shot %llu, NVLS %llu, direct %llu; other "
-                "collectives %llu (direct %llu)", rank, stats.one_shot, stats.two_shot, stats.nvls, stats.direct_allreduce,
-                stats.other, stats.direct_other);
+                "collectives %llu (direct %llu); on symmetric memory %llu", rank, stats.one_shot, stats.two_shot, stats.nvls,
+                stats.direct_allreduce, stats.other, stats.direct_other, stats.symmetric);
         for (auto &kv : ipc_cache) cudaIpcCloseMemHandle(kv.second);
+        for (SymmetricRegion *r : sym_regions) delete r;
         delete region;
         if (status_host != nullptr) cudaFreeHost(status_host);
     }
@@ -184,6 +191,46 @@ public:
 
     xccl_status_t create_test() override { return XCCL_OK; }
 
+    // Symmetric allocations (xccl_team_mem_alloc): one more region like the workspace, owned by the caller.
+    xccl_status_t sym_alloc(size_t bytes, void **ptr) override
+    {
+        SymmetricRegion *r  = nullptr;
+        xccl_status_t    st = SymmetricRegion::create(oob, bytes, cfg.nvls, &r);
+        if (st != XCCL_OK) return st;
+        sym_regions.push_back(r);
+        *ptr = r->base[(size_t)rank];
+        return XCCL_OK;
+    }
+    xccl_status_t sym_free(void *ptr) override
+    {
+        for (size_t i = 0; i < sym_regions.size(); i++) {
+            if (sym_regions[i]->base[(size_t)rank] == (char *)ptr) {
+                if (stream != nullptr) cudaStreamSynchronize(stream);
+                cudaDeviceSynchronize();
+                // nobody unmaps while a peer may still be inside a collective on this memory
+                int              one = 1;
+                std::vector<int> all((size_t)size);
+                xccl_status_t    st = oob.allgather_blocking(&one, all.data(), sizeof(int));
+                delete sym_regions[i];
+                sym_regions.erase(sym_regions.begin() + (long)i);
+                return st;
+            }
+        }
+        return XCCL_ERR_NO_ELEM;
+    }
+    // The multicast address of [p, p + bytes) when that range lies inside one symmetric allocation bound to the
+    // multicast object; nullptr otherwise.
+    char *mc_address(const void *p, size_t bytes) const
+    {
+        for (const SymmetricRegion *r : sym_regions) {
+            const char *b = r->base[(size_t)rank];
+            if (r->mc_base != nullptr && (const char *)p >= b && (const char *)p + bytes <= b + r->bytes) {
+                return r->mc_base + ((const char *)p - b);
+            }
+        }
+        return nullptr;
+    }
+
     xccl_status_t collective_init(const xccl_coll_op_args_t &args, xccl_memory_type_t, xccl_coll_req **req) override
     {
         auto         *r  = new NvlReq(this, args);
@@ -200,8 +247,9 @@ public:
     NvlCfg           cfg;
     OobGroup         oob;
     std::map<std::string, void *> ipc_cache;
+    std::vector<SymmetricRegion *> sym_regions;
     struct {
-        unsigned long long one_shot = 0, two_shot = 0, nvls = 0, direct_allreduce = 0, other = 0, direct_other = 0;
+        unsigned long long one_shot = 0, two_shot = 0, nvls = 0, direct_allreduce = 0, other = 0, direct_other = 0, symmetric = 0;
     } stats;
     SymmetricRegion *region = nullptr;
     World            world{};
@@ -309,6 +357,26 @@ xccl_status_t NvlReq::prepare()
         break;
     default: break;
     }
+    // Buffers in symmetric memory (same offset on every rank: the caller's contract) need no registration and
+    // no workspace: in-switch reduction and multicast act on them directly.
+    if (team_->cfg.symmetric && !team_->sym_regions.empty()) {
+        void *src = bi.src_buffer, *dst = bi.dst_buffer;
+        if (src == XCCL_IN_PLACE || src == nullptr) src = dst;
+        const bool same_out = !(args_.field_mask & XCCL_COLL_OP_ARGS_FIELD_EPILOGUE) ||
+                              args_.epilogue.out_dt == XCCL_DT_UNSUPPORTED || args_.epilogue.out_dt == XCCL_DT_LAST_PREDEFINED ||
+                              args_.epilogue.out_dt == args_.reduce_info.dt;
+        if (args_.coll_type == XCCL_ALLREDUCE && same_out && msg != 0 && msg % 16 == 0 &&
+            nvls_supported(args_.reduce_info.dt, args_.reduce_info.op) && (((uintptr_t)src | (uintptr_t)dst) & 15) == 0) {
+            mc_src_ = team_->mc_address(src, msg);
+            mc_dst_ = team_->mc_address(dst, msg);
+            sym_    = mc_src_ != nullptr && mc_dst_ != nullptr;
+        } else if (args_.coll_type == XCCL_BCAST && bi.len != 0 && bi.len % 16 == 0 && (((uintptr_t)src | (uintptr_t)dst) & 15) == 0) {
+            mc_dst_ = team_->mc_address(dst, bi.len);
+            sym_    = mc_dst_ != nullptr;
+        }
+        if (sym_) return XCCL_OK;
+    }
+    if (args_.alg.set_by_user && args_.alg.id == ALG_SYMMETRIC) return XCCL_ERR_INVALID_PARAM;  // not symmetric memory
     if (msg != 0 && team_->cfg.direct && (forced || msg >= team_->cfg.direct_min)) {
         void *src = bi.src_buffer, *dst = bi.dst_buffer;
         if (src == XCCL_IN_PLACE || src == nullptr) {
@@ -424,6 +492,25 @@ xccl_status_t NvlReq::post()
     xccl_status_t st = team_->order_after_last_post(s);
     if (st != XCCL_OK) return st;
     if (start_ != nullptr) XCCL_CUDA_CHECK(cudaEventRecord(start_, s));
+    if (sym_) {
+        const size_t bytes = args_.coll_type == XCCL_BCAST ? c.len : c.count * xccl_dt_size(dt);
+        const bool   user  = args_.alg.set_by_user && args_.alg.id != ALG_AUTO;
+        // small reductions stay with the one-shot kernel (one flag round trip less than two barriers)
+        const bool   take  = user ? args_.alg.id == ALG_SYMMETRIC
+                                  : (args_.coll_type == XCCL_BCAST ? bytes >= team_->cfg.symmetric_min
+                                                                   : bytes >= team_->cfg.symmetric_min && bytes > team_->cfg.one_shot_max);
+        if (take) {
+            c.mc_src[0] = mc_src_;
+            c.mc_dst[0] = mc_dst_;
+            st          = launch_symmetric(w, c, (int)args_.coll_type, dt, cfg, s);
+            if (st != XCCL_OK) return st;
+            team_->stats.symmetric++;
+            XCCL_CUDA_CHECK(cudaEventRecord(done_, s));
+            in_flight_ = true;
+            team_->posted(this, s);
+            return XCCL_OK;
+        }
+    }
     if (direct_) {
         for (int p = 0; p < team_->size; p++) {
             c.peer_src[p] = peer_src_[p];
@@ -596,6 +683,8 @@ public:
             {"BCAST_MC_MIN", "0", "Broadcasts from this size go through the NVSwitch multicast mapping when available", OptType::MEMUNITS},
             {"DIRECT", "y", "Register the buffers of large messages with the peers (CUDA IPC) and run zero-copy kernels on them", OptType::BOOL},
             {"DIRECT_MIN", "0", "Messages from this size register their buffers and use the direct (zero-copy) kernels (0: from the tuning file, else only on request; measured crossover 32m-256m)", OptType::MEMUNITS},
+            {"SYMMETRIC", "y", "Run collectives whose buffers come from xccl_team_mem_alloc zero-copy through the multicast mapping", OptType::BOOL},
+            {"SYMMETRIC_MIN", "32k", "Smallest message that takes the symmetric (zero-copy NVLS) path", OptType::MEMUNITS},
             {"TUNING_FILE", "", "Measured thresholds, lines of `team_size one_shot_max nvls_min direct_min` (see bench/collectives.py --table)", OptType::STRING},
             {"MAX_BLOCKS", "128", "Upper bound of thread blocks per collective kernel (at most 128)", OptType::UINT},
             {"THREADS", "512", "Threads per block of the collective kernels", OptType::UINT},
@@ -637,6 +726,8 @@ public:
         if (!c.direct_min_set) c.direct_min = ~(size_t)0;
         c.tuning_file     = cfg.str("TUNING_FILE");
         c.direct          = cfg.flag("DIRECT");
+        c.symmetric       = cfg.flag("SYMMETRIC");
+        c.symmetric_min   = (size_t)cfg.num("SYMMETRIC_MIN");
         c.max_blocks      = std::max(1, std::min((int)cfg.num("MAX_BLOCKS"), kMaxBlocks));
         c.threads         = std::max(32, std::min((int)cfg.num("THREADS"), 512)) / 32 * 32;
         c.wait_timeout_ms = cfg.real("WAIT_TIMEOUT_MS");

@@ -395,7 +395,8 @@ enum xccl_nvlink_alg_id {               /* nvlink team allreduce */
     XCCL_NVLINK_ALG_ONE_SHOT = 1,
     XCCL_NVLINK_ALG_TWO_SHOT = 2,
     XCCL_NVLINK_ALG_NVLS = 3,
-    XCCL_NVLINK_ALG_DIRECT = 4   /* zero-copy kernels on buffers registered with the peers at init */
+    XCCL_NVLINK_ALG_DIRECT = 4,  /* zero-copy kernels on buffers registered with the peers at init */
+    XCCL_NVLINK_ALG_SYMMETRIC = 5 /* in-switch reduction and multicast directly on buffers from xccl_team_mem_alloc */
 };
 
 /* Persistent request life cycle. init captures the arguments; post starts one execution and
@@ -435,6 +436,17 @@ xccl_status_t xccl_global_mem_unmap(xccl_mem_h memh);
 xccl_status_t xccl_team_query(xccl_team_h team, int *rank, int *size);
 /* Which TL serves (coll, memory type) on this team; XCCL_TL_NULL when none does. */
 xccl_tl_id_t  xccl_team_coll_tl(xccl_team_h team, xccl_collective_type_t coll, xccl_memory_type_t mem);
+/* Symmetric device memory (extension; collective over the team: every member calls it with the same
+ * size, in the same order relative to its other collective calls on the team). Each member gets `bytes`
+ * of device memory on its own GPU that every other member has mapped and that is bound to the NVSwitch
+ * multicast object when the fabric offers one. Collectives whose buffers lie in such memory, at the SAME
+ * OFFSET of the allocation on every member, run zero-copy: the in-switch reduction (multimem.ld_reduce)
+ * reads the source buffers in place and the multicast store writes the destinations in place, nothing is
+ * staged through the team's workspace. This is the NVSwitch counterpart of registering user buffers with
+ * the SHARP library. XCCL_ERR_NOT_IMPLEMENTED when no team library of the team offers it. Memory is
+ * returned with xccl_team_mem_free (collective too) or when the team is destroyed. */
+xccl_status_t xccl_team_mem_alloc(xccl_team_h team, size_t bytes, void **ptr);
+xccl_status_t xccl_team_mem_free(xccl_team_h team, void *ptr);
 /* Device time of the last completed execution of a CUDA request in microseconds, or a
  * negative value when the request keeps no timing (host requests, timing disabled). */
 double        xccl_collective_elapsed_us(xccl_coll_req_h request);

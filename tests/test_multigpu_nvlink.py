@@ -193,6 +193,40 @@ def _rank_main(rank, size, job, tls, nvls):
         for s_ in range(size):
             assert torch.all(dst[rd[s_]:rd[s_] + rcnt[s_]] == float(100 * s_ + rank)), ("alltoallv", s_)
         out["big_alltoallv"] = "ok"
+    if (tls & K.TL_NVLINK) and out.get("nvls") == "ok":
+        # symmetric memory: in-switch reduction and multicast straight on the caller's buffers
+        nbytes = 8 << 20
+        mem = team.mem_alloc(2 * nbytes)
+        for dtype in (torch.float32, torch.bfloat16):
+            es = torch.tensor([], dtype=dtype).element_size()
+            for count in (4096, 65536 + 8, (1 << 20) + 16):
+                src = mem[:count * es].view(dtype)
+                dst = mem[nbytes:nbytes + count * es].view(dtype)
+                src.copy_(_vals(rank, count, dtype, seed=50).to(dev))
+                dst.zero_()
+                req = team.allreduce(src, dst, stream=stream, alg=K.NVLINK_ALG_SYMMETRIC, scale=0.5)
+                for _ in range(3):
+                    req.post()
+                req.wait()
+                want = (torch.stack([_vals(r, count, dtype, seed=50).double() for r in range(size)]).sum(0) * 0.5).to(dtype)
+                assert torch.equal(dst.cpu(), want), ("symmetric", dtype, count)
+                req.finalize()
+                # in place, chosen without being asked for (size above the one-shot range)
+                if count * es > (1 << 20):
+                    team.allreduce("in_place", src, stream=stream).run().finalize()
+                    assert torch.equal(src.cpu(), (want.double() * 2).to(dtype)), ("symmetric in place", dtype, count)
+        buf = mem[:1 << 20]
+        if rank == 1:
+            buf.copy_(torch.arange(1 << 20, device=dev, dtype=torch.int64).to(torch.uint8))
+        else:
+            buf.zero_()
+        torch.cuda.synchronize()
+        team.bcast(buf, 1, stream=stream).run().finalize()
+        assert torch.equal(buf.cpu(), torch.arange(1 << 20, dtype=torch.int64).to(torch.uint8))
+        # a root whose source is ordinary memory, destinations symmetric
+        team.barrier().run().finalize()
+        team.mem_free(mem)
+        out["symmetric"] = "ok"
     torch.cuda.synchronize()
     team.close()
     ctx.close()

@@ -50,6 +50,7 @@ IN_PLACE = 1
 
 HOST_ALG_LINEAR, HOST_ALG_KNOMIAL, HOST_ALG_SRA = 0, 1, 2
 NVLINK_ALG_AUTO, NVLINK_ALG_ONE_SHOT, NVLINK_ALG_TWO_SHOT, NVLINK_ALG_NVLS, NVLINK_ALG_DIRECT = 0, 1, 2, 3, 4
+NVLINK_ALG_SYMMETRIC = 5
 
 
 # ---------------------------------------------------------------- structures

@@ -259,6 +259,34 @@ class Team:
     def coll_tl(self, coll: int, mem: int = K.MEM_HOST) -> int:
         return int(K.load().xccl_team_coll_tl(self.h, coll, mem))
 
+    def mem_alloc(self, nbytes: int):
+        """Symmetric device memory (``xccl_team_mem_alloc``; collective: every member calls it with the same
+        size). Returns a uint8 torch tensor over the memory; view it as any dtype. Collectives whose buffers lie
+        in such memory at the same offset on every member run zero-copy through the NVSwitch multicast mapping."""
+        import torch
+        L = K.load()
+        L.xccl_team_mem_alloc.restype = C.c_int
+        L.xccl_team_mem_alloc.argtypes = [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)]
+        p = C.c_void_p()
+        _check(L.xccl_team_mem_alloc(self.h, int(nbytes), C.byref(p)), "xccl_team_mem_alloc")
+        ptr = int(p.value)
+
+        class _Mem:
+            __cuda_array_interface__ = {"shape": (int(nbytes),), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+        t = torch.as_tensor(_Mem(), device=torch.device("cuda", torch.cuda.current_device()))
+        self._sym = getattr(self, "_sym", {})
+        self._sym[t.data_ptr()] = ptr
+        return t
+
+    def mem_free(self, tensor) -> None:
+        """Returns memory of ``mem_alloc`` (collective)."""
+        L = K.load()
+        L.xccl_team_mem_free.restype = C.c_int
+        L.xccl_team_mem_free.argtypes = [C.c_void_p, C.c_void_p]
+        ptr = getattr(self, "_sym", {}).pop(tensor.data_ptr(), tensor.data_ptr())
+        _check(L.xccl_team_mem_free(self.h, C.c_void_p(ptr)), "xccl_team_mem_free")
+
     # ------------------------------------------------------------ request builders
     def _args(self, coll: int, src: Any, dst: Any, length: int, alg: Optional[int], stream: Any,
               keep: list) -> K.CollArgs:

@@ -54,6 +54,21 @@ def _rank_main(rank: int, size: int, job: str, opts: dict) -> list:
     ctx_c = Context(lib, oob, tls=K.TL_NCCL | K.TL_UCX)
     team_c = Team(ctx_c)
     impls.append(("nccl", team_c))
+    # what a caller gets without naming an algorithm or changing an option: "auto" on ordinary tensors,
+    # "symmetric" on buffers from Team.mem_alloc (zero-copy NVLS above the one-shot range)
+    ctx_a = Context(lib, oob, tls=K.TL_NVLINK | K.TL_UCX)
+    team_a = Team(ctx_a)
+    sym_mem = None
+    if opts.get("symmetric", True):
+        try:
+            sym_mem = team_a.mem_alloc(2 * max(opts["sizes"]) + 4096)
+        except Exception as e:  # no multicast on this machine
+            if rank == 0:
+                print(f"symmetric memory unavailable: {e}", file=sys.stderr)
+    from .clocks import ClockSampler
+    sampler = ClockSampler(rank)
+    sampler.start()
+    import time as _time
     stream = torch.cuda.Stream()
     sh = stream.cuda_stream
 
@@ -64,11 +79,18 @@ def _rank_main(rank: int, size: int, job: str, opts: dict) -> list:
     def run_case(coll: str, impl: str, team, nbytes: int, dtype, alg, alg_name: str):
         es = torch.tensor([], dtype=dtype).element_size()
         n = size
+        t_begin = _time.monotonic()
         iters = 50 if nbytes <= (1 << 20) else (10 if nbytes <= (64 << 20) else 4)
         if coll == "allreduce":
             count = max(nbytes // es, 1)
-            src = torch.randn(count, device=dev).to(dtype)
-            dst = torch.empty_like(src)
+            if alg_name == "symmetric":
+                half = sym_mem.numel() // 2 // 4096 * 4096
+                src = sym_mem[:count * es].view(dtype)
+                dst = sym_mem[half:half + count * es].view(dtype)
+                src.copy_(torch.randn(count, device=dev).to(dtype))
+            else:
+                src = torch.randn(count, device=dev).to(dtype)
+                dst = torch.empty_like(src)
             kw = dict(alg=alg, stream=sh)
             if impl == "nvlink":
                 kw.update(scale=1.0 / n)
@@ -93,7 +115,10 @@ def _rank_main(rank: int, size: int, job: str, opts: dict) -> list:
             req = team.reduce_scatter(src, dst, stream=sh, alg=alg)
             factor, total = (n - 1) / n, per * n * es
         elif coll == "bcast":
-            buf = torch.randn(max(nbytes // es, 1), device=dev).to(dtype)
+            if alg_name == "symmetric":
+                buf = sym_mem[:max(nbytes // es, 1) * es].view(dtype)
+            else:
+                buf = torch.randn(max(nbytes // es, 1), device=dev).to(dtype)
             req = team.bcast(buf, 0, stream=sh, alg=alg)
             factor, total = 1.0, buf.numel() * es
         else:
@@ -122,8 +147,10 @@ def _rank_main(rank: int, size: int, job: str, opts: dict) -> list:
             return {"coll": coll, "impl": impl, "alg": alg_name, "bytes": total, "error": str(e)[:80]}
         us = max_ranks(ms * 1e3)
         req.finalize()
+        clk = sampler.window(t_begin, _time.monotonic())
         return {"coll": coll, "impl": impl, "alg": alg_name, "dtype": str(dtype).replace("torch.", ""), "gpus": n,
-                "bytes": total, "us": round(us, 2), "bus_gbs": round(factor * total / (us * 1e-6) / 1e9, 2)}
+                "bytes": total, "us": round(us, 2), "bus_gbs": round(factor * total / (us * 1e-6) / 1e9, 2),
+                "iters": iters, "sm_mhz": clk["sm_mhz"], "clock_reasons": clk["reasons"]}
 
     dtypes = [getattr(torch, d) for d in opts["dtypes"]]
     for coll in opts["colls"]:
@@ -145,13 +172,21 @@ def _rank_main(rank: int, size: int, job: str, opts: dict) -> list:
                 if coll in ("allreduce", "alltoall", "allgather", "reduce_scatter") and nbytes >= (1 << 20):
                     # zero-copy kernels on buffers registered with the peers when the request is initialised
                     cases.append(("nvlink", team_n, K.NVLINK_ALG_DIRECT, "direct"))
+                cases.append(("nvlink", team_a, None, "auto"))
+                if sym_mem is not None and coll in ("allreduce", "bcast") and nbytes >= 16 and nbytes % 16 == 0:
+                    cases.append(("nvlink", team_a, None, "symmetric"))
                 cases.append(("nccl", team_c, None, "nccl"))
                 for impl, team, alg, name in cases:
                     r = run_case(coll, impl, team, nbytes, dtype, alg, name)
                     if rank == 0:
                         results.append(r)
     torch.cuda.synchronize()
-    team_n.close(); team_c.close(); ctx_n.close(); ctx_c.close(); lib.close(); oob.close()
+    clocks = sampler.stop()
+    if rank == 0:
+        results.append({"clocks_whole_run": clocks})
+    if sym_mem is not None:
+        team_a.mem_free(sym_mem)
+    team_n.close(); team_c.close(); team_a.close(); ctx_n.close(); ctx_c.close(); ctx_a.close(); lib.close(); oob.close()
     return results
 
 
@@ -192,8 +227,10 @@ def main() -> None:
     ap.add_argument("--workspace", default="512m")
     ap.add_argument("--max-blocks", type=int, default=128)
     ap.add_argument("--table", default=None, help="write the derived selection table to this file")
+    ap.add_argument("--no-symmetric", action="store_true", help="skip the rows on symmetric memory")
     a = ap.parse_args()
     opts = {"colls": a.colls.split(","), "dtypes": a.dtypes.split(","), "workspace": a.workspace,
+            "symmetric": not a.no_symmetric,
             "max_blocks": a.max_blocks, "sizes": _sizes(_parse_size(a.min_bytes), _parse_size(a.max_bytes), a.step)}
     res = run_ranks(_rank_main, a.gpus, opts, timeout=1500, start_method="spawn")
     for r in res[0]:

@@ -55,6 +55,9 @@ class TpMlp:
         env = os.environ.get("XCCL_TP_H2D_OVERLAP")
         self.overlap_h2d = (env == "1") or (env is None and tp == 1)
         self._copy_stream = None
+        self._y_alt = None
+        self._d2h_stream = None
+        self._full_steps = 0
 
     def forward(self, x_shards: Optional[list] = None) -> list:
         """x_shards: one [tokens/tp, hidden] bf16 tensor per local rank, or None when the input was
@@ -82,6 +85,40 @@ class TpMlp:
         # mean of squares in ONE reduction kernel (fp32 accumulation), no fp32 copy of the output
         norm = torch.linalg.vector_norm(y[0], dtype=torch.float32).cpu()   # the device->host read of the step
         return norm.square() / y[0].numel()                                 # finished on the host
+
+    def forward_from_host_full(self, x_pinned: list, y_pinned: list) -> None:
+        """End-to-end step whose result is the whole output shard: the input arrives from pinned host memory, the
+        [tokens/tp, hidden] output goes back to ``y_pinned[step parity]`` on a copy stream, so the read of step i
+        overlaps the kernels of step i+1 (outputs alternate between two device buffers). ``wait_outputs()`` returns
+        when every read issued so far has landed."""
+        if self._y_alt is None:
+            self._y_alt = [torch.empty_like(t) for t in self.y]
+            self._d2h_stream = torch.cuda.Stream()
+            self._y_free = [torch.cuda.Event(), torch.cuda.Event()]
+        k = self._full_steps & 1
+        self._full_steps += 1
+        main = torch.cuda.current_stream()
+        main.wait_event(self._y_free[k])           # the read of step i-2 has left this output buffer
+        if self.overlap_h2d:
+            if self._copy_stream is None:
+                self._copy_stream = torch.cuda.Stream()
+            self.ws.h2d_begin(x_pinned, self._copy_stream)
+        else:
+            for dst, src in zip(self.x_shards, x_pinned):
+                dst.copy_(src, non_blocking=True)
+        self.y, self._y_alt = self._y_alt, self.y
+        y = self.forward()
+        done = torch.cuda.Event()
+        done.record(main)
+        with torch.cuda.stream(self._d2h_stream):
+            self._d2h_stream.wait_event(done)
+            for dst, src in zip(y_pinned[k], y):
+                dst.copy_(src, non_blocking=True)
+            self._y_free[k].record(self._d2h_stream)
+
+    def wait_outputs(self) -> None:
+        if self._d2h_stream is not None:
+            self._d2h_stream.synchronize()
 
     def check_error(self) -> None:
         e = self.ws.error()
@@ -164,6 +201,44 @@ class TorchTpMlp:
         self.x_shard.copy_(x_pinned, non_blocking=True)
         y = self.forward()
         return torch.linalg.vector_norm(y, dtype=torch.float32).cpu().square() / y.numel()
+
+    def forward_from_host_full(self, x_pinned: torch.Tensor, y_pinned: list) -> None:
+        if getattr(self, "_reader", None) is None:
+            self._reader = PipelinedOutputReader(self.y)
+        self.x_shard.copy_(x_pinned, non_blocking=True)
+        self._reader.read(self.forward(), y_pinned)
+
+    def wait_outputs(self) -> None:
+        if getattr(self, "_reader", None) is not None:
+            self._reader.wait()
+
+
+class PipelinedOutputReader:
+    """The read-back of ``forward_from_host_full`` for an implementation whose forward returns a fresh or reused
+    output tensor: the result is copied to a staging buffer in the main stream's order and read to pinned memory on
+    a copy stream, two steps in flight. The comparison arms use it so that all arms overlap the same way."""
+
+    def __init__(self, like: torch.Tensor):
+        self.stage = [torch.empty_like(like), torch.empty_like(like)]
+        self.stream = torch.cuda.Stream()
+        self.free = [torch.cuda.Event(), torch.cuda.Event()]
+        self.steps = 0
+
+    def read(self, y: torch.Tensor, y_pinned: list) -> None:
+        k = self.steps & 1
+        self.steps += 1
+        main = torch.cuda.current_stream()
+        main.wait_event(self.free[k])
+        self.stage[k].copy_(y, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record(main)
+        with torch.cuda.stream(self.stream):
+            self.stream.wait_event(done)
+            y_pinned[k].copy_(self.stage[k], non_blocking=True)
+            self.free[k].record(self.stream)
+
+    def wait(self) -> None:
+        self.stream.synchronize()
 
 
 def reference_forward_fp32(x_full: torch.Tensor, w_gate_full: torch.Tensor, w_up_full: torch.Tensor,
