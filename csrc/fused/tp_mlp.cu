@@ -33,7 +33,7 @@ struct TpWorkspace {
     uint32_t *error = nullptr;
     size_t    off_xg = 0, off_part = 0, total = 0;
     uint32_t  seq_ag = 0, seq_rs = 0, rs_count[2] = {0, 0};
-    int       copy_ctas = 16;
+    int       copy_ctas = 0;      // CTAs of the allgather->GEMM kernel that pull the remote shards; 0 = by team size
     bool      rs_fused  = true;   // XCCL_TP_RS_FUSED=0: separate reduce phase after the last tile
     // input rows arriving from the host while the allgather->GEMM kernel already runs
     uint32_t   *in_flags[kMaxTpRanks] = {nullptr};  // per LOCAL rank: one word per chunk of in_rows rows
@@ -146,6 +146,10 @@ xccl_status_t xccl_tp_ws_create(const xccl_oob_collectives_t *oob, int emu_ranks
             }
         }
     }
+    // Copy CTAs only have to stay ahead of the tile walk (the walk starts on the local shard): 8 ranks need about
+    // 200 GB/s of the link, fewer ranks much less. Every CTA taken from the MMA side costs tensor throughput, and
+    // with 8 ranks 70 CTA pairs walk the 896 tiles of the 8192 x 7168 projection in 13 waves where 66 need 14.
+    if (w->copy_ctas <= 0) w->copy_ctas = w->tp >= 8 ? 8 : 4;
     int tiles_m = (M + kBM - 1) / kBM;
     if (st == XCCL_OK && (M % kBM != 0 || tiles_m % w->tp != 0)) st = XCCL_ERR_INVALID_PARAM;
     for (int l = 0; l < w->n_local && st == XCCL_OK; l++) {

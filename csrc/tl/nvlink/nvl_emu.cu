@@ -123,6 +123,7 @@ xccl_status_t xccl_nvlink_emu_collective(void *world, int coll_type, const void 
     c.do_scale = (scale != 1.0f);
     c.parity   = e->parity & 1;
     c.src_es = c.dst_es = es;
+    c.push   = (alg == ALG_ONE_SHOT && (coll_type == XCCL_ALLGATHER || coll_type == XCCL_ALLTOALL) && push_fits(w, coll_type, len)) ? 1 : 0;
     LaunchCfg cfg;
     cfg.cooperative = true;
     cfg.blocks      = blocks;

@@ -476,6 +476,51 @@ template <int KIND, bool kMc> __global__ void __launch_bounds__(512) mover_kerne
     self_end(w, s);
 }
 
+// Push form of allgather / alltoall for messages that fit one workspace half: every rank stores its segments
+// straight into slot [its rank] of the DESTINATION ranks' workspaces, the ranks meet at the barrier, and each
+// copies its own workspace out. Against the pull form (copy in, barrier, load from the peers) the loads after the
+// barrier are local, which takes one NVLink round trip off the latency.
+template <int KIND> __global__ void __launch_bounds__(512) push_mover_kernel(World w, Call c)
+{
+    Self         s   = self_begin(w);
+    const Byte  *src = (const Byte *)c.src[s.local];
+    Byte        *dst = (Byte *)c.dst[s.local];
+    const size_t seg_bytes = (KIND == MV_ALLGATHER) ? c.len / w.size : c.len;
+    const size_t n    = (seg_bytes + 15) / 16;
+    const size_t hoff = (size_t)c.parity * (w.ws_bytes / 2);
+    const Range  r    = block_range(n);
+    const size_t cnt  = r.hi - r.lo;
+    const bool   src_al = (((uintptr_t)src | seg_bytes) & 15) == 0;
+    const bool   dst_al = (((uintptr_t)dst | seg_bytes) & 15) == 0;
+    stream_packs<4>(
+        0, cnt * (size_t)w.size,
+        [&](size_t it) {
+            const uint32_t q = (uint32_t)(it / cnt);
+            const int      p = (s.rank + (int)q) % w.size;
+            return load_pack<Byte>(src + (KIND == MV_ALLTOALL ? (size_t)p * seg_bytes : 0), r.lo + (it - q * cnt), seg_bytes, src_al);
+        },
+        [&](size_t it, uint4 v) {
+            const uint32_t q = (uint32_t)(it / cnt);
+            const int      p = (s.rank + (int)q) % w.size;
+            st_16(w.ws[p] + hoff + ((size_t)s.rank * n + r.lo + (it - q * cnt)) * 16, v);
+        });
+    block_barrier(w, s);
+    if (!s.failed) {
+        const char *mine = w.ws[s.rank] + hoff;
+        stream_packs<4>(
+            0, cnt * (size_t)w.size,
+            [&](size_t it) {
+                const uint32_t q = (uint32_t)(it / cnt);
+                return ld_nc16(mine + ((size_t)q * n + r.lo + (it - q * cnt)) * 16);
+            },
+            [&](size_t it, uint4 v) {
+                const uint32_t q = (uint32_t)(it / cnt);
+                store_bytes(dst + (size_t)q * seg_bytes, r.lo + (it - q * cnt), seg_bytes, dst_al, v);
+            });
+    }
+    self_end(w, s);
+}
+
 // alltoallv: any counts. A rank's outgoing segments, each rounded up to a 16-byte pack and laid end to end in
 // destination order, form its "stream". Round k stages window k of that stream (cap bytes) in the workspace half
 // of alternating parity, the ranks meet at a barrier, and every receiver pulls the part of its segment that lies
@@ -958,12 +1003,24 @@ xccl_status_t launch_reduce_scatter(const World &w, const Call &c, xccl_dt_t dt,
     return XCCL_DISPATCH_IO(dt, out_dt, return (reduce_typed<T, O, true>(w, c, cfg, stream)););
 }
 
+bool push_fits(const World &w, int coll, size_t len)
+{
+    const size_t seg = (coll == XCCL_ALLGATHER) ? len / (size_t)w.size : len;
+    return ((seg + 15) / 16) * 16 * (size_t)w.size <= w.ws_bytes / 2;
+}
+
 template <int KIND, bool kMc = false>
 static xccl_status_t mover(const World &w, const Call &c, const LaunchCfg &cfg, cudaStream_t stream)
 {
     size_t seg    = (KIND == MV_ALLGATHER) ? c.len / (size_t)w.size : c.len;
     size_t npacks = (seg + 15) / 16;
     if (npacks == 0) return XCCL_OK;
+    if (KIND != MV_BCAST && c.push && npacks * 16 * (size_t)w.size <= w.ws_bytes / 2) {
+        auto k      = push_mover_kernel<KIND == MV_BCAST ? MV_ALLGATHER : KIND>;
+        int  blocks = pick_blocks(k, w, cfg, npacks * (size_t)w.size, 2);
+        return launch(k, dim3((unsigned)blocks, (unsigned)w.n_local), dim3((unsigned)cfg.threads), cfg.cooperative, stream,
+                      w, c);
+    }
     auto k      = mover_kernel<KIND, kMc>;
     int  blocks = pick_blocks(k, w, cfg, npacks * (KIND == MV_BCAST ? 1 : (size_t)w.size), 2);
     return launch(k, dim3((unsigned)blocks, (unsigned)w.n_local), dim3((unsigned)cfg.threads), cfg.cooperative, stream,

@@ -22,6 +22,7 @@ struct Call {
     int             do_scale;
     int             parity;            // which half of the workspace this launch uses
     int             src_es, dst_es;    // alltoallv element sizes
+    int             push;              // allgather / alltoall: store into the destinations' workspaces (one chunk only)
     // Direct algorithms: every rank's user buffers as mapped in this process, by TEAM rank (peer
     // mappings of registered buffers in a real team, the plain pointers when ranks are emulated).
     const void     *peer_src[kMaxRanks];
@@ -74,6 +75,8 @@ xccl_status_t launch_sync(const World &w, const Call &c, int kind, const LaunchC
 xccl_status_t launch_timeout_probe(const World &w, unsigned long long budget_ns, cudaStream_t stream);
 
 bool nvls_supported(xccl_dt_t dt, xccl_op_t op);
+// allgather / alltoall: true when the whole exchange fits one workspace half in the push layout
+bool push_fits(const World &w, int coll, size_t len);
 
 }  // namespace nvl
 }  // namespace xccl

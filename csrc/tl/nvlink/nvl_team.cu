@@ -36,6 +36,7 @@ struct NvlCfg {
     bool   direct        = true;
     bool   symmetric     = true;        // zero-copy NVLS on buffers from xccl_team_mem_alloc
     size_t symmetric_min = 32u << 10;
+    size_t push_max      = 256u << 10;  // allgather / alltoall up to this many bytes per rank use the push form
     std::string tuning_file;
     int    max_blocks    = 64;
     int    threads       = 512;
@@ -88,6 +89,7 @@ public:
 
 private:
     xccl_status_t complete();
+    bool          push_wanted(int coll, size_t total_bytes) const;
     NvlTeam            *team_;
     xccl_coll_op_args_t args_;
     cudaEvent_t         done_ = nullptr, start_ = nullptr;
@@ -452,6 +454,17 @@ xccl_status_t NvlReq::register_buffers(void *src, void *dst, size_t src_bytes, s
     return XCCL_OK;
 }
 
+// allgather / alltoall: the push form when asked for (alg one-shot), never when the pull form is asked for (alg
+// two-shot), otherwise up to PUSH_MAX bytes per rank; always only when the exchange fits one workspace half.
+bool NvlReq::push_wanted(int coll, size_t total_bytes) const
+{
+    const size_t len = args_.buffer_info.len;
+    if (!push_fits(team_->world, coll, len)) return false;
+    if (args_.alg.set_by_user && args_.alg.id == ALG_ONE_SHOT) return true;
+    if (args_.alg.set_by_user && args_.alg.id == ALG_TWO_SHOT) return false;
+    return total_bytes <= team_->cfg.push_max;
+}
+
 xccl_status_t NvlReq::post()
 {
     // A request that is still in flight may be posted again: posts of one request are ordered by its stream, and
@@ -495,10 +508,15 @@ xccl_status_t NvlReq::post()
     if (sym_) {
         const size_t bytes = args_.coll_type == XCCL_BCAST ? c.len : c.count * xccl_dt_size(dt);
         const bool   user  = args_.alg.set_by_user && args_.alg.id != ALG_AUTO;
-        // small reductions stay with the one-shot kernel (one flag round trip less than two barriers)
-        const bool   take  = user ? args_.alg.id == ALG_SYMMETRIC
-                                  : (args_.coll_type == XCCL_BCAST ? bytes >= team_->cfg.symmetric_min
-                                                                   : bytes >= team_->cfg.symmetric_min && bytes > team_->cfg.one_shot_max);
+        // Asked for by name: always. Asked for NVLS (the in-switch path, e.g. by the sharp / hmc team libraries):
+        // zero-copy from the threshold on, staged below it. Not asked for anything: additionally, small reductions
+        // stay with the one-shot kernel (one flag round trip instead of two barriers).
+        bool take;
+        if (user) {
+            take = args_.alg.id == ALG_SYMMETRIC || (args_.alg.id == ALG_NVLS && bytes >= team_->cfg.symmetric_min);
+        } else {
+            take = bytes >= team_->cfg.symmetric_min && (args_.coll_type == XCCL_BCAST || bytes > team_->cfg.one_shot_max);
+        }
         if (take) {
             c.mc_src[0] = mc_src_;
             c.mc_dst[0] = mc_dst_;
@@ -568,10 +586,12 @@ xccl_status_t NvlReq::post()
         break;
     }
     case XCCL_ALLGATHER:
+        c.push = push_wanted(XCCL_ALLGATHER, c.len) ? 1 : 0;
         st = launch_allgather(w, c, cfg, s);
         team_->phase += chunks_used(w, XCCL_ALLGATHER, c.count, c.len, dt);
         break;
     case XCCL_ALLTOALL:
+        c.push = push_wanted(XCCL_ALLTOALL, c.len * (size_t)team_->size) ? 1 : 0;
         st = launch_alltoall(w, c, cfg, s);
         team_->phase += chunks_used(w, XCCL_ALLTOALL, c.count, c.len, dt);
         break;
@@ -683,6 +703,7 @@ public:
             {"BCAST_MC_MIN", "0", "Broadcasts from this size go through the NVSwitch multicast mapping when available", OptType::MEMUNITS},
             {"DIRECT", "y", "Register the buffers of large messages with the peers (CUDA IPC) and run zero-copy kernels on them", OptType::BOOL},
             {"DIRECT_MIN", "0", "Messages from this size register their buffers and use the direct (zero-copy) kernels (0: from the tuning file, else only on request; measured crossover 32m-256m)", OptType::MEMUNITS},
+            {"PUSH_MAX", "256k", "Allgather / alltoall messages up to this size (bytes per rank) store into the destinations' workspaces instead of being pulled", OptType::MEMUNITS},
             {"SYMMETRIC", "y", "Run collectives whose buffers come from xccl_team_mem_alloc zero-copy through the multicast mapping", OptType::BOOL},
             {"SYMMETRIC_MIN", "32k", "Smallest message that takes the symmetric (zero-copy NVLS) path", OptType::MEMUNITS},
             {"TUNING_FILE", "", "Measured thresholds, lines of `team_size one_shot_max nvls_min direct_min` (see bench/collectives.py --table)", OptType::STRING},
@@ -726,6 +747,7 @@ public:
         if (!c.direct_min_set) c.direct_min = ~(size_t)0;
         c.tuning_file     = cfg.str("TUNING_FILE");
         c.direct          = cfg.flag("DIRECT");
+        c.push_max        = (size_t)cfg.num("PUSH_MAX");
         c.symmetric       = cfg.flag("SYMMETRIC");
         c.symmetric_min   = (size_t)cfg.num("SYMMETRIC_MIN");
         c.max_blocks      = std::max(1, std::min((int)cfg.num("MAX_BLOCKS"), kMaxBlocks));

@@ -5,10 +5,25 @@
 // src/team_lib/sharp/xccl_sharp_lib.c:387-391) and "hmc" (hardware multicast: bcast only,
 // src/team_lib/hmc/xccl_hmc_lib.c:132-212). Their NVSwitch counterparts are the multimem
 // instructions: multimem.ld_reduce lets the switch add the ranks' buffers, multimem.st lets it
-// replicate a store. Both team libraries here keep the reference's ids, capabilities and option
-// names and serve their collectives by forwarding to an inner NVLink team with the NVLS
-// algorithm forced; they come up only when the NVLink team could bind a multicast object.
+// replicate a store. Both team libraries keep the reference's ids, capabilities and option names
+// and run on an inner NVLink team with the in-switch algorithms forced.
+//
+// The sharp team's two data paths (src/team_lib/sharp/xccl_sharp_collective.c:61-170) map as follows:
+//   zero-copy   the reference registers the user's buffers with the SHARP library and lets the switch work on
+//               them in place for messages of ZCOPY_THRESH bytes or more. Here the registered memory is what
+//               xccl_team_mem_alloc hands out (symmetric, bound to the multicast object): from ZCOPY_THRESH on,
+//               multimem.ld_reduce reads the source buffers and multimem.st writes the destinations directly.
+//   bounce copy smaller messages, and buffers that are not registered memory, are staged through the team's
+//               pre-registered bounce buffers: BCOPY_BUF_NUM buffers of BCOPY_BUF_SIZE bytes form the inner
+//               team's workspace, which is bound to the multicast object at team creation.
+//   RCACHE      the registration cache for ordinary device buffers: CUDA IPC mappings of the peers' allocations,
+//               kept per allocation ("no" never registers; requests then always take the bounce path).
+//   NET_DEVICES the fabric to use; only "nvswitch" exists on this platform, anything else fails context creation.
+#include <algorithm>
 #include <chrono>
+#include <string>
+#include <utility>
+#include <vector>
 
 #include "../../core/core.h"
 #include "../../cuda/cuda_common.h"
@@ -29,6 +44,9 @@ public:
     }
     xccl_status_t create_test() override { return XCCL_OK; }
     xccl_status_t collective_init(const xccl_coll_op_args_t &args, xccl_memory_type_t, xccl_coll_req **req) override;
+    // registered memory of this team: symmetric allocations of the inner NVLink team
+    xccl_status_t sym_alloc(size_t bytes, void **ptr) override { return xccl_team_mem_alloc(inner, bytes, ptr); }
+    xccl_status_t sym_free(void *ptr) override { return xccl_team_mem_free(inner, ptr); }
     FwdContext *fctx;
     xccl_team_h inner = nullptr;
 };
@@ -42,6 +60,8 @@ public:
         if (inner != nullptr) xccl_context_destroy(inner);
         if (lib != nullptr) xccl_lib_cleanup(lib);
     }
+    // extra (name, value) pairs for the inner NVLink context
+    std::vector<std::pair<std::string, std::string>> inner_opts;
     xccl_status_t init(const char *prefix)
     {
         xccl_lib_params_t lp{};
@@ -55,6 +75,7 @@ public:
         if (st != XCCL_OK) return st;
         xccl_tl_id_t id = XCCL_TL_NVLINK;
         xccl_context_config_modify(&id, cc, "NVLS", "yes");
+        for (auto &kv : inner_opts) xccl_context_config_modify(&id, cc, kv.first.c_str(), kv.second.c_str());
         st = xccl_context_create(lib, &cp, cc, &inner);
         xccl_context_config_release(cc);
         return st;
@@ -115,16 +136,29 @@ public:
     std::vector<OptField> context_options() const override
     {
         return {
-            {"RCACHE", "try", "Accepted for compatibility: buffers are staged through the registered workspace", OptType::TERNARY},
-            {"ZCOPY_THRESH", "1024", "Accepted for compatibility", OptType::MEMUNITS},
-            {"BCOPY_BUF_NUM", "10", "Accepted for compatibility", OptType::UINT},
-            {"NET_DEVICES", "nvswitch", "Accepted for compatibility", OptType::STRING},
+            {"RCACHE", "try", "Keep a cache of registrations (CUDA IPC mappings) of ordinary device buffers; no: never register", OptType::TERNARY},
+            {"ZCOPY_THRESH", "1024", "Messages of at least this size in registered (xccl_team_mem_alloc) memory are reduced in place by the switch", OptType::MEMUNITS},
+            {"BCOPY_BUF_NUM", "10", "Bounce buffers pre-registered with the fabric for the staged path", OptType::UINT},
+            {"BCOPY_BUF_SIZE", "12800k", "Bytes of one bounce buffer", OptType::MEMUNITS},
+            {"NET_DEVICES", "nvswitch", "Fabric to use; this platform has \"nvswitch\" only", OptType::STRING},
         };
     }
-    xccl_status_t context_create(xccl_lib *, const xccl_context_params_t &params, const OptTable &,
+    xccl_status_t context_create(xccl_lib *, const xccl_context_params_t &params, const OptTable &cfg,
                                  TlContext **ctx) override
     {
-        auto          c  = std::make_unique<FwdContext>(params, caps.coll_types);
+        const std::string dev = cfg.str("NET_DEVICES");
+        if (!dev.empty() && dev != "nvswitch" && dev != "all") {
+            tl_error(this, "sharp: no fabric device \"%s\" (only \"nvswitch\")", dev.c_str());
+            return XCCL_ERR_NO_RESOURCE;
+        }
+        auto c = std::make_unique<FwdContext>(params, caps.coll_types);
+        const unsigned long long ws = std::max<unsigned long long>(
+            (unsigned long long)cfg.num("BCOPY_BUF_NUM") * (unsigned long long)cfg.num("BCOPY_BUF_SIZE"), 1ull << 20);
+        c->inner_opts.push_back({"WORKSPACE_SIZE", std::to_string(ws)});
+        c->inner_opts.push_back({"SYMMETRIC_MIN", std::to_string((unsigned long long)cfg.num("ZCOPY_THRESH"))});
+        const std::string rc = cfg.str("RCACHE");
+        const bool        no_rcache = !rc.empty() && (rc[0] == 'n' || rc[0] == 'N' || rc[0] == '0' || rc == "off");
+        c->inner_opts.push_back({"DIRECT", no_rcache ? "n" : "y"});
         xccl_status_t st = c->init("SHARP_nvlink");
         if (st != XCCL_OK) return st;
         *ctx = c.release();

@@ -285,6 +285,31 @@ def test_emu_byte_collectives_stay_inside_their_buffers(world4, dev):
             assert torch.equal(g.view, keep[1]) and g.guards_intact(), ("bcast", per)
 
 
+def test_emu_push_allgather_alltoall(world4, dev):
+    """The push forms (stores into the destinations' workspaces) on odd, unaligned byte buffers, between pull-form
+    calls so that both share the workspace parity bookkeeping."""
+    n = 4
+    for per in (1, 13, 4099, 70001):
+        srcs = [_Guarded(per * n, dev, fill=0x11) for _ in range(n)]
+        dsts = [_Guarded(per * n, dev, fill=0x22) for _ in range(n)]
+        for r in range(n):
+            srcs[r].view.copy_((torch.arange(per * n, device=dev) * 7 + r * 31) % 251)
+        world4.alltoall([s.view for s in srcs], [d.view for d in dsts], alg=K.NVLINK_ALG_ONE_SHOT)
+        for r in range(n):
+            want = torch.cat([srcs[q].view[r * per:(r + 1) * per] for q in range(n)])
+            assert torch.equal(dsts[r].view, want) and dsts[r].guards_intact(), ("alltoall push", per, r)
+        parts = [_Guarded(per, dev, fill=0x33) for _ in range(n)]
+        for r in range(n):
+            parts[r].view.copy_((torch.arange(per, device=dev) * 3 + r * 17) % 253)
+        world4.allgather([p_.view for p_ in parts], [d.view for d in dsts], alg=K.NVLINK_ALG_ONE_SHOT)
+        want = torch.cat([p_.view for p_ in parts])
+        for r in range(n):
+            assert torch.equal(dsts[r].view, want) and dsts[r].guards_intact(), ("allgather push", per, r)
+        world4.allgather([p_.view for p_ in parts], [d.view for d in dsts])   # pull form next to it
+        for r in range(n):
+            assert torch.equal(dsts[r].view, want)
+
+
 def test_emu_alltoallv(world4, dev):
     n = 4
     sc = [[(s * 3 + d * 5 + 1) for d in range(n)] for s in range(n)]  # elements rank s sends to rank d

@@ -325,3 +325,69 @@ def test_host_team_serves_cuda_buffers():
         pytest.skip("needs 2 GPUs")
     res = run_ranks(_host_team_cuda_main, 2, timeout=180, start_method="spawn")
     assert res == ["ok", "ok"]
+
+
+def _fabric_rank_main(rank, size, job):
+    """The in-fabric offload team libraries (ids of the reference's sharp and hmc teams) on NVSwitch: allreduce and
+    barrier through the sharp team - bounce path on ordinary tensors, zero-copy on registered memory from
+    ZCOPY_THRESH on - and bcast through the hmc team."""
+    from xccl_b200.api import Context, Lib, ShmOob, Team, XcclError
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    oob = ShmOob(job, rank, size)
+    lib = Lib()
+    out = {}
+    try:
+        ctx = Context(lib, oob, tls=K.TL_SHARP | K.TL_HMC | K.TL_UCX,
+                      config={K.TL_SHARP: {"ZCOPY_THRESH": "64k", "BCOPY_BUF_NUM": "4", "BCOPY_BUF_SIZE": "1m"}})
+    except XcclError as e:
+        return {"skipped": f"no multicast fabric: {e}"}
+    team = Team(ctx)
+    if team.coll_tl(K.ALLREDUCE, K.MEM_CUDA) != K.TL_SHARP:
+        team.close(); ctx.close(); lib.close(); oob.close()
+        return {"skipped": "the sharp team did not come up (no multicast)"}
+    assert team.coll_tl(K.BCAST, K.MEM_CUDA) == K.TL_HMC
+    stream = torch.cuda.current_stream().cuda_stream
+    # bounce path: ordinary tensors, also larger than the 4 MiB of bounce buffers
+    for count in (1000, 300000, (3 << 20) + 8):
+        src = _vals(rank, count, torch.float32, seed=60).to(dev)
+        dst = torch.zeros_like(src)
+        team.allreduce(src, dst, stream=stream, scale=0.5).run().finalize()
+        want = torch.stack([_vals(r, count, torch.float32, seed=60) for r in range(size)]).sum(0) * 0.5
+        assert torch.equal(dst.cpu(), want), ("bounce", count)
+    # registered memory: below the threshold staged, from it on in place
+    mem = team.mem_alloc(16 << 20)
+    for count in (4096, 1 << 20):
+        src = mem[:count * 4].view(torch.float32)
+        dst = mem[8 << 20:(8 << 20) + count * 4].view(torch.float32)
+        src.copy_(_vals(rank, count, torch.float32, seed=61).to(dev))
+        req = team.allreduce(src, dst, stream=stream)
+        for _ in range(2):
+            req.post()
+        req.wait()
+        req.finalize()
+        want = torch.stack([_vals(r, count, torch.float32, seed=61) for r in range(size)]).sum(0)
+        assert torch.equal(dst.cpu(), want), ("registered", count)
+    team.barrier().run().finalize()
+    buf = _vals(1, 70000, torch.float32, seed=62).to(dev) if rank == 1 else torch.zeros(70000, device=dev)
+    team.bcast(buf, 1, stream=stream).run().finalize()
+    assert torch.equal(buf.cpu(), _vals(1, 70000, torch.float32, seed=62))
+    torch.cuda.synchronize()
+    team.mem_free(mem)
+    team.close(); ctx.close()
+    # a fabric device that does not exist: the sharp team stays out, the context is served by the rest
+    ctx2 = Context(lib, oob, tls=K.TL_SHARP | K.TL_UCX, config={K.TL_SHARP: {"NET_DEVICES": "mlx5_0:1"}})
+    team2 = Team(ctx2)
+    assert team2.coll_tl(K.ALLREDUCE, K.MEM_CUDA) != K.TL_SHARP
+    team2.close(); ctx2.close()
+    lib.close(); oob.close()
+    out["ok"] = True
+    return out
+
+
+def test_fabric_offload_teams_on_nvswitch():
+    if _ngpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    res = run_ranks(_fabric_rank_main, 2, timeout=240, start_method="spawn", env={"NCCL_NVLS_ENABLE": "0"})
+    print("sharp / hmc teams:", res[0])
+    assert all(("ok" in r) or ("skipped" in r) for r in res)

@@ -167,6 +167,10 @@ def _rank_main(rank: int, size: int, job: str, opts: dict) -> list:
                 elif coll == "bcast":
                     cases.append(("nvlink", team_n, K.NVLINK_ALG_TWO_SHOT, "pull"))
                     cases.append(("nvlink", team_n, K.NVLINK_ALG_NVLS, "multicast"))
+                elif coll in ("alltoall", "allgather"):
+                    cases.append(("nvlink", team_n, K.NVLINK_ALG_TWO_SHOT, "pull"))
+                    if nbytes <= (4 << 20):
+                        cases.append(("nvlink", team_n, K.NVLINK_ALG_ONE_SHOT, "push"))
                 else:
                     cases.append(("nvlink", team_n, None, "pull"))
                 if coll in ("allreduce", "alltoall", "allgather", "reduce_scatter") and nbytes >= (1 << 20):

@@ -68,16 +68,22 @@ def main() -> None:
         opt.step()
         return loss
 
+    from .clocks import ClockSampler
+    sampler = ClockSampler(local)
+    sampler.start()
     for _ in range(max(a.warmup, 3)):
         step()
     torch.cuda.synchronize()
     dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.mark_begin()
     e0.record()
     for _ in range(a.steps):
         loss = step()
     e1.record()
     torch.cuda.synchronize()
+    sampler.mark_end()
+    clocks = sampler.stop()
     ms = torch.tensor([e0.elapsed_time(e1) / a.steps], dtype=torch.float32, device=dev)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     grad_bytes = sum(p.numel() for p in model.parameters()) * 2
@@ -87,7 +93,7 @@ def main() -> None:
                           "gpus": world, "batch_per_gpu": a.batch, "dtype": "bf16", "bucket_mb": a.bucket_mb,
                           "ms_per_step": round(ms_v, 3), "images_per_s": round(a.batch * world / (ms_v * 1e-3), 1),
                           "steps_per_s": round(1e3 / ms_v, 3), "grad_bytes": grad_bytes,
-                          "loss": float(loss.item()), "data": "synthetic"}), flush=True)
+                          "loss": float(loss.item()), "data": "synthetic", "clocks": clocks}), flush=True)
     dist.barrier()
     dist.destroy_process_group()
 

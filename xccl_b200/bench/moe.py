@@ -51,6 +51,10 @@ def _rank_main(rank: int, size: int, job: str, o: dict) -> list:
         torch.cuda.synchronize()
         return max_ranks(e0.elapsed_time(e1) / iters)
 
+    from .clocks import ClockSampler
+    sampler = ClockSampler(rank)
+    sampler.start()
+    sampler.mark_begin()
     # ---- fused kernels
     ws = MoeWorkspace(T, H, E, Kk, oob=oob, cap_rows=min(size * T * Kk, 2 * T * Kk))
     y = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
@@ -134,6 +138,9 @@ def _rank_main(rank: int, size: int, job: str, o: dict) -> list:
         out.append({"impl": "nccl_alltoallv_torch", "gpus": size, "dispatch_ms": round(tb_d, 4),
                     "combine_ms": round(tb_c, 4), "total_ms": round(tb_d + tb_c, 4), "numerics_ok": okb})
     cnt_req.finalize()
+    sampler.mark_end()
+    if rank == 0:
+        out.append({"clocks_whole_run": sampler.stop()})
     team.close(); ctx.close(); lib.close(); oob.close()
     return out
 

@@ -49,11 +49,10 @@ class TpMlp:
         self.y = [torch.empty(tokens // tp, hidden, dtype=torch.bfloat16, device=self.device) for _ in ranks]
         self.x_shards = [self.ws.x_shard(i) for i in range(self.n_local)]
         self.launches = 0
-        # forward_from_host overlaps the host->device copy of the input with the first kernel. On by default on
-        # one GPU (measured: 10.2 -> 9.4 ms per end-to-end step of the 8192 x 8192 x 28672 block); with tp > 1 it
-        # is opt-in (XCCL_TP_H2D_OVERLAP=1) until it has been measured there; XCCL_TP_H2D_OVERLAP=0 turns it off.
-        env = os.environ.get("XCCL_TP_H2D_OVERLAP")
-        self.overlap_h2d = (env == "1") or (env is None and tp == 1)
+        # forward_from_host overlaps the host->device copy of the input with the first kernel (measured on the
+        # 8192 x 8192 x 28672 block: 10.2 -> 9.4 ms per end-to-end step on one GPU, 5.37 -> 5.21 ms on two).
+        # XCCL_TP_H2D_OVERLAP=0 turns it off.
+        self.overlap_h2d = os.environ.get("XCCL_TP_H2D_OVERLAP") != "0"
         self._copy_stream = None
         self._y_alt = None
         self._d2h_stream = None
