@@ -132,7 +132,7 @@ def main() -> None:
         step = lambda: model.forward(x_dev)           # noqa: E731
         e2e_step = lambda: model.forward_from_host(x_pin)  # noqa: E731
         full_step = lambda: model.forward_from_host_full(x_pin, y_pin)  # noqa: E731
-        launches_per_step = 4 if args.dtype == "fp8" else 2
+        launches_per_step = 3 if args.dtype == "fp8" else 2
     else:
         from xccl_b200.models.tp_mlp import TorchTpMlp
         model = TorchTpMlp(TOKENS, HIDDEN, FFN, tp=world, rank=rank)

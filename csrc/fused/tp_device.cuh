@@ -259,6 +259,118 @@ __device__ void copy_cta_loop(const GemmParams &p, int rank, int local, int copy
     if (threadIdx.x == 0) *epoch_slot = epoch;
 }
 
+// Copier warps of the allgather mode (copy_mode 1): instead of setting whole CTAs aside for the copy, the last two
+// warps of EVERY CTA pull this CTA's share of each remote row block with plain 16-byte loads from the peer and
+// stores into the local gathered buffer. One SM sustains only a few tens of GB/s of remote loads, whatever engine
+// issues them, so the copy is spread over all SMs, where it needs about 1.5 GB/s from each and costs no tensor
+// throughput. CTA 0's copiers also run the two cross-rank barriers (peers have published their shards / everybody
+// has finished reading) and release the other CTAs through a counter in local memory.
+constexpr int kCopierThreads = 64;
+constexpr int kGoSlot = 1100, kDoneSlot = 1101;  // words of the pad's counter area (the reduce-scatter counters end at 1024)
+
+__device__ void copier_warps_loop(const GemmParams &p, int rank, int local, int tid, const AbortFlag &ab)
+{
+    const int    n_cta   = gridDim.x;
+    const int    me      = blockIdx.x;
+    const int    tiles_m = (p.M + kBM - 1) / kBM;
+    const int    mbs     = tiles_m / p.tp_size;
+    const int    a_bytes = p.a_bytes > 0 ? p.a_bytes : 2;
+    const size_t blk_bytes  = (size_t)kBM * p.K * a_bytes;
+    const size_t blk_packs  = blk_bytes / 16;
+    const size_t per  = (blk_packs + n_cta - 1) / n_cta;
+    const size_t lo   = min((size_t)me * per, blk_packs), hi = min(lo + per, blk_packs);
+    const size_t sblk_bytes = (a_bytes == 1) ? (size_t)kBM * (p.K / 128) * 4 : 0;
+    const size_t sblk_packs = sblk_bytes / 16;
+    const size_t sper = (sblk_packs + n_cta - 1) / n_cta;
+    const size_t slo  = min((size_t)me * sper, sblk_packs), shi = min(slo + sper, sblk_packs);
+    uint32_t    *go   = p.pad[rank] + nvl::kPadCounterOff + kGoSlot;
+    uint32_t    *done = p.pad[rank] + nvl::kPadCounterOff + kDoneSlot;
+    auto sync_copiers = [] { asm volatile("bar.sync 6, 64;" ::: "memory"); };
+    bool ok = true;
+
+    if (me == 0) {
+        // my own shard may still be arriving from the host: the peers are told to read it only when all of it is here
+        if (tid == 0 && p.in_ready[local] != nullptr) {
+            const int chunks = (p.M / p.tp_size + p.in_rows_per_flag - 1) / p.in_rows_per_flag;
+            for (int c = 0; c < chunks; c++) {
+                if (!wait_counter(p.in_ready[local] + c, p.in_target, true, ab, 9)) break;
+            }
+        }
+        sync_copiers();
+        // opening barrier among the ranks (flag row 0 of the pads)
+        uint32_t *epoch_slot = p.pad[rank] + nvl::kPadEpochOff;
+        const uint32_t epoch = *epoch_slot + 1;
+        int bad = 0;
+        if (tid < p.tp_size) {
+            nvl::st_release_sys(p.pad[tid] + rank, epoch);
+            if (!nvl::wait_flag(p.pad[rank] + tid, epoch, ab.budget_ns)) bad = 1;
+        }
+        if (bad) {
+            *ab.smem = 1;
+            atomicCAS(ab.global, 0u, 0x300u);
+        }
+        sync_copiers();
+        if (tid == 0) {
+            *epoch_slot = epoch;
+            red_release_gpu_add(go, 1u);   // go counts launches: seq
+        }
+    }
+    if (tid == 0) ok = wait_counter(go, p.seq, false, ab, 0xa);
+    sync_copiers();
+    ok = (*ab.smem == 0);
+
+    const int n_blocks = (p.tp_size - 1) * mbs;
+    for (int b = 0; b < n_blocks && ok; b++) {
+        const int shard = (rank + 1 + b / mbs) % p.tp_size;
+        const int blk   = shard * mbs + b % mbs;
+        {
+            const char *src = reinterpret_cast<const char *>(p.xg[shard]) + (size_t)blk * blk_bytes;
+            char       *dst = reinterpret_cast<char *>(p.xg[rank]) + (size_t)blk * blk_bytes;
+            size_t      i   = lo + tid;
+            for (; i + 7 * kCopierThreads < hi; i += 8 * kCopierThreads) {
+                uint4 v[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) v[u] = nvl::ld_nc16(src + (i + (size_t)u * kCopierThreads) * 16);
+#pragma unroll
+                for (int u = 0; u < 8; u++) *reinterpret_cast<uint4 *>(dst + (i + (size_t)u * kCopierThreads) * 16) = v[u];
+            }
+            for (; i < hi; i += kCopierThreads) *reinterpret_cast<uint4 *>(dst + i * 16) = nvl::ld_nc16(src + i * 16);
+        }
+        if (sblk_packs != 0) {
+            const char *src = reinterpret_cast<const char *>(p.sg[shard]) + (size_t)blk * sblk_bytes;
+            char       *dst = reinterpret_cast<char *>(p.sg[rank]) + (size_t)blk * sblk_bytes;
+            for (size_t i = slo + tid; i < shi; i += kCopierThreads) *reinterpret_cast<uint4 *>(dst + i * 16) = nvl::ld_nc16(src + i * 16);
+        }
+        sync_copiers();
+        if (tid == 0) {
+            // the TMA unit (async proxy) of any CTA of this rank reads these rows next
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            __threadfence();
+            red_release_gpu_add(p.ready[local] + blk, 1u);
+        }
+    }
+    // closing: nobody overwrites a shard that a peer may still be reading
+    sync_copiers();
+    if (tid == 0) red_release_gpu_add(done, 1u);
+    if (me == 0) {
+        if (tid == 0) wait_counter(done, p.seq * (uint32_t)n_cta, false, ab, 0xb);
+        sync_copiers();
+        uint32_t *epoch_slot = p.pad[rank] + nvl::kPadEpochOff;
+        const uint32_t epoch = *epoch_slot + 1;
+        int bad = 0;
+        if (tid < p.tp_size) {
+            nvl::st_release_sys(p.pad[tid] + rank, epoch);
+            if (!nvl::wait_flag(p.pad[rank] + tid, epoch, ab.budget_ns)) bad = 1;
+        }
+        if (bad) {
+            *ab.smem = 1;
+            atomicCAS(ab.global, 0u, 0x301u);
+        }
+        sync_copiers();
+        if (tid == 0) *epoch_slot = epoch;
+    }
+}
+
 // Reduce phase of GEMM -> reduce-scatter: every rank has stored its partial tiles for MY rows into my
 // partial buffer (slot = source rank, parity = launch sequence) and counted them into my arrival
 // counters; when a 128-row block has arrived from every rank, add the partials up in fp32 and write

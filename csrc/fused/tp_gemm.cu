@@ -1,20 +1,26 @@
 // Tensor-parallel GEMM kernels for sm_100a (see tp_gemm.cuh for the operations).
 //
-// CTA anatomy (192 threads, one CTA per SM, persistent over output tiles of 128 x 256):
-//   warp 0   one elected thread issues TMA tiled loads (A: 128 x 64, B: 256 x 64 bf16, 128B swizzle)
-//            into a 4-stage shared-memory ring guarded by full/empty mbarriers
-//   warp 1   one elected thread issues tcgen05.mma (M128 N256 K16, 4 per stage) accumulating fp32 in
-//            tensor memory; tcgen05.commit releases the stage and, after the last K block, hands the
-//            accumulator to the epilogue. Two accumulators (2 x 256 TMEM columns) alternate so the
-//            epilogue of tile i overlaps the MMAs of tile i+1
-//   warps 2-5  read their 32 TMEM lanes with tcgen05.ld, apply the epilogue (bf16 cast or
-//            silu(gate)*up), transpose through shared memory and write 128-byte row segments to
-//            local or peer memory
-// No TMA load uses cluster multicast and no TMA load reads another GPU's memory: remote operands
-// are first copied into local memory by the copy CTAs of this same kernel.
+// Default layout: CTA pairs. A cluster of two CTAs (192 threads each, one CTA per SM, persistent) owns an output tile
+// of 256 x 256: tcgen05.mma.cta_group::2 (M256 N256 K16) is issued by CTA 0 of the pair and accumulates fp32 in the
+// tensor memory of both CTAs. Each CTA stages its own 128 rows of A and HALF of the B tile per K block of 64, so a
+// stage is 32 KB and the ring has six. When the shape or the device cannot place pairs, the same kernel runs as
+// single CTAs on 128 x 256 tiles with a four-stage ring of 48 KB.
+//   warp 0   one elected thread issues TMA tiled loads (128B swizzle) into the ring, guarded by full/empty
+//            mbarriers; in pair mode the loads carry .cta_group::2 and both CTAs' bytes are counted on the barrier of
+//            the CTA that issues the MMAs
+//   warp 1   one elected thread (of CTA 0 in pair mode) issues the MMAs; tcgen05.commit releases the stage and, after
+//            the last K block, hands the accumulator to the epilogue. Two accumulators (2 x 256 TMEM columns)
+//            alternate so the epilogue of tile i overlaps the MMAs of tile i+1
+//   warps 2-5  read their 32 TMEM lanes with tcgen05.ld, apply the epilogue (bf16 cast, silu(gate)*up, or the sum
+//            with the peers' partial tiles in reduce-scatter mode), transpose through shared memory and write
+//            128-byte row segments to local or peer memory
+// Tiles are walked in a shape-dependent order and the walkers are kept in soft lockstep so that CTAs sharing rows of A
+// or B hit them in L2 together. No TMA load uses cluster multicast and no TMA load reads another GPU's memory:
+// remote operands are first copied into local memory by the copy CTAs of this same kernel.
 #include <algorithm>
 #include <cstdio>
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 
 #include "../cuda/cuda_common.h"
 #include "sm100_ptx.cuh"
@@ -25,25 +31,37 @@ namespace xccl {
 namespace tp {
 namespace {
 
-template <bool kPair>
-__global__ void __launch_bounds__(kThreads, 1)
+// kFp8: block-scaled e4m3 operands (1 x 128 activation scales, 128 x 128 weight scales). A stage holds 128 bytes of
+// K per row, which is 64 bf16 or 128 fp8 values, so both types share one shared-memory geometry. The tensor cores run
+// kind::f8f6f4 and the product of ONE 128-wide K block lands in a fresh tensor-memory buffer (two alternate); eight
+// promotion warps (two per TMEM lane quarter, 128 accumulator columns each) add it into fp32 registers with the two
+// scales while the next K block is multiplied, and run the epilogue of the tile from those registers.
+template <bool kPair, bool kFp8>
+__global__ void __launch_bounds__(kFp8 ? kThreadsFp8 : kThreads, 1)
 tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
 {
-    constexpr int      kNS = kPair ? kStagesPair : kStages;   // pipeline stages
+    constexpr int      kNS = kFp8 ? (kPair ? kStagesPair - 1 : kStages - 1) : (kPair ? kStagesPair : kStages);  // pipeline stages
     constexpr uint32_t kBB = kPair ? kBBytes / 2 : kBBytes;   // bytes of B per stage in this CTA
     constexpr uint32_t kSB = kABytes + kBB;                   // bytes per stage in this CTA
+    constexpr int      kKE = kFp8 ? 2 * kBK : kBK;            // K elements per stage (128 bytes per row)
+    constexpr int      kEpiWarps  = kFp8 ? 8 : 4;
+    constexpr uint32_t kEpiBytesK = kEpiWarps * 32 * kStageRowBytes;
+    // ring of stages, then the epilogue staging rows, then the barriers. The copy CTAs' ring (192 KB) must end
+    // before the barriers in both layouts.
+    constexpr uint32_t kRingBytes = kFp8 ? (uint32_t)(kStages * kStageBytes) - (kEpiBytesK - kEpiBytes) : (uint32_t)(kStages * kStageBytes);
+    static_assert(kNS * kSB <= kRingBytes, "stages fit the ring");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t       *smem_gen  = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t sA        = smem_base;
     const uint32_t sB        = smem_base + kNS * kABytes;
-    uint8_t       *epi_gen   = smem_gen + kStages * kStageBytes;
-    const uint32_t bars      = smem_base + kStages * kStageBytes + kEpiBytes;
+    uint8_t       *epi_gen   = smem_gen + kRingBytes;
+    const uint32_t bars      = smem_base + kRingBytes + kEpiBytesK;
     auto full_bar       = [&](int s) { return bars + 8u * s; };
     auto empty_bar      = [&](int s) { return bars + 8u * (kNS + s); };
     auto tmem_full_bar  = [&](int a) { return bars + 8u * (2 * kNS + a); };
     auto tmem_empty_bar = [&](int a) { return bars + 8u * (2 * kNS + 2 + a); };
-    volatile uint32_t *tmem_slot  = reinterpret_cast<volatile uint32_t *>(epi_gen + kEpiBytes + 8 * (2 * kNS + 4));
+    volatile uint32_t *tmem_slot  = reinterpret_cast<volatile uint32_t *>(epi_gen + kEpiBytesK + 8 * (2 * kNS + 4));
     volatile uint32_t *abort_slot = tmem_slot + 1;
 
     const int warp  = threadIdx.x / 32, lane = threadIdx.x % 32;
@@ -57,6 +75,8 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
 
     if (threadIdx.x == 0) *abort_slot = 0;
     __syncthreads();
+
+    constexpr int kCopierWarp0 = (kFp8 ? kThreadsFp8 : kThreads) / 32 - 2;  // the last two warps: copiers (allgather mode)
 
     // ---- copy CTAs (allgather mode) never touch the tensor cores
     if ((int)blockIdx.x >= p.n_gemm_ctas) {
@@ -72,7 +92,7 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
         }
         for (int a = 0; a < 2; a++) {
             mbar_init(tmem_full_bar(a), 1);
-            mbar_init(tmem_empty_bar(a), kPair ? 8 : 4);  // epilogue warps of every CTA of the tile
+            mbar_init(tmem_empty_bar(a), (kPair ? 2 : 1) * kEpiWarps);  // epilogue warps of every CTA of the tile
         }
         mbar_fence_init();
         tma_prefetch_desc(tmA);
@@ -98,7 +118,7 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
     const int tiles_m    = kPair ? (tiles_m128 + 1) / 2 : tiles_m128;     // row blocks of a tile (256 rows in pair mode)
     const int tiles_n    = (p.N + kBN - 1) / kBN;
     const int total   = tiles_m * tiles_n;
-    const int kblocks = (p.K + kBK - 1) / kBK;
+    const int kblocks = (p.K + kKE - 1) / kKE;
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -128,7 +148,7 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
                 if (kPair) tl.mb = tl.mb * 2 + (int)cta_rank;  // this CTA's 128-row block
                 if (p.comm == COMM_ALLGATHER_A && tl.shard != rank) {
                     // rows of this block are being copied in by the copy CTAs of this kernel
-                    const uint32_t n_copy = gridDim.x - p.n_gemm_ctas;
+                    const uint32_t n_copy = p.copy_mode == 1 ? gridDim.x : gridDim.x - p.n_gemm_ctas;
                     ok = wait_counter(p.ready[local] + tl.mb, p.seq * n_copy, false, ab, 1);
                     asm volatile("fence.proxy.async.global;" ::: "memory");
                     if (!ok) break;
@@ -163,23 +183,23 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
                             mbar_arrive_expect_tx(full_bar(s), 2 * kSB);
                             armed[s] = (int)phase;
                         }
-                        load(sA + s * kABytes, tmA, kb * kBK, tl.mb * kBM, fb, pol_a);
+                        load(sA + s * kABytes, tmA, kb * kKE, tl.mb * kBM, fb, pol_a);
                         if (p.epilogue == EPI_SWIGLU) {
                             // columns 0..127 of the tile are "gate" (rank 0 stages them), 128..255 "up" (rank 1)
-                            load(sB + s * kBB, cta_rank == 0 ? tmB0 : tmB1, kb * kBK, tl.nb * (kBN / 2), fb, pol_b);
+                            load(sB + s * kBB, cta_rank == 0 ? tmB0 : tmB1, kb * kKE, tl.nb * (kBN / 2), fb, pol_b);
                         } else {
-                            load(sB + s * kBB, tmB0, kb * kBK, tl.nb * kBN + (int)cta_rank * (kBN / 2), fb, pol_b);
+                            load(sB + s * kBB, tmB0, kb * kKE, tl.nb * kBN + (int)cta_rank * (kBN / 2), fb, pol_b);
                         }
                     } else {
                         mbar_arrive_expect_tx(full_bar(s), kSB);
                         armed[s] = (int)phase;
-                        load(sA + s * kABytes, tmA, kb * kBK, tl.mb * kBM, full_bar(s), pol_a);
+                        load(sA + s * kABytes, tmA, kb * kKE, tl.mb * kBM, full_bar(s), pol_a);
                         if (p.epilogue == EPI_SWIGLU) {
-                            load(sB + s * kBB, tmB0, kb * kBK, tl.nb * (kBN / 2), full_bar(s), pol_b);
-                            load(sB + s * kBB + kBB / 2, tmB1, kb * kBK, tl.nb * (kBN / 2), full_bar(s), pol_b);
+                            load(sB + s * kBB, tmB0, kb * kKE, tl.nb * (kBN / 2), full_bar(s), pol_b);
+                            load(sB + s * kBB + kBB / 2, tmB1, kb * kKE, tl.nb * (kBN / 2), full_bar(s), pol_b);
                         } else {
-                            load(sB + s * kBB, tmB0, kb * kBK, tl.nb * kBN, full_bar(s), pol_b);
-                            load(sB + s * kBB + kBB / 2, tmB0, kb * kBK, tl.nb * kBN + kBN / 2, full_bar(s), pol_b);
+                            load(sB + s * kBB, tmB0, kb * kKE, tl.nb * kBN, full_bar(s), pol_b);
+                            load(sB + s * kBB + kBB / 2, tmB0, kb * kKE, tl.nb * kBN + kBN / 2, full_bar(s), pol_b);
                         }
                     }
                     if (++s == kNS) {
@@ -198,10 +218,16 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
                 }
             }
         }
+    } else if (warp >= kCopierWarp0) {
+        // ------------------------------------------------------------ copier warps
+        if (p.comm == COMM_ALLGATHER_A && p.copy_mode == 1 && p.tp_size > 1) {
+            copier_warps_loop(p, rank, local, (int)threadIdx.x - kCopierWarp0 * 32, ab);
+        }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if ((!kPair || cta_rank == 0) && elect_one()) {
-            const uint32_t idesc = make_idesc(1, 1, kPair ? 2 * kBM : kBM, kBN);
+            const uint32_t idesc = kFp8 ? make_idesc(0, 0, kPair ? 2 * kBM : kBM, kBN)   // e4m3 x e4m3 -> fp32
+                                        : make_idesc(1, 1, kPair ? 2 * kBM : kBM, kBN);  // bf16 x bf16 -> fp32
             int            s = 0;
             uint32_t       phase = 0, acc_phase = 0;
             int            a = 0;
@@ -215,7 +241,37 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
                     mma_commit(bar);
                 }
             };
-            for (int t = unit; t < total && ok; t += n_units) {
+            for (int t = unit; kFp8 && t < total && ok; t += n_units) {
+                // one product buffer per K block: the promotion warps empty it while the next block is multiplied
+                for (int kb = 0; kb < kblocks; kb++) {
+                    if (!mbar_wait(tmem_empty_bar(a), acc_phase ^ 1, ab, 3) || !mbar_wait(full_bar(s), phase, ab, 4)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t d_tmem = tmem_base + (uint32_t)a * kBN;
+                    const uint64_t da = make_desc_sw128(sA + s * kABytes);
+                    const uint64_t db = make_desc_sw128(sB + s * kBB);
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        // 32 fp8 values = 32 bytes further along K inside the 128-byte swizzle row
+                        if (kPair) {
+                            mma_f8_pair(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, k != 0);
+                        } else {
+                            mma_f8(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, k != 0);
+                        }
+                    }
+                    commit(empty_bar(s));
+                    commit(tmem_full_bar(a));
+                    if (++s == kNS) {
+                        s = 0;
+                        phase ^= 1;
+                    }
+                    a ^= 1;
+                    if (a == 0) acc_phase ^= 1;
+                }
+            }
+            for (int t = unit; !kFp8 && t < total && ok; t += n_units) {
                 if (!mbar_wait(tmem_empty_bar(a), acc_phase ^ 1, ab, 3)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)a * kBN;
@@ -246,6 +302,213 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
                 commit(tmem_full_bar(a));
                 a ^= 1;
                 if (a == 0) acc_phase ^= 1;
+            }
+        }
+    } else if (kFp8) {
+        // ------------------------------------------------------------ promotion + epilogue warps (fp8)
+        const int      quarter = warp % 4;        // TMEM lanes this warp may read: 32*quarter ..
+        const int      half    = (warp - 2) / 4;  // which 128 of the 256 accumulator columns
+        uint8_t       *stage   = epi_gen + (warp - 2) * 32 * kStageRowBytes;
+        uint32_t       acc_phase = 0;
+        int            a = 0;
+        const int      mbs   = (p.comm == COMM_NONE) ? tiles_m128 : tiles_m128 / p.tp_size;
+        const bool     swi   = p.epilogue == EPI_SWIGLU;
+        const int      n_out = swi ? p.N / 2 : p.N;
+        // the two 64-column ranges of the accumulator this warp owns: plain tiles one weight block (128 columns),
+        // SwiGLU tiles 64 "gate" columns and the 64 "up" columns of the same outputs
+        const int      c0 = swi ? half * 64 : half * 128, c1 = swi ? kBN / 2 + half * 64 : half * 128 + 64;
+        bool           ok = true;
+        for (int t = unit; t < total && ok; t += n_units) {
+            Tile tl = tile_of(p, rank, t, tiles_m, tiles_n);
+            if (kPair) tl.mb = tl.mb * 2 + (int)cta_rank;
+            const int  row    = tl.mb * kBM + quarter * 32 + lane;
+            const bool row_ok = row < p.M;
+            // running sums as pairs: the promotion is one packed fp32 FMA per two columns
+            float2     acc2[64];
+#pragma unroll
+            for (int j = 0; j < 64; j++) acc2[j] = make_float2(0.0f, 0.0f);
+            const float *sa_row = p.sg[rank] + (size_t)(row_ok ? row : 0) * kblocks;
+            // weight scales: [rows / 128][K / 128]; a plain tile spans two weight blocks, a SwiGLU tile one of each matrix
+            const int    wblk = (tl.nb * 2 + half) * 128 < p.N ? tl.nb * 2 + half : 0;  // a last tile may be half outside N
+            const float *sb_0 = swi ? p.sb0[local] + (size_t)tl.nb * kblocks : p.sb0[local] + (size_t)wblk * kblocks;
+            const float *sb_1 = swi ? p.sb1[local] + (size_t)tl.nb * kblocks : sb_0;
+            for (int kb = 0; kb < kblocks; kb++) {
+                if (!mbar_wait(tmem_full_bar(a), acc_phase, ab, 5)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                // the scales of gathered rows arrive with the rows: read them only now that the product of this K
+                // block exists (its operands were released by the copy CTAs), and from L2, not a stale L1 line
+                const float a_s = row_ok ? __ldcg(sa_row + kb) : 0.0f;
+                const float s0 = a_s * __ldg(sb_0 + kb), s1 = a_s * __ldg(sb_1 + kb);
+                const uint32_t t_acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)a * kBN;
+                // eight chunks of 16 columns through two register buffers: the load of chunk c+1 is in flight while
+                // chunk c is added up
+                uint32_t v[2][16];
+                tmem_ld_32x16(t_acc + (uint32_t)c0, v[0]);
+#pragma unroll
+                for (int c = 0; c < 8; c++) {
+                    tmem_ld_wait();
+                    if (c < 7) tmem_ld_32x16(t_acc + (uint32_t)(((c + 1) < 4 ? c0 : c1) + ((c + 1) & 3) * 16), v[(c + 1) & 1]);
+                    const float  sc  = (c < 4) ? s0 : s1;
+                    const float2 sc2 = make_float2(sc, sc);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const float2 x = make_float2(__uint_as_float(v[c & 1][2 * j]), __uint_as_float(v[c & 1][2 * j + 1]));
+                        acc2[c * 8 + j] = __ffma2_rn(sc2, x, acc2[c * 8 + j]);
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    if (kPair) {
+                        mbar_arrive_cluster(map_to_cta(tmem_empty_bar(a), 0));
+                    } else {
+                        mbar_arrive(tmem_empty_bar(a));
+                    }
+                }
+                a ^= 1;
+                if (a == 0) acc_phase ^= 1;
+            }
+            if (!ok) break;
+            // ---- epilogue of the tile from the registers
+            float acc[128];
+#pragma unroll
+            for (int j = 0; j < 64; j++) {
+                acc[2 * j]     = acc2[j].x;
+                acc[2 * j + 1] = acc2[j].y;
+            }
+            __nv_bfloat16 *out;
+            size_t         ld;
+            int            row0;
+            const bool     own_rs = (p.comm == COMM_REDUCE_SCATTER_C) && p.rs_fused != 0 && tl.shard == rank;
+            const __nv_bfloat16 *rs_parts = nullptr;
+            size_t               rs_slot  = 0;
+            if (own_rs) {
+                const size_t shard_rows = (size_t)mbs * kBM;
+                rs_slot  = shard_rows * (size_t)p.N;
+                rs_parts = p.part[rank] + (size_t)(p.seq & 1) * p.tp_size * rs_slot;
+                out      = p.C[local];
+                ld       = (size_t)p.ldc;
+                row0     = (tl.mb - tl.shard * mbs) * kBM;
+                int good = 1;
+                if (lane < p.tp_size && lane != rank) {
+                    const uint32_t *ctr = p.pad[rank] + nvl::kPadCounterOff + ((p.seq & 1) * p.tp_size + lane) * 64 +
+                                          (tl.mb - tl.shard * mbs);
+                    good = (p.rs_debug_local || wait_counter(ctr, p.rs_target, true, ab, 6)) ? 1 : 0;
+                }
+                if (!__all_sync(0xffffffffu, good)) break;
+            } else if (p.comm == COMM_REDUCE_SCATTER_C) {
+                const size_t shard_rows = (size_t)mbs * kBM;
+                out  = p.part[p.rs_debug_local ? rank : tl.shard] + ((size_t)(p.seq & 1) * p.tp_size + rank) * shard_rows * (size_t)p.N;
+                ld   = (size_t)p.N;
+                row0 = (tl.mb - tl.shard * mbs) * kBM;
+            } else {
+                out  = p.C[local];
+                ld   = (size_t)p.ldc;
+                row0 = tl.mb * kBM;
+            }
+            const int rows_valid = ((p.comm == COMM_REDUCE_SCATTER_C) ? mbs * kBM : p.M) - row0;
+            if (swi) {
+#pragma unroll
+                for (int j = 0; j < 64; j++) acc[j] = silu(acc[j]) * acc[64 + j];
+            }
+            // first output column of this warp's registers, and how many 64-column groups they hold
+            const int col_base = swi ? tl.nb * (kBN / 2) + half * 64 : tl.nb * kBN + half * 128;
+            const int groups   = swi ? 1 : 2;
+            if (swi && p.out_fp8 != 0) {
+                // the 128 outputs of this row in this tile are one 1 x 128 quantisation block of the next GEMM's
+                // activations: amax over both halves (the partner warp holds the other 64), one scale, e4m3 bytes
+                float amax = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 64; j++) amax = fmaxf(amax, fabsf(acc[j]));
+                float *xch = reinterpret_cast<float *>(stage);  // 32 floats of this warp's staging rows
+                xch[lane]  = amax;
+                asm volatile("bar.sync %0, 64;" ::"r"(2 + quarter) : "memory");
+                const float *other = reinterpret_cast<const float *>(epi_gen + ((warp - 2) ^ 4) * 32 * kStageRowBytes);
+                amax               = fmaxf(amax, other[lane]);
+                asm volatile("bar.sync %0, 64;" ::"r"(2 + quarter) : "memory");
+                const float sc = fmaxf(amax, 1e-12f) / 448.0f, inv = 1.0f / sc;
+                uint8_t    *o8 = reinterpret_cast<uint8_t *>(p.C[local]);
+                if (row_ok) {
+                    if (half == 0) p.out_scale[local][(size_t)row * (size_t)(n_out / 128) + tl.nb] = sc;
+                    uint4 *dstp = reinterpret_cast<uint4 *>(o8 + (size_t)row * (size_t)p.ldc + col_base);
+#pragma unroll
+                    for (int g4 = 0; g4 < 4; g4++) {
+                        uint32_t w4[4];
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {
+                            const int j = g4 * 16 + q * 4;
+                            w4[q] = (uint32_t)__nv_cvt_float_to_fp8(acc[j] * inv, __NV_SATFINITE, __NV_E4M3) |
+                                    ((uint32_t)__nv_cvt_float_to_fp8(acc[j + 1] * inv, __NV_SATFINITE, __NV_E4M3) << 8) |
+                                    ((uint32_t)__nv_cvt_float_to_fp8(acc[j + 2] * inv, __NV_SATFINITE, __NV_E4M3) << 16) |
+                                    ((uint32_t)__nv_cvt_float_to_fp8(acc[j + 3] * inv, __NV_SATFINITE, __NV_E4M3) << 24);
+                        }
+                        dstp[g4] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                    }
+                }
+            } else {
+                for (int g = 0; g < groups; g++) {
+                    uint4 *rowp = reinterpret_cast<uint4 *>(stage + lane * kStageRowBytes);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        // g is 0 or 1: constant indices after unrolling both branches
+                        if (g == 0) {
+                            rowp[j] = make_uint4(pack_bf16x2(acc[8 * j], acc[8 * j + 1]), pack_bf16x2(acc[8 * j + 2], acc[8 * j + 3]),
+                                                 pack_bf16x2(acc[8 * j + 4], acc[8 * j + 5]), pack_bf16x2(acc[8 * j + 6], acc[8 * j + 7]));
+                        } else {
+                            rowp[j] = make_uint4(pack_bf16x2(acc[64 + 8 * j], acc[64 + 8 * j + 1]), pack_bf16x2(acc[64 + 8 * j + 2], acc[64 + 8 * j + 3]),
+                                                 pack_bf16x2(acc[64 + 8 * j + 4], acc[64 + 8 * j + 5]), pack_bf16x2(acc[64 + 8 * j + 6], acc[64 + 8 * j + 7]));
+                        }
+                    }
+                    __syncwarp();
+                    const int col0 = col_base + g * 64;
+#pragma unroll
+                    for (int it = 0; it < 8; it++) {
+                        const int r = it * 4 + lane / 8, chunk = lane % 8;
+                        const int grow = quarter * 32 + r, gcol = col0 + chunk * 8;
+                        if (grow < rows_valid && gcol < n_out) {
+                            uint4 v = *reinterpret_cast<const uint4 *>(stage + r * kStageRowBytes + chunk * 16);
+                            if (own_rs) {
+                                // (registers are scarce next to the 128 running sums: two partials in flight at a time)
+                                const size_t off = (size_t)(row0 + grow) * (size_t)p.N + gcol;
+                                float        sum[8];
+#pragma unroll
+                                for (int e = 0; e < 8; e++) sum[e] = 0.0f;
+                                for (int src = 0; src < p.tp_size; src += 2) {
+                                    uint4 x0 = (src == rank) ? v : nvl::ld_nc16(rs_parts + (size_t)src * rs_slot + off);
+                                    uint4 x1 = make_uint4(0, 0, 0, 0);
+                                    if (src + 1 < p.tp_size) x1 = (src + 1 == rank) ? v : nvl::ld_nc16(rs_parts + (size_t)(src + 1) * rs_slot + off);
+                                    const __nv_bfloat162 *h0 = reinterpret_cast<const __nv_bfloat162 *>(&x0);
+                                    const __nv_bfloat162 *h1 = reinterpret_cast<const __nv_bfloat162 *>(&x1);
+#pragma unroll
+                                    for (int e = 0; e < 4; e++) {
+                                        const float2 f0 = __bfloat1622float2(h0[e]), f1 = __bfloat1622float2(h1[e]);
+                                        sum[2 * e] += f0.x;
+                                        sum[2 * e + 1] += f0.y;
+                                        sum[2 * e] += f1.x;
+                                        sum[2 * e + 1] += f1.y;
+                                    }
+                                }
+                                v = make_uint4(pack_bf16x2(sum[0], sum[1]), pack_bf16x2(sum[2], sum[3]),
+                                               pack_bf16x2(sum[4], sum[5]), pack_bf16x2(sum[6], sum[7]));
+                            }
+                            *reinterpret_cast<uint4 *>(out + (size_t)(row0 + grow) * ld + gcol) = v;
+                        }
+                    }
+                    __syncwarp();
+                }
+            }
+            if (p.comm == COMM_REDUCE_SCATTER_C && !own_rs) {
+                // all eight epilogue warps have stored their part of the rows: tell the owner one more tile arrived
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                if (warp == 2 && lane == 0) {
+                    __threadfence_system();
+                    uint32_t *ctr = p.pad[p.rs_debug_local ? rank : tl.shard] + nvl::kPadCounterOff +
+                                    ((p.seq & 1) * p.tp_size + rank) * 64 + (tl.mb - tl.shard * mbs);
+                    nvl::red_release_sys_add(ctr, 1u);
+                }
             }
         }
     } else {
@@ -285,13 +548,13 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
                 if (lane < p.tp_size && lane != rank) {
                     const uint32_t *ctr = p.pad[rank] + nvl::kPadCounterOff + ((p.seq & 1) * p.tp_size + lane) * 64 +
                                           (tl.mb - tl.shard * mbs);
-                    good = wait_counter(ctr, p.rs_target, true, ab, 6) ? 1 : 0;
+                    good = (p.rs_debug_local || wait_counter(ctr, p.rs_target, true, ab, 6)) ? 1 : 0;
                 }
                 if (!__all_sync(0xffffffffu, good)) break;
             } else if (p.comm == COMM_REDUCE_SCATTER_C) {
                 // slot `rank` of the owner's partial buffer, parity by launch sequence
                 const size_t shard_rows = (size_t)mbs * kBM;
-                out  = p.part[tl.shard] + ((size_t)(p.seq & 1) * p.tp_size + rank) * shard_rows * (size_t)p.N;
+                out  = p.part[p.rs_debug_local ? rank : tl.shard] + ((size_t)(p.seq & 1) * p.tp_size + rank) * shard_rows * (size_t)p.N;
                 ld   = (size_t)p.N;
                 row0 = (tl.mb - tl.shard * mbs) * kBM;
             } else {
@@ -390,7 +653,7 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (warp == 2 && lane == 0) {
                     __threadfence_system();
-                    uint32_t *ctr = p.pad[tl.shard] + nvl::kPadCounterOff +
+                    uint32_t *ctr = p.pad[p.rs_debug_local ? rank : tl.shard] + nvl::kPadCounterOff +
                                     ((p.seq & 1) * p.tp_size + rank) * 64 + (tl.mb - tl.shard * mbs);
                     nvl::red_release_sys_add(ctr, 1u);
                 }
@@ -418,6 +681,30 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
 }
 
 }  // namespace
+
+const OptTable &tp_options()
+{
+    static OptTable t = [] {
+        OptTable o("TP_", {
+            {"GEMM_PAIR", "y", "Run the GEMM kernels as CTA pairs (cta_group::2, 256 x 256 tiles) when the shape allows", OptType::BOOL},
+            {"GEMM_GROUP", "0", "Row blocks of tiles walked together before moving along N (0: chosen from the shape)", OptType::UINT},
+            {"GEMM_L2HINT", "0", "Cache hints of the operand loads: 0 none, 1 A and B evict_last, 2 A evict_last / B evict_first, 3 the reverse", OptType::UINT},
+            {"GEMM_L2PROMO", "3", "L2 promotion of the tensor maps: 0 none, 1 64 B, 2 128 B, 3 256 B", OptType::UINT},
+            {"GEMM_STCS", "n", "Mark output stores as streaming (evict first)", OptType::BOOL},
+            {"GEMM_SYNC", "y", "Keep the tile walkers in soft lockstep (one counter per wave of tiles)", OptType::BOOL},
+            {"GEMM_SYNC_KBLOCKS", "0", "Also synchronise every this many K blocks inside a tile (0: tile starts only)", OptType::UINT},
+            {"GEMM_SYNC_NS", "30000", "Longest wait at a lockstep point in nanoseconds; running out is not an error", OptType::UINT},
+            {"COPY_MODE", "1", "allgather->GEMM: 1 = two copier warps in every CTA pull the remote shards, 0 = whole CTAs are set aside for it (COPY_CTAS)", OptType::UINT},
+            {"COPY_CTAS", "0", "Copy mode 0: CTAs that pull the remote shards (0: 16)", OptType::UINT},
+            {"RS_DEBUG_LOCAL", "n", "Diagnostic, wrong results: GEMM->reduce-scatter stores every partial tile into local memory and waits for nobody, to time the kernel without its NVLink traffic", OptType::BOOL},
+            {"RS_FUSED", "y", "GEMM->reduce-scatter: add the peers' partial tiles in the epilogue of the local tiles instead of a reduce phase after the last tile", OptType::BOOL},
+            {"H2D_CHUNK_ROWS", "256", "Rows per chunk of the overlapped host->device input copy", OptType::UINT},
+        });
+        o.read(nullptr, nullptr);
+        return o;
+    }();
+    return t;
+}
 
 uint32_t *error_word()
 {
@@ -456,11 +743,7 @@ xccl_status_t make_tensor_map_2d(CUtensorMap *map, const void *base, uint64_t ro
     cuuint64_t strides[1] = {ld * 2};
     cuuint32_t box[2]     = {(cuuint32_t)kBK, box_rows};
     cuuint32_t estr[2]    = {1, 1};
-    static int promo = -1;
-    if (promo < 0) {
-        const char *e = getenv("XCCL_TP_GEMM_L2PROMO");  // 0 none, 1 64 B, 2 128 B, 3 256 B
-        promo         = (e != nullptr) ? std::max(0, std::min(3, atoi(e))) : 3;
-    }
+    const int promo = (int)std::max(0ll, std::min(3ll, tp_options().num("GEMM_L2PROMO")));
     const CUtensorMapL2promotion pr = promo == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE
                                     : promo == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
                                     : promo == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
@@ -471,7 +754,27 @@ xccl_status_t make_tensor_map_2d(CUtensorMap *map, const void *base, uint64_t ro
     return XCCL_OK;
 }
 
+namespace {
+xccl_status_t launch_gemm_impl(const GemmParams &p_in, const GemmLaunch &l, cudaStream_t stream, bool fp8);
+}
+
 xccl_status_t launch_gemm(const GemmParams &p_in, const GemmLaunch &l, cudaStream_t stream)
+{
+    return launch_gemm_impl(p_in, l, stream, false);
+}
+
+// Block-scaled fp8: K in whole 128-wide scale blocks, N in whole 128-column weight blocks.
+xccl_status_t launch_gemm_fp8(const GemmParams &p_in, const GemmLaunch &l, cudaStream_t stream)
+{
+    GemmParams p = p_in;
+    if (p.M <= 0 || p.N <= 0 || p.K <= 0 || p.K % 128 != 0 || p.N % 128 != 0) return XCCL_ERR_INVALID_PARAM;
+    if (p.out_fp8 != 0 && p.epilogue != EPI_SWIGLU) return XCCL_ERR_INVALID_PARAM;
+    p.a_bytes = 1;
+    return launch_gemm_impl(p, l, stream, true);
+}
+
+namespace {
+xccl_status_t launch_gemm_impl(const GemmParams &p_in, const GemmLaunch &l, cudaStream_t stream, bool fp8)
 {
     GemmParams p = p_in;
     if (p.K % 8 != 0 || p.N % 8 != 0 || p.M <= 0 || p.N <= 0 || p.K <= 0) return XCCL_ERR_INVALID_PARAM;
@@ -485,45 +788,30 @@ xccl_status_t launch_gemm(const GemmParams &p_in, const GemmLaunch &l, cudaStrea
     XCCL_CUDA_CHECK(cudaGetDevice(&dev));
     XCCL_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     if (!attr_set[dev]) {
-        XCCL_CUDA_CHECK(cudaFuncSetAttribute(tp_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-        XCCL_CUDA_CHECK(cudaFuncSetAttribute(tp_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        XCCL_CUDA_CHECK(cudaFuncSetAttribute(tp_gemm_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        XCCL_CUDA_CHECK(cudaFuncSetAttribute(tp_gemm_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        XCCL_CUDA_CHECK(cudaFuncSetAttribute(tp_gemm_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        XCCL_CUDA_CHECK(cudaFuncSetAttribute(tp_gemm_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
         attr_set[dev] = true;
     }
     int ctas = l.ctas > 0 ? l.ctas : sms / std::max(l.n_local, 1);
     if (p.n_gemm_ctas <= 0 || p.n_gemm_ctas > ctas) p.n_gemm_ctas = ctas;
-    if (p.comm == COMM_ALLGATHER_A && p.tp_size > 1 && p.n_gemm_ctas == ctas) return XCCL_ERR_INVALID_PARAM;
+    if (p.comm == COMM_ALLGATHER_A && p.tp_size > 1 && p.copy_mode == 0 && p.n_gemm_ctas == ctas) return XCCL_ERR_INVALID_PARAM;
+    if (p.copy_mode == 1) p.n_gemm_ctas = ctas;
     if (p.error == nullptr) p.error = error_word();
     if (p.budget_ns == 0) p.budget_ns = 4000000000ull;
 
     // CTA pairs (clusters of two, one 256-row tile per pair) when the shape allows: an even number of
     // CTAs in each role and, with communication, row shards made of whole 256-row tiles.
-    static int pair_env = -1;
-    if (pair_env < 0) {
-        const char *e = getenv("XCCL_TP_GEMM_PAIR");
-        pair_env      = (e == nullptr || atoi(e) != 0) ? 1 : 0;
-    }
-    static int group_env = -1;
-    if (group_env < 0) {
-        const char *e = getenv("XCCL_TP_GEMM_GROUP");
-        group_env     = (e != nullptr && atoi(e) > 0) ? atoi(e) : 0;
-    }
+    const OptTable &opt       = tp_options();
+    const int       pair_env  = opt.flag("GEMM_PAIR") ? 1 : 0;
+    const int       group_env = (int)opt.num("GEMM_GROUP");
     if (p.group_rows <= 0) p.group_rows = group_env;
-    static int hint_env = -1, stcs_env = -1;
-    if (hint_env < 0) {
-        const char *e = getenv("XCCL_TP_GEMM_L2HINT");
-        hint_env      = (e != nullptr) ? std::max(0, std::min(3, atoi(e))) : 0;
-        e             = getenv("XCCL_TP_GEMM_STCS");
-        stcs_env      = (e != nullptr && atoi(e) != 0) ? 1 : 0;
-    }
-    static int sync_env = -1, sync_kb_env = 0, sync_ns_env = 30000;
-    if (sync_env < 0) {
-        const char *e = getenv("XCCL_TP_GEMM_SYNC");
-        sync_env      = (e == nullptr || atoi(e) != 0) ? 1 : 0;
-        e             = getenv("XCCL_TP_GEMM_SYNC_KBLOCKS");
-        if (e != nullptr) sync_kb_env = std::max(0, atoi(e));
-        e = getenv("XCCL_TP_GEMM_SYNC_NS");
-        if (e != nullptr) sync_ns_env = std::max(0, atoi(e));
-    }
+    const int hint_env    = (int)std::max(0ll, std::min(3ll, opt.num("GEMM_L2HINT")));
+    const int stcs_env    = opt.flag("GEMM_STCS") ? 1 : 0;
+    const int sync_env    = opt.flag("GEMM_SYNC") ? 1 : 0;
+    const int sync_kb_env = (int)opt.num("GEMM_SYNC_KBLOCKS");
+    const int sync_ns_env = (int)opt.num("GEMM_SYNC_NS");
     for (int i = 0; i < kMaxTpRanks; i++) p.sync_ctr[i] = nullptr;
     p.sync_points = 0;
     if (sync_env == 1 && l.n_local <= kMaxTpRanks) {
@@ -531,7 +819,7 @@ xccl_status_t launch_gemm(const GemmParams &p_in, const GemmLaunch &l, cudaStrea
         // worth it only when a walker has several tiles: the drift builds up over tiles
         const int  tile_rows = 2 * kBM;
         const long tiles     = (long)((p.M + tile_rows - 1) / tile_rows) * ((p.N + kBN - 1) / kBN);
-        const int  kblocks   = (p.K + kBK - 1) / kBK;
+        const int  kblocks   = (p.K + (fp8 ? 2 * kBK : kBK) - 1) / (fp8 ? 2 * kBK : kBK);
         const int  per_tile  = sync_kb_env > 0 ? (kblocks + sync_kb_env - 1) / sync_kb_env : 1;
         const long waves     = (tiles + std::max(1, ctas / 2) - 1) / std::max(1, ctas / 2) * 2 + 2;  // single-CTA walkers: half-size tiles
         const long points    = std::min<long>(waves * per_tile, kSyncPoints);
@@ -563,7 +851,7 @@ xccl_status_t launch_gemm(const GemmParams &p_in, const GemmLaunch &l, cudaStrea
     p.group_rows           = group_single;
 
     cudaLaunchConfig_t cfg{};
-    cfg.blockDim         = dim3(kThreads);
+    cfg.blockDim         = dim3(fp8 ? kThreadsFp8 : kThreads);
     cfg.dynamicSmemBytes = kSmemBytes;
     cfg.stream           = stream;
     cudaLaunchAttribute attr[2];
@@ -586,9 +874,11 @@ xccl_status_t launch_gemm(const GemmParams &p_in, const GemmLaunch &l, cudaStrea
         cfg.gridDim              = dim3((unsigned)pctas, (unsigned)l.n_local);
         // every CTA of the grid must be resident at once: roles wait for one another
         int         max_clusters = 0;
-        cudaError_t oe           = cudaOccupancyMaxActiveClusters(&max_clusters, tp_gemm_kernel<true>, &cfg);
+        cudaError_t oe           = fp8 ? cudaOccupancyMaxActiveClusters(&max_clusters, tp_gemm_kernel<true, true>, &cfg)
+                                       : cudaOccupancyMaxActiveClusters(&max_clusters, tp_gemm_kernel<true, false>, &cfg);
         if (oe == cudaSuccess && pp.n_gemm_ctas >= 2 && max_clusters * 2 >= pctas * l.n_local) {
-            cudaError_t le = cudaLaunchKernelEx(&cfg, tp_gemm_kernel<true>, pp, l);
+            cudaError_t le = fp8 ? cudaLaunchKernelEx(&cfg, tp_gemm_kernel<true, true>, pp, l)
+                                 : cudaLaunchKernelEx(&cfg, tp_gemm_kernel<true, false>, pp, l);
             if (le == cudaSuccess) return XCCL_OK;
             (void)cudaGetLastError();
             xccl_warn("tp gemm: launch with CTA pairs refused (%s); using single CTAs", cudaGetErrorString(le));
@@ -600,9 +890,14 @@ xccl_status_t launch_gemm(const GemmParams &p_in, const GemmLaunch &l, cudaStrea
         cfg.numAttrs      = 1;
     }
     cfg.gridDim = dim3((unsigned)ctas, (unsigned)l.n_local);
-    XCCL_CUDA_CHECK(cudaLaunchKernelEx(&cfg, tp_gemm_kernel<false>, p, l));
+    if (fp8) {
+        XCCL_CUDA_CHECK(cudaLaunchKernelEx(&cfg, tp_gemm_kernel<false, true>, p, l));
+    } else {
+        XCCL_CUDA_CHECK(cudaLaunchKernelEx(&cfg, tp_gemm_kernel<false, false>, p, l));
+    }
     return XCCL_OK;
 }
+}  // namespace
 
 }  // namespace tp
 }  // namespace xccl
@@ -669,6 +964,11 @@ int xccl_tp_tile_order(int tiles_m, int tiles_n, int tp, int rank, int comm, int
         shard[t] = tl.shard;
     }
     return total;
+}
+
+void xccl_tp_config_print(FILE *stream)
+{
+    if (stream != nullptr) xccl::tp::tp_options().print(stream, "fused tensor-parallel kernels", XCCL_CONFIG_PRINT_CONFIG | XCCL_CONFIG_PRINT_DOC | XCCL_CONFIG_PRINT_HEADER);
 }
 
 uint32_t xccl_gemm_last_error(void)

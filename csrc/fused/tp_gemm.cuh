@@ -16,6 +16,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include "../core/config.h"
 #include "../tl/nvlink/nvl_device.cuh"
 #include "xccl/xccl.h"
 
@@ -23,7 +24,8 @@ namespace xccl {
 namespace tp {
 
 constexpr int kBM = 128, kBN = 256, kBK = 64, kStages = 4;
-constexpr int kThreads = 192;           // warp 0: TMA, warp 1: MMA, warps 2-5: epilogue
+constexpr int kThreads = 256;           // warp 0: TMA, warp 1: MMA, warps 2-5: epilogue, warps 6-7: copiers (allgather mode)
+constexpr int kThreadsFp8 = 384;        // block-scaled fp8: warps 2-9 promote the per-K-block products and run the epilogue, 10-11 copy
 constexpr int kMaxTpRanks = 8;
 
 enum Epilogue { EPI_STORE = 0, EPI_SWIGLU = 1 };
@@ -35,7 +37,8 @@ struct GemmParams {
     int comm;
     int tp_size;          // ranks taking part (1 without communication)
     int rank_base;        // team rank of blockIdx.y == 0
-    int n_gemm_ctas;      // CTAs (per rank) that run MMA tiles; the rest copy (allgather mode)
+    int n_gemm_ctas;      // CTAs (per rank) that run MMA tiles; the rest copy (allgather mode, copy_mode 0)
+    int copy_mode;        // allgather mode: 0 = whole CTAs set aside for the copy, 1 = two copier warps in every CTA
     int group_rows;       // row blocks of tiles walked together before moving along N (0 = chosen from the shape)
     int l2_hint;          // operand loads: 0 no hint, 1 A and B evict_last, 2 A evict_last / B evict_first, 3 the reverse
     int st_stream;        // 1: output stores are marked streaming (evict first)
@@ -49,6 +52,7 @@ struct GemmParams {
     unsigned  sync_budget_ns;
     uint32_t seq;         // launch sequence number (starts at 1): readiness counters and buffer parity follow it
     uint32_t rs_target;   // reduce-scatter: running total of tiles per (source, row block) for this parity
+    int      rs_debug_local;  // diagnostic (wrong results): partial tiles go to local memory and nobody is waited for
     int      rs_fused;    // reduce-scatter: 1 = the tiles of the local rows (walked last) add the other ranks' partial
                           // tiles in their epilogue and write the result; 0 = a reduce phase after the last tile
     unsigned long long budget_ns;
@@ -72,6 +76,10 @@ struct GemmParams {
     float         *sg[kMaxTpRanks];        // TEAM rank: scales of A, [M, K/128]; gathered together with xg in allgather mode
     const float   *sb0[kMaxTpRanks];       // LOCAL rank: scales of B0, [rows/128, K/128]
     const float   *sb1[kMaxTpRanks];       // LOCAL rank: scales of B1 (SwiGLU "up")
+    // fp8 SwiGLU: 1 = C is an e4m3 matrix [M, F] (ldc bytes per row) quantised per row and 128 columns in the epilogue,
+    // with its scales written to out_scale [M, F / 128]: the activations of the next GEMM, with no pass in between
+    int            out_fp8;
+    float         *out_scale[kMaxTpRanks]; // LOCAL rank
     // reduce-scatter mode: part[r] = rank r's partial buffer [tp_size][M/tp_size][N] as mapped here
     __nv_bfloat16 *part[kMaxTpRanks];     // indexed by TEAM rank
     uint32_t      *pad[kMaxTpRanks];      // signal pads (TEAM rank) for barriers and arrival counters
@@ -97,6 +105,10 @@ xccl_status_t launch_gemm(const GemmParams &p, const GemmLaunch &l, cudaStream_t
 xccl_status_t make_tensor_map_u8(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 xccl_status_t launch_gemm_fp8(const GemmParams &p, const GemmLaunch &l, cudaStream_t stream);
 
+// Tuning options of the fused kernels: the option table "TP_" of the library's configuration system, read once from
+// the environment (XCCL_TP_<NAME>) like every other option table and listed by xccl_tp_config_print().
+const OptTable &tp_options();
+
 size_t gemm_smem_bytes();
 uint32_t *error_word();  // per-device error word shared by the GEMM kernels
 
@@ -112,4 +124,6 @@ xccl_status_t xccl_gemm_swiglu_bf16(const void *A, const void *Wg, const void *W
                                     void *stream);
 // Last error word written by a GEMM kernel on the current device (0 = none); clears it.
 uint32_t      xccl_gemm_last_error(void);
+// Prints the tuning options of the fused kernels (XCCL_TP_*) with their current values and documentation.
+void          xccl_tp_config_print(FILE *stream);
 }

@@ -34,6 +34,8 @@ struct TpWorkspace {
     size_t    off_xg = 0, off_part = 0, total = 0;
     uint32_t  seq_ag = 0, seq_rs = 0, rs_count[2] = {0, 0};
     int       copy_ctas = 0;      // CTAs of the allgather->GEMM kernel that pull the remote shards; 0 = by team size
+    int       copy_mode = 1;      // 1: copier warps in every CTA, 0: whole copy CTAs
+    bool      rs_debug_local = false;
     bool      rs_fused  = true;   // XCCL_TP_RS_FUSED=0: separate reduce phase after the last tile
     // input rows arriving from the host while the allgather->GEMM kernel already runs
     uint32_t   *in_flags[kMaxTpRanks] = {nullptr};  // per LOCAL rank: one word per chunk of in_rows rows
@@ -105,10 +107,11 @@ xccl_status_t xccl_tp_ws_create(const xccl_oob_collectives_t *oob, int emu_ranks
     w->M = M;
     w->K = K;
     w->N_rs = N_rs;
-    const char *cc = std::getenv("XCCL_TP_COPY_CTAS");
-    if (cc != nullptr && std::atoi(cc) > 0) w->copy_ctas = std::atoi(cc);
-    const char *rf = std::getenv("XCCL_TP_RS_FUSED");
-    if (rf != nullptr) w->rs_fused = std::atoi(rf) != 0;
+    w->copy_ctas = (int)tp_options().num("COPY_CTAS");
+    w->copy_mode = (int)tp_options().num("COPY_MODE") != 0 ? 1 : 0;
+    w->rs_debug_local = tp_options().flag("RS_DEBUG_LOCAL");
+    w->rs_fused  = tp_options().flag("RS_FUSED");
+    w->in_rows   = std::max(1, (int)tp_options().num("H2D_CHUNK_ROWS"));
     layout(w);
     xccl_status_t st = XCCL_OK;
     if (oob == nullptr) {
@@ -146,10 +149,10 @@ xccl_status_t xccl_tp_ws_create(const xccl_oob_collectives_t *oob, int emu_ranks
             }
         }
     }
-    // Copy CTAs only have to stay ahead of the tile walk (the walk starts on the local shard): 8 ranks need about
-    // 200 GB/s of the link, fewer ranks much less. Every CTA taken from the MMA side costs tensor throughput, and
-    // with 8 ranks 70 CTA pairs walk the 896 tiles of the 8192 x 7168 projection in 13 waves where 66 need 14.
-    if (w->copy_ctas <= 0) w->copy_ctas = w->tp >= 8 ? 8 : 4;
+    // Copy mode 0 (whole copy CTAs): one SM pulls only 16-20 GB/s over NVLink (measured on 8 GPUs: 4 copy CTAs 1.52 ms,
+    // 8: 0.92 ms, 16: 0.76 ms for the 8192 x 7168 x 8192 projection whose MMAs take 0.68 ms), so 16 of them are needed
+    // to stay ahead of the tile walk, and each costs tensor throughput. Copy mode 1 spreads the copy over all SMs.
+    if (w->copy_ctas <= 0) w->copy_ctas = 16;
     int tiles_m = (M + kBM - 1) / kBM;
     if (st == XCCL_OK && (M % kBM != 0 || tiles_m % w->tp != 0)) st = XCCL_ERR_INVALID_PARAM;
     for (int l = 0; l < w->n_local && st == XCCL_OK; l++) {
@@ -243,11 +246,12 @@ xccl_status_t xccl_tp_ag_gemm_swiglu(xccl_tp_ws_h w, const void *const *Wg, cons
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     int ctas      = sms / w->n_local;
-    int copy_ctas = w->tp > 1 ? std::max(1, std::min(w->copy_ctas, ctas / 4)) : 0;
+    int copy_ctas = (w->tp > 1 && w->copy_mode == 0) ? std::max(1, std::min(w->copy_ctas, ctas / 4)) : 0;
     l.n_local     = w->n_local;
     l.ctas        = ctas;
     l.cooperative = w->tp > 1;
     p.n_gemm_ctas = ctas - copy_ctas;
+    p.copy_mode   = w->copy_mode;
     for (int r = 0; r < w->tp; r++) {
         p.xg[r]  = w->xg(r);
         p.pad[r] = w->pad(r);
@@ -320,6 +324,7 @@ xccl_status_t xccl_tp_gemm_rs(xccl_tp_ws_h w, const void *const *Hin, const void
     w->rs_count[p.seq & 1] += (uint32_t)tiles_n;
     p.rs_target = w->rs_count[p.seq & 1];
     p.rs_fused  = w->rs_fused ? 1 : 0;
+    p.rs_debug_local = w->rs_debug_local ? 1 : 0;
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -374,6 +379,13 @@ xccl_status_t xccl_tp_ag_gemm_swiglu_fp8(xccl_tp_ws_h w, const void *const *Wg8,
                                          const void *const *Wu8, const float *const *sWu, void *const *Hout, int F_local,
                                          void *stream)
 {
+    return xccl_tp_ag_gemm_swiglu_fp8q(w, Wg8, sWg, Wu8, sWu, Hout, nullptr, F_local, stream);
+}
+
+xccl_status_t xccl_tp_ag_gemm_swiglu_fp8q(xccl_tp_ws_h w, const void *const *Wg8, const float *const *sWg,
+                                          const void *const *Wu8, const float *const *sWu, void *const *Hout,
+                                          float *const *out_scales, int F_local, void *stream)
+{
     if (w == nullptr || Wg8 == nullptr || sWg == nullptr || Wu8 == nullptr || sWu == nullptr || Hout == nullptr ||
         F_local % 128 != 0 || w->K % 128 != 0) {
         return XCCL_ERR_INVALID_PARAM;
@@ -389,17 +401,18 @@ xccl_status_t xccl_tp_ag_gemm_swiglu_fp8(xccl_tp_ws_h w, const void *const *Wg8,
     p.rank_base = w->rank_base;
     p.seq       = ++w->seq_ag;
     p.error     = w->error;
-    p.ldc       = F_local;
+    p.ldc       = F_local;   // elements of the output row: bf16 values, or e4m3 bytes with out_scales
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     int ctas      = sms / w->n_local;
-    int copy_ctas = w->tp > 1 ? std::max(1, std::min(w->copy_ctas, ctas / 4)) : 0;
-    copy_ctas     = (copy_ctas + 1) & ~1;  // the same count as the bf16 kernel uses: the ready flags count copy CTAs
+    int copy_ctas = (w->tp > 1 && w->copy_mode == 0) ? std::max(1, std::min(w->copy_ctas, ctas / 4)) : 0;
     l.n_local     = w->n_local;
-    l.ctas        = ctas & ~1;
+    l.ctas        = ctas;
     l.cooperative = w->tp > 1;
-    p.n_gemm_ctas = l.ctas - copy_ctas;
+    p.n_gemm_ctas = ctas - copy_ctas;
+    p.copy_mode   = w->copy_mode;
+    if (out_scales != nullptr) p.out_fp8 = 1;
     for (int r = 0; r < w->tp; r++) {
         p.xg[r]  = w->xg(r);
         p.sg[r]  = w->sx(r);
@@ -412,10 +425,11 @@ xccl_status_t xccl_tp_ag_gemm_swiglu_fp8(xccl_tp_ws_h w, const void *const *Wg8,
         p.sb1[i]   = sWu[i];
         xccl_status_t st = make_tensor_map_u8(&l.tmA[i], w->xg(w->rank_base + i), (uint64_t)w->M, (uint64_t)w->K, 128);
         if (st != XCCL_OK) return st;
-        st = make_tensor_map_u8(&l.tmB0[i], Wg8[i], (uint64_t)F_local, (uint64_t)w->K, 64);
+        st = make_tensor_map_u8(&l.tmB0[i], Wg8[i], (uint64_t)F_local, (uint64_t)w->K, kBN / 2);
         if (st != XCCL_OK) return st;
-        st = make_tensor_map_u8(&l.tmB1[i], Wu8[i], (uint64_t)F_local, (uint64_t)w->K, 64);
+        st = make_tensor_map_u8(&l.tmB1[i], Wu8[i], (uint64_t)F_local, (uint64_t)w->K, kBN / 2);
         if (st != XCCL_OK) return st;
+        if (out_scales != nullptr) p.out_scale[i] = out_scales[i];
     }
     return launch_gemm_fp8(p, l, (cudaStream_t)stream);
 }
@@ -439,8 +453,10 @@ xccl_status_t xccl_tp_gemm_rs_fp8(xccl_tp_ws_h w, const void *const *H8, const f
     p.seq       = ++w->seq_rs;
     p.error     = w->error;
     p.ldc       = w->N_rs;
-    w->rs_count[p.seq & 1] += (uint32_t)(p.N / 128);  // tiles of 128 columns per row block
+    w->rs_count[p.seq & 1] += (uint32_t)((p.N + kBN - 1) / kBN);  // tiles per row block
     p.rs_target = w->rs_count[p.seq & 1];
+    p.rs_fused  = w->rs_fused ? 1 : 0;
+    p.rs_debug_local = w->rs_debug_local ? 1 : 0;
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -459,7 +475,7 @@ xccl_status_t xccl_tp_gemm_rs_fp8(xccl_tp_ws_h w, const void *const *H8, const f
         p.sg[w->rank_base + i] = const_cast<float *>(sH[i]);
         xccl_status_t st = make_tensor_map_u8(&l.tmA[i], H8[i], (uint64_t)w->M, (uint64_t)F_local, 128);
         if (st != XCCL_OK) return st;
-        st = make_tensor_map_u8(&l.tmB0[i], Wd8[i], (uint64_t)w->N_rs, (uint64_t)F_local, 128);
+        st = make_tensor_map_u8(&l.tmB0[i], Wd8[i], (uint64_t)w->N_rs, (uint64_t)F_local, kBN / 2);
         if (st != XCCL_OK) return st;
         l.tmB1[i] = l.tmB0[i];
     }

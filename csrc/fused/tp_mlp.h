@@ -53,6 +53,11 @@ float        *xccl_tp_ws_sx_shard(xccl_tp_ws_h ws, int local_rank);   // [M/tp, 
 xccl_status_t xccl_tp_ag_gemm_swiglu_fp8(xccl_tp_ws_h ws, const void *const *Wg8, const float *const *sWg,
                                          const void *const *Wu8, const float *const *sWu, void *const *Hout, int F_local,
                                          void *stream);
+// The same with the output quantised in the epilogue: H8out[M, F_local] e4m3 and sHout[M, F_local/128] fp32 (1 x 128
+// blocks), ready to be the activations of xccl_tp_gemm_rs_fp8 without a pass in between.
+xccl_status_t xccl_tp_ag_gemm_swiglu_fp8q(xccl_tp_ws_h ws, const void *const *Wg8, const float *const *sWg,
+                                          const void *const *Wu8, const float *const *sWu, void *const *H8out,
+                                          float *const *sHout, int F_local, void *stream);
 // Y[M/tp, N] (bf16) = reduce-scatter of H8 Wd8^T; H8: [M, F_local] e4m3 with sH [M, F_local/128];
 // Wd8: [N, F_local] e4m3 with sWd [N/128, F_local/128]
 xccl_status_t xccl_tp_gemm_rs_fp8(xccl_tp_ws_h ws, const void *const *H8, const float *const *sH, const void *const *Wd8,

@@ -308,7 +308,7 @@ public:
         return {
             {"REPLICATE_TEAM", "hier", "Team library to replicate", OptType::STRING},
             {"REPLICAS_NUMBER", "2", "How many replicas (rails)", OptType::UINT},
-            {"THREADS_NUMBER", "0", "Progress threads; 0 = the caller progresses (the reference defaults to 2)", OptType::UINT},
+            {"THREADS_NUMBER", "2", "Progress threads that drive the replicas (reference default, src/team_lib/multirail/xccl_mrail_lib.c:40); 0 = the caller progresses", OptType::UINT},
             {"ASYNC_POLL_COUNT", "3", "Tests per request before a progress thread moves on", OptType::UINT},
             {"NET_DEVICES", "all", "Accepted for compatibility", OptType::STRING},
         };

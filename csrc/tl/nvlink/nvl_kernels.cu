@@ -47,6 +47,17 @@ __device__ __forceinline__ Range block_range(size_t npacks)
     return Range{lo, min(lo + per, npacks)};
 }
 
+// Range of block b in chunk number `chunk` of a chunked kernel that alternates between the two workspace halves.
+// Blocks of different index are not ordered with one another, and a half is reused two chunks later: from the third
+// chunk on the block ranges are cut from the chunk capacity (the same pack ranges of the half in every chunk), not
+// from what the chunk holds, so a block that runs ahead never writes where a block that lags still reads.
+__device__ __forceinline__ Range chunk_range(size_t n, size_t cap, size_t chunk)
+{
+    if (chunk < 2) return block_range(n);
+    const Range r = block_range(cap);
+    return Range{min(r.lo, n), min(r.hi, n)};
+}
+
 __device__ __forceinline__ Range sub_range(Range r, int n, int k)
 {
     size_t len = r.hi - r.lo;
@@ -253,7 +264,7 @@ __global__ void __launch_bounds__(512) allreduce_two_shot_kernel(World w, Call c
         const size_t hoff  = (size_t)parity * half;
         const size_t e_off = c0 * E;
         const size_t cnt   = c.count - e_off;  // elements from this chunk's start to the end
-        const Range  r     = block_range(n);
+        const Range  r     = chunk_range(n, cap, c0 / cap);
         char        *mine  = w.ws[s.rank] + hoff;
 
         // 1. my input piece -> my workspace
@@ -332,19 +343,20 @@ __global__ void __launch_bounds__(512) reduce_kernel(World w, Call c)
         const size_t hoff  = (size_t)parity * half;
         const size_t e_off = c0 * E;
         const size_t cnt   = c.count - e_off;
-        const Range  r     = block_range(n);
+        const Range  r     = chunk_range(n, cap, c0 / cap);
+        const size_t stride = (c0 / cap < 2) ? n : cap;  // packs between segments in the half: fixed once halves are reused
         char        *mine  = w.ws[s.rank] + hoff;
         for (int q = 0; q < nseg; q++) {
             const T   *seg = src + (size_t)q * c.count + e_off;
             const bool al  = ((uintptr_t)seg & 15) == 0;
             stream_packs<4>(
                 r.lo, r.hi, [&](size_t i) { return load_pack<T>(seg, i, cnt, al); },
-                [&](size_t i, uint4 v) { st_16(mine + ((size_t)q * n + i) * 16, v); });
+                [&](size_t i, uint4 v) { st_16(mine + ((size_t)q * stride + i) * 16, v); });
         }
         block_barrier(w, s);
         if (s.failed) break;
         if (i_reduce) {
-            const size_t seg_off = hoff + (size_t)my_seg * n * 16;
+            const size_t seg_off = hoff + (size_t)my_seg * stride * 16;
             reduce_packs<T, kSum, 2>([&](int q) { return (const char *)w.ws[q] + seg_off; }, w.size, r.lo, r.hi, c.op, [&](size_t i, A(&acc)[E]) {
 #pragma unroll
                 for (int e = 0; e < E; e++) acc[e] = dev::scaled(acc[e], c.scale, c.do_scale != 0);
@@ -394,7 +406,8 @@ template <int KIND, bool kMc> __global__ void __launch_bounds__(512) mover_kerne
         const size_t hoff  = (size_t)parity * half;
         const size_t b_off = c0 * 16;
         const size_t left  = seg_bytes - b_off;
-        const Range  r     = block_range(n);
+        const Range  r     = chunk_range(n, cap, c0 / cap);
+        const size_t stride = (c0 / cap < 2) ? n : cap;  // packs between segments in the half: fixed once halves are reused
         char        *mine  = w.ws[s.rank] + hoff;
 
         if (KIND != MV_BCAST || s.rank == c.root) {
@@ -410,7 +423,7 @@ template <int KIND, bool kMc> __global__ void __launch_bounds__(512) mover_kerne
                     },
                     [&](size_t it, uint4 v) {
                         const uint32_t q = (uint32_t)it / (uint32_t)cnt;
-                        st_16(mine + ((size_t)q * n + r.lo + (it - q * cnt)) * 16, v);
+                        st_16(mine + ((size_t)q * stride + r.lo + (it - q * cnt)) * 16, v);
                     });
             } else
             for (int q = 0; q < nseg_ws; q++) {
@@ -425,7 +438,7 @@ template <int KIND, bool kMc> __global__ void __launch_bounds__(512) mover_kerne
                         if (kMc) {
                             mm_st_16(w.mc_ws + hoff + i * 16, v);
                         } else {
-                            st_16(mine + ((size_t)q * n + i) * 16, v);
+                            st_16(mine + ((size_t)q * stride + i) * 16, v);
                         }
                         if (own != nullptr) store_bytes(own, i, left, own_al, v);
                     });
@@ -453,7 +466,7 @@ template <int KIND, bool kMc> __global__ void __launch_bounds__(512) mover_kerne
                 [&](size_t it) {
                     const uint32_t q = (uint32_t)it / (uint32_t)cnt;
                     const int      p = (s.rank + (int)q) % w.size;
-                    return ld_nc16(w.ws[p] + hoff + ((size_t)seg * n + r.lo + (it - q * cnt)) * 16);
+                    return ld_nc16(w.ws[p] + hoff + ((size_t)seg * stride + r.lo + (it - q * cnt)) * 16);
                 },
                 [&](size_t it, uint4 v) {
                     const uint32_t q = (uint32_t)it / (uint32_t)cnt;
@@ -464,7 +477,7 @@ template <int KIND, bool kMc> __global__ void __launch_bounds__(512) mover_kerne
             for (int q = 0; q < w.size; q++) {
                 const int   p    = (s.rank + q) % w.size;
                 const int   seg  = (KIND == MV_ALLTOALL) ? s.rank : 0;
-                const char *from = w.ws[p] + hoff + (size_t)seg * n * 16;
+                const char *from = w.ws[p] + hoff + (size_t)seg * stride * 16;
                 Byte       *out  = dst + (size_t)p * seg_bytes + b_off;
                 const bool  al   = ((uintptr_t)out & 15) == 0;
                 stream_packs<4>(
@@ -527,10 +540,30 @@ template <int KIND> __global__ void __launch_bounds__(512) push_mover_kernel(Wor
 // inside the window. A header per block index, written in round 0, publishes the sender's per-destination bytes;
 // after the first barrier every block reads all N headers and so knows every stream's length: the number of
 // rounds (the longest stream divided by the window) is the same on all ranks without any host exchange.
+//
+// Who moves what: block b of a sender stages slice b of the window, block b of a receiver pulls what slice b holds
+// for it, so the barrier among the b-th blocks orders every byte. Blocks of different index are NOT ordered with one
+// another and may drift apart by more than a round; a half is reused two rounds later, so from the third round on the
+// slices are the same byte ranges of the half in every round (window / blocks), whatever the window holds. Only the
+// first use of each half (rounds 0 and 1) may cut its slices to the bytes actually present, which keeps all blocks
+// busy for exchanges smaller than a window.
+//
 // Whatever the number of rounds, the launch counts as ONE workspace half for the caller's parity bookkeeping: a
 // closing barrier after a multi-round exchange makes sure no peer still reads either half when the next
 // collective begins.
 constexpr size_t kVHeaderBytes = (size_t)kMaxBlocks * kMaxRanks * 4;
+
+// Slice of window k (stream offsets) that block b handles, for a stream of `total` bytes.
+__device__ __forceinline__ Range v_slice(size_t total, size_t cap, size_t k, int b, int nblocks)
+{
+    const size_t w0 = k * cap;
+    if (total <= w0) return Range{w0, w0};
+    const size_t len   = min(cap, total - w0);
+    const size_t basis = (k < 2) ? len : cap;  // bytes the slices are cut from
+    const size_t per   = ((basis / 16 + nblocks - 1) / nblocks) * 16;
+    const size_t lo    = min(w0 + (size_t)b * per, w0 + len);
+    return Range{lo, min(lo + per, w0 + len)};
+}
 
 __global__ void __launch_bounds__(512) alltoallv_kernel(World w, Call c)
 {
@@ -544,29 +577,30 @@ __global__ void __launch_bounds__(512) alltoallv_kernel(World w, Call c)
     const size_t    cap  = (half - kVHeaderBytes) & ~(size_t)15;  // stream bytes per round
     int             parity = c.parity;
     size_t          rounds = 1;
+    size_t          my_total = 0;
+    for (int q = 0; q < w.size; q++) my_total += (((size_t)sc[q] * c.src_es + 15) / 16) * 16;
 
     for (size_t k = 0; k < rounds; k++, parity ^= 1) {
         const size_t hoff = (size_t)parity * half;
         char        *mine = w.ws[s.rank] + hoff;
-        const size_t w0 = k * cap, w1 = w0 + cap;
+        const size_t w0   = k * cap;
         if (k == 0) {
             uint32_t *hdr = reinterpret_cast<uint32_t *>(mine) + (size_t)blockIdx.x * kMaxRanks;
             if ((int)threadIdx.x < w.size) hdr[threadIdx.x] = sc[threadIdx.x] * (uint32_t)c.src_es;
         }
-        // stage the part of each outgoing segment that lies in [w0, w1)
-        size_t off = 0;
-        for (int q = 0; q < w.size; q++) {
+        // stage my slice of the window: the parts of the outgoing segments that lie inside it
+        const Range sl = v_slice(my_total, cap, k, blockIdx.x, gridDim.x);
+        size_t      off = 0;
+        for (int q = 0; q < w.size && sl.lo < sl.hi; q++) {
             const size_t bytes = (size_t)sc[q] * c.src_es;
             const size_t n     = (bytes + 15) / 16;
-            const size_t lo = max(off, w0), hi = min(off + n * 16, w1);
+            const size_t lo = max(off, sl.lo), hi = min(off + n * 16, sl.hi);
             if (lo < hi) {
                 const Byte *seg = src + (size_t)sd[q] * c.src_es;
                 const bool  al  = ((uintptr_t)seg & 15) == 0;
-                const size_t p0 = (lo - off) / 16;
-                const Range  r  = block_range((hi - lo) / 16);
-                char        *to = mine + kVHeaderBytes + (off - w0);  // may point before the data area; indexed from p0 on
+                char       *to  = mine + kVHeaderBytes + (off - w0);  // may point before the data area; indexed from lo on
                 stream_packs<4>(
-                    p0 + r.lo, p0 + r.hi, [&](size_t i) { return load_pack<Byte>(seg, i, bytes, al); },
+                    (lo - off) / 16, (hi - off) / 16, [&](size_t i) { return load_pack<Byte>(seg, i, bytes, al); },
                     [&](size_t i, uint4 v) { st_16(to + i * 16, v); });
             }
             off += n * 16;
@@ -593,21 +627,24 @@ __global__ void __launch_bounds__(512) alltoallv_kernel(World w, Call c)
             const int       p    = (s.rank + q) % w.size;
             const char     *peer = w.ws[p] + hoff;
             const uint32_t *ph   = sh_hdr + p * kMaxRanks;
-            size_t          poff = 0;
-            for (int j = 0; j < s.rank; j++) poff += (((size_t)ph[j] + 15) / 16) * 16;
+            size_t          poff = 0, ptotal = 0;
+            for (int j = 0; j < w.size; j++) {
+                const size_t padded = (((size_t)ph[j] + 15) / 16) * 16;
+                if (j < s.rank) poff += padded;
+                ptotal += padded;
+            }
+            const Range  psl   = v_slice(ptotal, cap, k, blockIdx.x, gridDim.x);  // what the sender's block staged
             const size_t sent  = ph[s.rank];
             const size_t want  = (size_t)dc[p] * c.dst_es;
             const size_t bytes = min(sent, want);
             const size_t n     = (sent + 15) / 16;  // the sender's partition
-            const size_t lo = max(poff, w0), hi = min(poff + n * 16, w1);
+            const size_t lo = max(poff, psl.lo), hi = min(poff + n * 16, psl.hi);
             if (lo >= hi) continue;
             Byte        *out  = dst + (size_t)dd[p] * c.dst_es;
             const bool   al   = ((uintptr_t)out & 15) == 0;
-            const size_t p0   = (lo - poff) / 16;
-            const Range  r    = block_range((hi - lo) / 16);
             const char  *from = peer + kVHeaderBytes + (poff - w0);
             stream_packs<4>(
-                p0 + r.lo, p0 + r.hi, [&](size_t i) { return ld_nc16(from + i * 16); },
+                (lo - poff) / 16, (hi - poff) / 16, [&](size_t i) { return ld_nc16(from + i * 16); },
                 [&](size_t i, uint4 v) { store_bytes(out, i, bytes, al, v); });
         }
     }

@@ -80,9 +80,9 @@ CASES = {
                                                       "HOST_HIERARCHY": "y"}}, K.TL_MPOD, None),
     "mpod_coalesce": (K.TL_MPOD | K.TL_UCX, {K.TL_MPOD: {"POD_SIZE": "2", "ALLREDUCE_ALGORITHM": "coalesce",
                                                          "HOST_HIERARCHY": "y"}}, K.TL_MPOD, None),
-    "mrail_ucx": (K.TL_MRAIL | K.TL_UCX, {K.TL_MRAIL: {"REPLICATE_TEAM": "ucx", "REPLICAS_NUMBER": "3"},
+    "mrail_ucx": (K.TL_MRAIL | K.TL_UCX, {K.TL_MRAIL: {"REPLICATE_TEAM": "ucx", "REPLICAS_NUMBER": "3", "THREADS_NUMBER": "0"},
                                           K.TL_HIER: {"ENABLE_NVLINK": "no"}}, K.TL_MRAIL, None),
-    "mrail_hier": (K.TL_MRAIL | K.TL_UCX, {K.TL_MRAIL: {"REPLICATE_TEAM": "hier", "REPLICAS_NUMBER": "2"},
+    "mrail_hier": (K.TL_MRAIL | K.TL_UCX, {K.TL_MRAIL: {"REPLICATE_TEAM": "hier", "REPLICAS_NUMBER": "2", "THREADS_NUMBER": "2"},
                                            K.TL_HIER: {"ENABLE_NVLINK": "no"}}, K.TL_MRAIL, None),
 }
 

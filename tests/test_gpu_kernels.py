@@ -551,7 +551,7 @@ def test_moe_dispatch_combine_matches_reference(dev, ranks):
 
 
 # ----------------------------------------------------------------------------- block-scaled fp8 GEMM
-@pytest.mark.parametrize("M,N,K_", [(128, 128, 128), (256, 384, 512), (1000, 256, 1024)])
+@pytest.mark.parametrize("M,N,K_", [(128, 128, 128), (256, 384, 512), (1000, 256, 1024), (2048, 1024, 2048)])
 def test_gemm_fp8_blockscaled_matches_dequantised_reference(dev, M, N, K_):
     from xccl_b200.ops import gemm
     a = torch.randn(M, K_, device=dev) * torch.rand(M, 1, device=dev) * 3
@@ -582,14 +582,14 @@ def test_quantize_rows_kernel_matches_torch(dev):
     _loaded_native()
 
 
-@pytest.mark.parametrize("tp", [1, 2, 4])
-def test_tp_mlp_fp8_fused_matches_dequantised_reference(dev, tp):
+@pytest.mark.parametrize("tp,fuse_quant", [(1, True), (2, True), (4, True), (2, False)])
+def test_tp_mlp_fp8_fused_matches_dequantised_reference(dev, tp, fuse_quant):
     """fp8 allgather->GEMM+SwiGLU and GEMM->reduce-scatter (ranks emulated in one launch) against fp32
     products of exactly the quantised operands the kernels consumed."""
     from xccl_b200.models.tp_mlp import TpMlpFp8
     from xccl_b200.ops import gemm
     tokens, hidden, ffn = 1024, 512, 1024
-    mlp = TpMlpFp8(tokens, hidden, ffn, tp=tp, emulate=True)
+    mlp = TpMlpFp8(tokens, hidden, ffn, tp=tp, emulate=True, fuse_quant=fuse_quant)
     try:
         g = torch.Generator(device=dev).manual_seed(6)
         x = torch.randn(tokens, hidden, device=dev, generator=g).to(torch.bfloat16)
@@ -604,7 +604,15 @@ def test_tp_mlp_fp8_fused_matches_dequantised_reference(dev, tp):
                 wu = gemm.dequantize(mlp.w_up8[r], mlp.s_up[r], 128)
                 wd = gemm.dequantize(mlp.w_down8[r], mlp.s_down[r], 128)
                 h_want = torch.nn.functional.silu(xq @ wg.t()) * (xq @ wu.t())
-                torch.testing.assert_close(mlp.h[r].float(), h_want, rtol=2e-2, atol=2e-2 * float(h_want.abs().max()))
+                if fuse_quant:
+                    # the intermediate exists only as e4m3 with 1 x 128 scales: one e4m3 step (2^-3 relative) of the
+                    # block maximum at most, and scales that are the block maxima over 448
+                    h_got = gemm.dequantize(mlp.h8[r], mlp.sh[r], 1)
+                    blk = h_want.view(tokens, -1, 128).abs().amax(-1)
+                    torch.testing.assert_close(mlp.sh[r] * 448.0, blk.clamp_min(1e-12 * 448), rtol=3e-2, atol=1e-6)
+                    assert float(((h_got - h_want).abs().view(tokens, -1, 128).amax(-1) / blk.clamp_min(1e-6)).max()) <= 0.07
+                else:
+                    torch.testing.assert_close(mlp.h[r].float(), h_want, rtol=2e-2, atol=2e-2 * float(h_want.abs().max()))
                 y_want += gemm.dequantize(mlp.h8[r], mlp.sh[r], 1) @ wd.t()
             got = torch.cat(y, 0).float()
             torch.testing.assert_close(got, y_want, rtol=2e-2, atol=2e-2 * float(y_want.abs().max()))

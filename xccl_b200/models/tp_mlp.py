@@ -131,11 +131,13 @@ class TpMlp:
 class TpMlpFp8(TpMlp):
     """The same block on the fp8 tensor cores: activations quantised per row and 128 columns, weights per
     128 x 128 block (e4m3, fp32 scales). Per step: quantise the input shard into the gathered buffer,
-    allgather->GEMM+SwiGLU (fp8 rows and scales travel together inside the kernel), quantise the
-    intermediate, GEMM->reduce-scatter. Four launches."""
+    allgather->GEMM+SwiGLU (fp8 rows and scales travel together inside the kernel; its epilogue quantises the
+    intermediate, which is written once, as fp8), GEMM->reduce-scatter. Three launches. With
+    ``fuse_quant=False`` the intermediate is written as bf16 and quantised by a separate kernel (four launches)."""
 
-    def __init__(self, *args, **kw):
+    def __init__(self, *args, fuse_quant: bool = True, **kw):
         super().__init__(*args, **kw)
+        self.fuse_quant = fuse_quant
         self.overlap_h2d = False   # the input is quantised by a kernel first: it is copied whole, then quantised
         from ..ops.gemm import quantize_weight_128x128
         from ..ops.tp import quantize_rows
@@ -161,11 +163,14 @@ class TpMlpFp8(TpMlp):
                 dst.copy_(src, non_blocking=True)
         for i in range(self.n_local):
             self._quantize_rows(self.x_in[i], self.x8[i], self.sx[i])
-        self.ws.ag_gemm_swiglu_fp8(self.w_gate8, self.s_gate, self.w_up8, self.s_up, self.h)
-        for i in range(self.n_local):
-            self._quantize_rows(self.h[i], self.h8[i], self.sh[i])
+        if self.fuse_quant:
+            self.ws.ag_gemm_swiglu_fp8q(self.w_gate8, self.s_gate, self.w_up8, self.s_up, self.h8, self.sh)
+        else:
+            self.ws.ag_gemm_swiglu_fp8(self.w_gate8, self.s_gate, self.w_up8, self.s_up, self.h)
+            for i in range(self.n_local):
+                self._quantize_rows(self.h[i], self.h8[i], self.sh[i])
         self.ws.gemm_rs_fp8(self.h8, self.sh, self.w_down8, self.s_down, self.y)
-        self.launches += 2 + 2 * self.n_local
+        self.launches += 2 + (1 if self.fuse_quant else 2) * self.n_local
         return self.y
 
 

@@ -27,6 +27,7 @@ K.optional("xccl_tp_quantize_rows", C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_v
 K.optional("xccl_tp_ws_x8_shard", C.c_void_p, C.c_void_p, C.c_int)
 K.optional("xccl_tp_ws_sx_shard", C.c_void_p, C.c_void_p, C.c_int)
 K.optional("xccl_tp_ag_gemm_swiglu_fp8", C.c_int, C.c_void_p, _pp, _pp, _pp, _pp, _pp, C.c_int, C.c_void_p)
+K.optional("xccl_tp_ag_gemm_swiglu_fp8q", C.c_int, C.c_void_p, _pp, _pp, _pp, _pp, _pp, _pp, C.c_int, C.c_void_p)
 K.optional("xccl_tp_gemm_rs_fp8", C.c_int, C.c_void_p, _pp, _pp, _pp, _pp, _pp, C.c_int, C.c_void_p)
 
 
@@ -148,6 +149,18 @@ class TpWorkspace:
                                                  torch.cuda.current_stream().cuda_stream)
         if st != K.OK:
             raise XcclError(st, "xccl_tp_ag_gemm_swiglu_fp8")
+
+    def ag_gemm_swiglu_fp8q(self, w_gate8, s_gate, w_up8, s_up, out8: Sequence[torch.Tensor],
+                            out_scales: Sequence[torch.Tensor]) -> None:
+        """As ``ag_gemm_swiglu_fp8`` with the output quantised in the epilogue: ``out8`` [M, F_local] e4m3 and
+        ``out_scales`` [M, F_local/128] fp32, the activations of ``gemm_rs_fp8``."""
+        f_local = w_gate8[0].shape[0]
+        f8, f32 = torch.float8_e4m3fn, torch.float32
+        st = K.load().xccl_tp_ag_gemm_swiglu_fp8q(self.h, _raw_ptrs(w_gate8, f8), _raw_ptrs(s_gate, f32), _raw_ptrs(w_up8, f8),
+                                                  _raw_ptrs(s_up, f32), _raw_ptrs(out8, f8), _raw_ptrs(out_scales, f32),
+                                                  f_local, torch.cuda.current_stream().cuda_stream)
+        if st != K.OK:
+            raise XcclError(st, "xccl_tp_ag_gemm_swiglu_fp8q")
 
     def gemm_rs_fp8(self, h8, s_h, w_down8, s_down, out: Sequence[torch.Tensor]) -> None:
         f_local = h8[0].shape[1]
