@@ -268,6 +268,7 @@ __device__ void copy_cta_loop(const GemmParams &p, int rank, int local, int copy
 constexpr int kCopierThreads = 64;
 constexpr int kGoSlot = 1100, kDoneSlot = 1101;  // words of the pad's counter area (the reduce-scatter counters end at 1024)
 
+template <int kU>   // 16-byte loads a thread keeps in flight (as many as the kernel's register budget allows)
 __device__ void copier_warps_loop(const GemmParams &p, int rank, int local, int tid, const AbortFlag &ab)
 {
     const int    n_cta   = gridDim.x;
@@ -319,34 +320,63 @@ __device__ void copier_warps_loop(const GemmParams &p, int rank, int local, int 
     sync_copiers();
     ok = (*ab.smem == 0);
 
+    // The remote row blocks in the order the tile walk needs them; this CTA copies packs [lo, hi) of each. All of it is
+    // one sequence of items (block, pack) walked in batches of kCopierThreads x kU, whatever block an item belongs to:
+    // NVLink round trips under load take several microseconds, so what counts is how many bytes an SM keeps in flight
+    // (kU x 16 bytes per thread), not the block boundaries. A block is announced when the batch holding its last item
+    // has been stored.
     const int n_blocks = (p.tp_size - 1) * mbs;
-    for (int b = 0; b < n_blocks && ok; b++) {
-        const int shard = (rank + 1 + b / mbs) % p.tp_size;
-        const int blk   = shard * mbs + b % mbs;
-        {
-            const char *src = reinterpret_cast<const char *>(p.xg[shard]) + (size_t)blk * blk_bytes;
-            char       *dst = reinterpret_cast<char *>(p.xg[rank]) + (size_t)blk * blk_bytes;
-            size_t      i   = lo + tid;
-            for (; i + 7 * kCopierThreads < hi; i += 8 * kCopierThreads) {
-                uint4 v[8];
+    auto blk_of = [&](int b) { return ((rank + 1 + b / mbs) % p.tp_size) * mbs + b % mbs; };
+    auto copy_all = [&](size_t first, uint32_t cnt, size_t bytes_per_blk, bool scales, bool announce_blocks) {
+        const uint32_t total = (uint32_t)n_blocks * cnt;
+        int            announced = 0;
+        for (uint32_t j0 = 0; j0 < total && ok; j0 += kCopierThreads * kU) {
+            uint4 v[kU];
 #pragma unroll
-                for (int u = 0; u < 8; u++) v[u] = nvl::ld_nc16(src + (i + (size_t)u * kCopierThreads) * 16);
-#pragma unroll
-                for (int u = 0; u < 8; u++) *reinterpret_cast<uint4 *>(dst + (i + (size_t)u * kCopierThreads) * 16) = v[u];
+            for (int u = 0; u < kU; u++) {
+                const uint32_t j = j0 + (uint32_t)u * kCopierThreads + (uint32_t)tid;
+                if (j < total) {
+                    const uint32_t b = j / cnt, i = j - b * cnt;
+                    const int      blk = blk_of((int)b);
+                    const char    *src = reinterpret_cast<const char *>(scales ? (const void *)p.sg[blk / mbs] : (const void *)p.xg[blk / mbs]);
+                    v[u] = nvl::ld_nc16(src + (size_t)blk * bytes_per_blk + (first + i) * 16);
+                }
             }
-            for (; i < hi; i += kCopierThreads) *reinterpret_cast<uint4 *>(dst + i * 16) = nvl::ld_nc16(src + i * 16);
+#pragma unroll
+            for (int u = 0; u < kU; u++) {
+                const uint32_t j = j0 + (uint32_t)u * kCopierThreads + (uint32_t)tid;
+                if (j < total) {
+                    const uint32_t b = j / cnt, i = j - b * cnt;
+                    const int      blk = blk_of((int)b);
+                    char          *dst = reinterpret_cast<char *>(scales ? (void *)p.sg[rank] : (void *)p.xg[rank]);
+                    *reinterpret_cast<uint4 *>(dst + (size_t)blk * bytes_per_blk + (first + i) * 16) = v[u];
+                }
+            }
+            sync_copiers();
+            ok = (*ab.smem == 0);
+            if (announce_blocks && tid == 0) {
+                const uint32_t stored = min(j0 + (uint32_t)(kCopierThreads * kU), total);
+                if ((uint32_t)(announced + 1) * cnt <= stored) {
+                    // the TMA unit (async proxy) of any CTA of this rank reads these rows next
+                    asm volatile("fence.proxy.async.global;" ::: "memory");
+                    __threadfence();
+                    while ((uint32_t)(announced + 1) * cnt <= stored) {
+                        red_release_gpu_add(p.ready[local] + blk_of(announced), 1u);
+                        announced++;
+                    }
+                }
+            }
         }
-        if (sblk_packs != 0) {
-            const char *src = reinterpret_cast<const char *>(p.sg[shard]) + (size_t)blk * sblk_bytes;
-            char       *dst = reinterpret_cast<char *>(p.sg[rank]) + (size_t)blk * sblk_bytes;
-            for (size_t i = slo + tid; i < shi; i += kCopierThreads) *reinterpret_cast<uint4 *>(dst + i * 16) = nvl::ld_nc16(src + i * 16);
-        }
+    };
+    if (ok && shi > slo) copy_all(slo, (uint32_t)(shi - slo), sblk_bytes, true, false);   // scales first: covered by the data's fence
+    if (ok && hi > lo) {
+        copy_all(lo, (uint32_t)(hi - lo), blk_bytes, false, true);
+    } else if (ok) {
         sync_copiers();
         if (tid == 0) {
-            // the TMA unit (async proxy) of any CTA of this rank reads these rows next
             asm volatile("fence.proxy.async.global;" ::: "memory");
             __threadfence();
-            red_release_gpu_add(p.ready[local] + blk, 1u);
+            for (int bb = 0; bb < n_blocks; bb++) red_release_gpu_add(p.ready[local] + blk_of(bb), 1u);
         }
     }
     // closing: nobody overwrites a shard that a peer may still be reading

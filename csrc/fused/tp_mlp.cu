@@ -108,7 +108,7 @@ xccl_status_t xccl_tp_ws_create(const xccl_oob_collectives_t *oob, int emu_ranks
     w->K = K;
     w->N_rs = N_rs;
     w->copy_ctas = (int)tp_options().num("COPY_CTAS");
-    w->copy_mode = (int)tp_options().num("COPY_MODE") != 0 ? 1 : 0;
+    w->copy_mode = (int)tp_options().num("COPY_MODE");
     w->rs_debug_local = tp_options().flag("RS_DEBUG_LOCAL");
     w->rs_fused  = tp_options().flag("RS_FUSED");
     w->in_rows   = std::max(1, (int)tp_options().num("H2D_CHUNK_ROWS"));
@@ -153,6 +153,7 @@ xccl_status_t xccl_tp_ws_create(const xccl_oob_collectives_t *oob, int emu_ranks
     // 8: 0.92 ms, 16: 0.76 ms for the 8192 x 7168 x 8192 projection whose MMAs take 0.68 ms), so 16 of them are needed
     // to stay ahead of the tile walk, and each costs tensor throughput. Copy mode 1 spreads the copy over all SMs.
     if (w->copy_ctas <= 0) w->copy_ctas = 16;
+    if (w->copy_mode < 0) w->copy_mode = w->tp >= 8 ? 0 : 1;
     int tiles_m = (M + kBM - 1) / kBM;
     if (st == XCCL_OK && (M % kBM != 0 || tiles_m % w->tp != 0)) st = XCCL_ERR_INVALID_PARAM;
     for (int l = 0; l < w->n_local && st == XCCL_OK; l++) {

@@ -32,6 +32,48 @@ namespace {
 using dev::Pack;
 using dev::Traits;
 
+#ifdef XCCL_DEBUG_BOUNDS
+// Bounds-checking build (python -m xccl_b200.build --debug-bounds -> libxccl_bounds.so). Every 16-byte access of the
+// kernels in this file to a workspace, to the multicast mapping or to a peer's registered buffer is checked against
+// the address ranges the launch is entitled to (the host writes them into g_dbg before the launch). An access outside
+// them is NOT made: it is recorded (how many, the first address, its kind, the block) and skipped, so a wrong index
+// shows up as a report and wrong data, never as a fault. xccl_nvlink_debug_bounds_report reads the record.
+struct DbgRanges {
+    const char *lo[3 * kMaxRanks + 2];
+    const char *hi[3 * kMaxRanks + 2];
+    int         n;
+};
+__device__ DbgRanges          g_dbg;
+__device__ unsigned long long g_dbg_violation[4];  // count, first address, kind (1 store, 2 load, 3 mc store, 4 mc load), block
+
+__device__ __forceinline__ bool dbg_ok(const void *p, int kind)
+{
+    const char *a = (const char *)p;
+    for (int i = 0; i < g_dbg.n; i++) {
+        if (a >= g_dbg.lo[i] && a + 16 <= g_dbg.hi[i]) return true;
+    }
+    if (atomicAdd(&g_dbg_violation[0], 1ull) == 0ull) {
+        g_dbg_violation[1] = (unsigned long long)(uintptr_t)p;
+        g_dbg_violation[2] = (unsigned long long)kind;
+        g_dbg_violation[3] = ((unsigned long long)blockIdx.y << 32) | blockIdx.x;
+    }
+    return false;
+}
+// the unqualified names used by the kernels below resolve to these checked forms
+#define st_16(p, v)                                  \
+    do {                                             \
+        if (dbg_ok((p), 1)) ::xccl::nvl::st_16((p), (v)); \
+    } while (0)
+#define ld_nc16(p) (dbg_ok((p), 2) ? ::xccl::nvl::ld_nc16(p) : make_uint4(0, 0, 0, 0))
+#define mm_st_16(p, v)                                  \
+    do {                                                \
+        if (dbg_ok((p), 3)) ::xccl::nvl::mm_st_16((p), (v)); \
+    } while (0)
+#define XCCL_DBG_MC_LOAD_OK(p) dbg_ok((p), 4)
+#else
+#define XCCL_DBG_MC_LOAD_OK(p) true
+#endif
+
 template <typename T> struct Epp {
     static constexpr int value = 16 / (int)sizeof(T);
 };
@@ -279,7 +321,7 @@ __global__ void __launch_bounds__(512) allreduce_two_shot_kernel(World w, Call c
         if (kNvls) {
             char *mc = w.mc_ws + hoff;
             stream_packs<4>(
-                m.lo, m.hi, [&](size_t i) { return nvls_reduce<T>(mc + i * 16); },
+                m.lo, m.hi, [&](size_t i) { return XCCL_DBG_MC_LOAD_OK(mc + i * 16) ? nvls_reduce<T>(mc + i * 16) : make_uint4(0, 0, 0, 0); },
                 [&](size_t i, uint4 v) {
                     if (c.do_scale) {
                         auto x = from_raw<T>(v);
@@ -743,7 +785,7 @@ template <typename T> __global__ void __launch_bounds__(512) symmetric_allreduce
         const size_t lo  = min((size_t)s.rank * per, npacks), hi = min(lo + per, npacks);
         const Range  r   = sub_range(Range{lo, hi}, gridDim.x, blockIdx.x);
         stream_packs<8>(
-            r.lo, r.hi, [&](size_t i) { return nvls_reduce<T>(src + i * 16); },
+            r.lo, r.hi, [&](size_t i) { return XCCL_DBG_MC_LOAD_OK(src + i * 16) ? nvls_reduce<T>(src + i * 16) : make_uint4(0, 0, 0, 0); },
             [&](size_t i, uint4 v) {
                 if (c.do_scale) {
                     auto x = from_raw<T>(v);
@@ -825,6 +867,33 @@ __global__ void timeout_probe_kernel(World w, unsigned long long budget_ns)
 
 // ------------------------------------------------------------------ launch helpers
 
+#ifdef XCCL_DEBUG_BOUNDS
+// Ranges a launch may touch with its 16-byte accesses: every rank's workspace, the multicast mapping, and what the call
+// names (registered peer buffers, symmetric buffers through the multicast mapping) with generous but finite extents.
+void dbg_set_ranges(const World &w, const Call &c, cudaStream_t stream)
+{
+    DbgRanges r{};
+    auto add = [&](const void *p, size_t bytes) {
+        if (p == nullptr || bytes == 0 || r.n >= (int)(sizeof(r.lo) / sizeof(r.lo[0]))) return;
+        r.lo[r.n] = (const char *)p;
+        r.hi[r.n] = (const char *)p + bytes;
+        r.n++;
+    };
+    for (int p = 0; p < w.size; p++) add(w.ws[p], w.ws_bytes);
+    add(w.mc_ws, w.ws_bytes);
+    const size_t span = std::max<size_t>(std::max(c.len * (size_t)w.size, c.count * 16 * (size_t)w.size), 16);
+    for (int p = 0; p < w.size; p++) {
+        add(c.peer_src[p], span);
+        add(c.peer_dst[p], span);
+    }
+    add(c.mc_src[0], span);
+    add(c.mc_dst[0], span);
+    cudaMemcpyToSymbolAsync(g_dbg, &r, sizeof(r), 0, cudaMemcpyHostToDevice, stream);
+}
+template <typename... R> void dbg_prepare(cudaStream_t s, World w, Call c, R...) { dbg_set_ranges(w, c, s); }
+inline void dbg_prepare(cudaStream_t, World, unsigned long long) {}  // the timeout probe touches no data
+#endif
+
 template <typename... Args>
 xccl_status_t launch(void (*kernel)(Args...), dim3 grid, dim3 block, bool cooperative, cudaStream_t stream, Args... args)
 {
@@ -838,6 +907,9 @@ xccl_status_t launch(void (*kernel)(Args...), dim3 grid, dim3 block, bool cooper
     attr[0].val.cooperative = cooperative ? 1 : 0;
     cfg.attrs               = attr;
     cfg.numAttrs            = 1;
+#ifdef XCCL_DEBUG_BOUNDS
+    dbg_prepare(stream, args...);
+#endif
     XCCL_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, args...));
     return XCCL_OK;
 }
@@ -1109,3 +1181,21 @@ xccl_status_t launch_timeout_probe(const World &w, unsigned long long budget_ns,
 
 }  // namespace nvl
 }  // namespace xccl
+
+// Record of the bounds-checking build: out[0] = accesses that were refused since the last call, out[1] = the first
+// refused address, out[2] = its kind (1 store, 2 load, 3 multicast store, 4 multicast load), out[3] = (rank << 32) |
+// block. Clears the record. Returns XCCL_ERR_NOT_IMPLEMENTED in a library built without XCCL_DEBUG_BOUNDS.
+extern "C" xccl_status_t xccl_nvlink_debug_bounds_report(unsigned long long *out)
+{
+#ifdef XCCL_DEBUG_BOUNDS
+    if (out == nullptr) return XCCL_ERR_INVALID_PARAM;
+    XCCL_CUDA_CHECK(cudaDeviceSynchronize());
+    XCCL_CUDA_CHECK(cudaMemcpyFromSymbol(out, xccl::nvl::g_dbg_violation, 4 * sizeof(unsigned long long)));
+    unsigned long long zero[4] = {0, 0, 0, 0};
+    XCCL_CUDA_CHECK(cudaMemcpyToSymbol(xccl::nvl::g_dbg_violation, zero, sizeof(zero)));
+    return XCCL_OK;
+#else
+    (void)out;
+    return XCCL_ERR_NOT_IMPLEMENTED;
+#endif
+}

@@ -36,7 +36,7 @@ struct NvlCfg {
     bool   direct        = true;
     bool   symmetric     = true;        // zero-copy NVLS on buffers from xccl_team_mem_alloc
     size_t symmetric_min = 32u << 10;
-    size_t push_max      = 256u << 10;  // allgather / alltoall up to this many bytes per rank use the push form
+    size_t push_max      = 1u << 20;  // allgather / alltoall up to this many bytes per rank use the push form
     std::string tuning_file;
     int    max_blocks    = 64;
     int    threads       = 512;
@@ -703,7 +703,7 @@ public:
             {"BCAST_MC_MIN", "0", "Broadcasts from this size go through the NVSwitch multicast mapping when available", OptType::MEMUNITS},
             {"DIRECT", "y", "Register the buffers of large messages with the peers (CUDA IPC) and run zero-copy kernels on them", OptType::BOOL},
             {"DIRECT_MIN", "0", "Messages from this size register their buffers and use the direct (zero-copy) kernels (0: from the tuning file, else only on request; measured crossover 32m-256m)", OptType::MEMUNITS},
-            {"PUSH_MAX", "256k", "Allgather / alltoall messages up to this size (bytes per rank) store into the destinations' workspaces instead of being pulled", OptType::MEMUNITS},
+            {"PUSH_MAX", "1m", "Allgather / alltoall messages up to this size (bytes per rank) store into the destinations' workspaces instead of being pulled", OptType::MEMUNITS},
             {"SYMMETRIC", "y", "Run collectives whose buffers come from xccl_team_mem_alloc zero-copy through the multicast mapping", OptType::BOOL},
             {"SYMMETRIC_MIN", "32k", "Smallest message that takes the symmetric (zero-copy NVLS) path", OptType::MEMUNITS},
             {"TUNING_FILE", "", "Measured thresholds, lines of `team_size one_shot_max nvls_min direct_min` (see bench/collectives.py --table)", OptType::STRING},

@@ -199,6 +199,19 @@ public:
         return id == XCCL_TL_NVLINK || id == XCCL_TL_NCCL || id == XCCL_TL_SHARP || id == XCCL_TL_HMC;
     }
 
+    // A tensor in symmetric memory of the team (xccl_team_mem_alloc; collective: every rank calls it with the same
+    // size). Collectives on such tensors, at the same offset on every rank, run zero-copy through the NVSwitch
+    // multicast mapping. The memory is returned when the last reference to the tensor goes - call
+    // free_symmetric (collective) explicitly where the ranks must agree on the moment.
+    at::Tensor empty_symmetric(int64_t nbytes, c10::DeviceIndex dev)
+    {
+        c10::cuda::CUDAGuard guard(dev);
+        void *p = nullptr;
+        check(xccl_team_mem_alloc(team_, static_cast<size_t>(nbytes), &p), "xccl_team_mem_alloc");
+        return at::from_blob(p, {nbytes}, [](void *) {}, at::TensorOptions().dtype(at::kByte).device(at::kCUDA, dev));
+    }
+    void free_symmetric(const at::Tensor &t) { check(xccl_team_mem_free(team_, t.data_ptr()), "xccl_team_mem_free"); }
+
     // Which team library serves a collective for a memory type (for tests and logs).
     std::string coll_tl(int coll, bool cuda) const
     {
@@ -686,6 +699,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
               TORCH_CHECK(pg != nullptr, "not a b200xccl backend");
               return pg->allreduce_fused(std::move(in), std::move(out), scale);
           });
+    m.def("empty_symmetric", [](const c10::intrusive_ptr<c10d::Backend> &b, int64_t nbytes, int dev) {
+        auto *pg = dynamic_cast<ProcessGroupXccl *>(b.get());
+        TORCH_CHECK(pg != nullptr, "not a b200xccl backend");
+        return pg->empty_symmetric(nbytes, static_cast<c10::DeviceIndex>(dev));
+    });
+    m.def("free_symmetric", [](const c10::intrusive_ptr<c10d::Backend> &b, const at::Tensor &t) {
+        auto *pg = dynamic_cast<ProcessGroupXccl *>(b.get());
+        TORCH_CHECK(pg != nullptr, "not a b200xccl backend");
+        pg->free_symmetric(t);
+    });
     m.def("coll_tl", [](const c10::intrusive_ptr<c10d::Backend> &b, int coll, bool cuda) {
         auto *pg = dynamic_cast<ProcessGroupXccl *>(b.get());
         TORCH_CHECK(pg != nullptr, "not a b200xccl backend");

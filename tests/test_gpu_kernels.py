@@ -368,6 +368,77 @@ def test_emu_alltoallv_larger_than_the_workspace(dev):
         w.close()
 
 
+_BOUNDS_SCRIPT = r"""
+import ctypes as C, torch
+from xccl_b200 import _capi as K
+from xccl_b200.ops.emu import EmuWorld
+dev = torch.device("cuda:0")
+L = K.load()
+rep = (C.c_ulonglong * 4)()
+L.xccl_nvlink_debug_bounds_report.restype = C.c_int
+assert L.xccl_nvlink_debug_bounds_report(rep) == K.OK, "not a bounds-checking build"
+n = 4
+w = EmuWorld(n, 1 << 20)            # small halves: the chunk loops, window rounds and parity changes all run
+g = torch.Generator(device=dev).manual_seed(0)
+for count in (1, 1000, 70001, 300000):
+    srcs = [torch.randn(count, device=dev, generator=g) for _ in range(n)]
+    dsts = [torch.empty_like(s) for s in srcs]
+    for alg in (K.NVLINK_ALG_ONE_SHOT, K.NVLINK_ALG_TWO_SHOT, K.NVLINK_ALG_DIRECT):
+        if alg == K.NVLINK_ALG_ONE_SHOT and count * 4 * n > (1 << 19):
+            continue
+        if alg == K.NVLINK_ALG_DIRECT and count % 4:
+            continue
+        w.allreduce(srcs, dsts, alg=alg)
+        torch.testing.assert_close(dsts[2], torch.stack(srcs).sum(0), rtol=1e-5, atol=1e-5)
+    w.reduce(srcs, dsts, root=1)
+    rs = [torch.randn(count * n, device=dev, generator=g) for _ in range(n)]
+    rd = [torch.empty(count, device=dev) for _ in range(n)]
+    w.reduce_scatter(rs, rd)
+for per in (13, 4099, 200003):
+    bs = [torch.randint(0, 255, (per * n,), dtype=torch.uint8, device=dev) for _ in range(n)]
+    bd = [torch.empty_like(b) for b in bs]
+    w.alltoall(bs, bd)
+    w.alltoall(bs, bd, alg=K.NVLINK_ALG_ONE_SHOT)
+    w.bcast(bs, bd, 2)
+    ps = [torch.randint(0, 255, (per,), dtype=torch.uint8, device=dev) for _ in range(n)]
+    w.allgather(ps, bd)
+    w.allgather(ps, bd, alg=K.NVLINK_ALG_ONE_SHOT)
+sc = [[(7919 * (s + 1) + 15013 * d + 3) for d in range(n)] for s in range(n)]
+srcs, dsts, metas = [], [], []
+for r in range(n):
+    rc = [sc[s][r] for s in range(n)]
+    srcs.append(torch.randn(sum(sc[r]), device=dev, generator=g))
+    dsts.append(torch.empty(sum(rc), device=dev))
+    metas.append(torch.tensor(sc[r] + [sum(sc[r][:d]) for d in range(n)] + rc + [sum(rc[:s]) for s in range(n)],
+                              dtype=torch.int32, device=dev))
+w.alltoallv(srcs, dsts, metas, max(s.numel() for s in srcs) * 4)
+assert torch.equal(dsts[1][:sc[0][1]], srcs[0][sc[0][0]:sc[0][0] + sc[0][1]])
+w.barrier()
+assert L.xccl_nvlink_debug_bounds_report(rep) == K.OK
+w.close()
+print("violations", rep[0], hex(rep[1]), rep[2], rep[3])
+assert rep[0] == 0
+"""
+
+
+def test_emu_collectives_under_the_bounds_checking_build(dev):
+    """Every NVLink collective with all ranks emulated, on the library built with -DXCCL_DEBUG_BOUNDS: each 16-byte
+    access to a workspace or a peer buffer is checked against the ranges of its launch, an access outside them is
+    recorded and skipped. Results stay right and the record stays empty."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    lib = root / "xccl_b200" / "lib" / "libxccl_bounds.so"
+    if not lib.exists():
+        pytest.skip("libxccl_bounds.so is not built (python -m xccl_b200.build --debug-bounds)")
+    env = dict(os.environ, XCCL_B200_LIB=str(lib), PYTHONPATH=str(root))
+    r = subprocess.run([sys.executable, "-c", _BOUNDS_SCRIPT], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    assert "violations 0" in r.stdout
+
+
 def test_emu_sync_collectives_and_bounded_wait(world4, dev):
     for _ in range(3):
         world4.barrier()

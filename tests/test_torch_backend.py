@@ -145,6 +145,19 @@ def _pg_cuda_rank(rank, size, job, port, tls):
         tb.allreduce_fused(src, dst, 1.0 / size).wait()
         allv = [torch.randn(1 << 20, device=dev, generator=torch.Generator(device=dev).manual_seed(r)) for r in range(size)]
         torch.testing.assert_close(dst.float(), torch.stack(allv).sum(0) / size, rtol=1e-2, atol=2e-2)
+        if tls.startswith("nvlink"):
+            # tensors in symmetric memory: the same calls, served zero-copy when the fabric has multicast
+            try:
+                sym = tb.empty_symmetric((1 << 20,), torch.float32)
+            except RuntimeError:
+                sym = None
+            if sym is not None:
+                sym.copy_(torch.full((1 << 20,), float(rank + 1), device=dev))
+                dist.all_reduce(sym)
+                assert torch.all(sym == sum(range(1, size + 1)))
+                torch.cuda.synchronize()
+                dist.barrier()
+                tb.free_symmetric(sym)
         # DDP with the fused hook: gradients equal the average over ranks
         from torch.nn.parallel import DistributedDataParallel as DDP
         torch.manual_seed(0)

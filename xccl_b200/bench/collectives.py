@@ -4,7 +4,7 @@ NCCL team, one process per GPU.
     python -m xccl_b200.bench.collectives --gpus 8 [--colls allreduce,alltoall] [--max-bytes 1g]
 
 Every number is device time (CUDA events around `iters` back-to-back posts of one persistent request
-on one stream, no host wait between posts), the maximum over ranks, after warm-up. Bus bandwidth uses the usual factors: allreduce
+on one stream, no host wait between posts; the best of three such batches), the maximum over ranks, after warm-up. Bus bandwidth uses the usual factors: allreduce
 2(N-1)/N * S / t, allgather / reduce-scatter / alltoall (N-1)/N * S / t, bcast S / t.
 Allreduce runs with the fused 1/N post-scale, as gradient averaging would.
 Output: one JSON object per line on stdout (rank 0) and, with --table, a selection table
@@ -131,17 +131,21 @@ def _rank_main(rank: int, size: int, job: str, opts: dict) -> list:
                 warm.wait()
             torch.cuda.synchronize()
             oob.allgather_bytes(b"x")
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            with torch.cuda.stream(stream):
-                e0.record(stream)
-                for _ in range(iters):
-                    # posts of one request are ordered by its stream: no host wait between them, so the
-                    # number is device time per operation, not launch-and-synchronise time
-                    req.post()
-                req.wait()
-                e1.record(stream)
-            stream.synchronize()
-            ms = e0.elapsed_time(e1) / iters
+            # best of `reps` batches: one stray interruption of a rank (another tenant of the host, a lazily loaded
+            # kernel image) would otherwise sit in the average of a 50-post batch
+            ms = float("inf")
+            for _ in range(opts.get("reps", 3)):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                with torch.cuda.stream(stream):
+                    e0.record(stream)
+                    for _ in range(iters):
+                        # posts of one request are ordered by its stream: no host wait between them, so the
+                        # number is device time per operation, not launch-and-synchronise time
+                        req.post()
+                    req.wait()
+                    e1.record(stream)
+                stream.synchronize()
+                ms = min(ms, e0.elapsed_time(e1) / iters)
         except Exception as e:  # an algorithm that does not apply at this size
             req.finalize() if hasattr(req, "finalize") else None
             return {"coll": coll, "impl": impl, "alg": alg_name, "bytes": total, "error": str(e)[:80]}
@@ -232,9 +236,10 @@ def main() -> None:
     ap.add_argument("--max-blocks", type=int, default=128)
     ap.add_argument("--table", default=None, help="write the derived selection table to this file")
     ap.add_argument("--no-symmetric", action="store_true", help="skip the rows on symmetric memory")
+    ap.add_argument("--reps", type=int, default=3, help="batches per case; the best one is reported")
     a = ap.parse_args()
     opts = {"colls": a.colls.split(","), "dtypes": a.dtypes.split(","), "workspace": a.workspace,
-            "symmetric": not a.no_symmetric,
+            "symmetric": not a.no_symmetric, "reps": a.reps,
             "max_blocks": a.max_blocks, "sizes": _sizes(_parse_size(a.min_bytes), _parse_size(a.max_bytes), a.step)}
     res = run_ranks(_rank_main, a.gpus, opts, timeout=1500, start_method="spawn")
     for r in res[0]:

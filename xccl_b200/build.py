@@ -62,15 +62,21 @@ def _obj_for(src: Path, sanitize: str | None = None) -> Path:
 
 
 def _compile(src: Path, obj: Path, verbose: bool, ptxas_v: bool, sanitize: str | None = None) -> tuple[Path, int, str]:
-    san = [f"-fsanitize={sanitize}", "-fno-omit-frame-pointer"] if sanitize else []
+    if sanitize == "bounds":
+        # device-side bounds checks of the NVLink kernels (csrc/tl/nvlink/nvl_kernels.cu); host code as usual
+        san = []
+        extra = ["-DXCCL_DEBUG_BOUNDS"]
+    else:
+        san = [f"-fsanitize={sanitize}", "-fno-omit-frame-pointer"] if sanitize else []
+        extra = []
     if src.suffix == ".cu":
-        cmd = [NVCC, *NVCC_FLAGS, *COMMON_INC, "-c", str(src), "-o", str(obj)]
+        cmd = [NVCC, *NVCC_FLAGS, *extra, *COMMON_INC, "-c", str(src), "-o", str(obj)]
         for f in san:
             cmd[1:1] = ["-Xcompiler", f]
         if ptxas_v:
             cmd[1:1] = ["-Xptxas", "-v"]
     else:
-        cmd = [CXX, *CXX_FLAGS, *san, *COMMON_INC, *_cuda_include(), "-c", str(src), "-o", str(obj)]
+        cmd = [CXX, *CXX_FLAGS, *san, *extra, *COMMON_INC, *_cuda_include(), "-c", str(src), "-o", str(obj)]
     if verbose:
         print(" ".join(cmd), flush=True)
     r = subprocess.run(cmd, capture_output=True, text=True)
@@ -111,7 +117,7 @@ def build_native(force: bool = False, verbose: bool = False, ptxas_v: bool = Fal
     if todo or not lib.exists():
         cmd = [NVCC, "-shared", *ARCH_FLAGS, "-o", str(lib), *map(str, objs), "-lpthread", "-ldl", "-lrt",
                "-cudart", "static"]
-        if sanitize:
+        if sanitize and sanitize != "bounds":
             cmd += ["-Xcompiler", f"-fsanitize={sanitize}"]
         if verbose:
             print(" ".join(cmd), flush=True)
@@ -163,8 +169,11 @@ def main() -> None:
     ap.add_argument("-j", type=int, default=None)
     ap.add_argument("--sanitize", choices=["address", "thread"], default=None,
                     help="build libxccl_<sanitizer>.so with the host code instrumented (CPU tests only)")
+    ap.add_argument("--debug-bounds", action="store_true",
+                    help="build libxccl_bounds.so: the NVLink kernels check every workspace / peer access against the "
+                         "ranges of the launch and record (never make) an access outside them")
     a = ap.parse_args()
-    lib = build_native(a.force, a.verbose, a.ptxas_v, a.j, a.sanitize)
+    lib = build_native(a.force, a.verbose, a.ptxas_v, a.j, "bounds" if a.debug_bounds else a.sanitize)
     print(f"built {lib}")
     if a.torch:
         t = build_torch_ext(a.force, a.verbose)

@@ -57,6 +57,24 @@ def allreduce_fused(inp: torch.Tensor, out: torch.Tensor, scale: float, group=No
     return extension().allreduce_fused(_backend_of(group, inp.device), inp, out, float(scale))
 
 
+def empty_symmetric(shape, dtype: torch.dtype = torch.float32, group=None) -> torch.Tensor:
+    """A CUDA tensor in the team's symmetric memory (collective: every rank calls it with the same shape).
+    ``dist.all_reduce`` / ``broadcast`` on such tensors - the same tensor or the same offset of it on every rank - run
+    zero-copy: the NVSwitch adds the ranks' buffers in place and replicates the result. Free with ``free_symmetric``."""
+    dev = torch.cuda.current_device()
+    n = 1
+    for s_ in (shape if isinstance(shape, (tuple, list)) else (shape,)):
+        n *= int(s_)
+    nbytes = n * torch.tensor([], dtype=dtype).element_size()
+    raw = extension().empty_symmetric(_backend_of(group, torch.device("cuda", dev)), (nbytes + 255) // 256 * 256, dev)
+    return raw[:nbytes].view(dtype).view(shape)
+
+
+def free_symmetric(t: torch.Tensor, group=None) -> None:
+    """Returns memory of ``empty_symmetric`` (collective)."""
+    extension().free_symmetric(_backend_of(group, t.device), t)
+
+
 def coll_tl(coll: int, cuda: bool, group=None) -> str:
     dev = torch.device("cuda", torch.cuda.current_device()) if cuda else torch.device("cpu")
     return extension().coll_tl(_backend_of(group, dev), coll, cuda)
