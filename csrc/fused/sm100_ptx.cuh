@@ -276,7 +276,10 @@ __device__ __forceinline__ void cluster_sync_all()
 // arrival on an mbarrier that may live in the other CTA of the pair (shared::cluster address)
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar)
 {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+    // default semantics (release at CTA scope): a release at cluster scope makes the warp wait for every memory
+    // operation it has in flight, which the per-K-block arrivals of the fp8 promotion warps cannot afford; what the
+    // arrival has to order - the tensor-memory reads before it - is ordered by tcgen05.fence::before_thread_sync
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 // Tiled 2-D load into THIS CTA's shared memory whose completion bytes are counted on an mbarrier of
 // either CTA of the pair (shared::cluster address). One destination CTA; x as for tma_load_2d.

@@ -332,16 +332,26 @@ tp_gemm_kernel(GemmParams p, const __grid_constant__ GemmLaunch lp)
             const int    wblk = (tl.nb * 2 + half) * 128 < p.N ? tl.nb * 2 + half : 0;  // a last tile may be half outside N
             const float *sb_0 = swi ? p.sb0[local] + (size_t)tl.nb * kblocks : p.sb0[local] + (size_t)wblk * kblocks;
             const float *sb_1 = swi ? p.sb1[local] + (size_t)tl.nb * kblocks : sb_0;
+            // Scales are fetched one K block ahead: a load from L2 takes longer than the MMAs of a K block, and on the
+            // critical path of every block it would bound the kernel. The weight scales can be read at any time. The
+            // scales of gathered rows arrive with the rows, so the first one of a tile is read only when the product of
+            // its first K block exists (the whole row block was released by the copiers before that), from L2, not from
+            // a stale L1 line; from then on the next block's scale is requested while this block is added up.
+            float w0_next = __ldg(sb_0), w1_next = __ldg(sb_1), a_next = 0.0f;
             for (int kb = 0; kb < kblocks; kb++) {
                 if (!mbar_wait(tmem_full_bar(a), acc_phase, ab, 5)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after();
-                // the scales of gathered rows arrive with the rows: read them only now that the product of this K
-                // block exists (its operands were released by the copy CTAs), and from L2, not a stale L1 line
-                const float a_s = row_ok ? __ldcg(sa_row + kb) : 0.0f;
-                const float s0 = a_s * __ldg(sb_0 + kb), s1 = a_s * __ldg(sb_1 + kb);
+                if (kb == 0) a_next = row_ok ? __ldcg(sa_row) : 0.0f;
+                const float a_s = a_next, w0 = w0_next, w1 = w1_next;
+                if (kb + 1 < kblocks) {
+                    a_next  = row_ok ? __ldcg(sa_row + kb + 1) : 0.0f;
+                    w0_next = __ldg(sb_0 + kb + 1);
+                    w1_next = __ldg(sb_1 + kb + 1);
+                }
+                const float s0 = a_s * w0, s1 = a_s * w1;
                 const uint32_t t_acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)a * kBN;
                 // four batches of 32 columns: tcgen05.wait::ld waits for every load in flight, so a batch is "issue two
                 // 16-column loads, wait once, add up"; as few waits per K block as the register budget allows (the 128
