@@ -709,7 +709,7 @@ const OptTable &tp_options()
             {"GEMM_SYNC", "y", "Keep the tile walkers in soft lockstep (one counter per wave of tiles)", OptType::BOOL},
             {"GEMM_SYNC_KBLOCKS", "0", "Also synchronise every this many K blocks inside a tile (0: tile starts only)", OptType::UINT},
             {"GEMM_SYNC_NS", "30000", "Longest wait at a lockstep point in nanoseconds; running out is not an error", OptType::UINT},
-            {"COPY_MODE", "-1", "allgather->GEMM: 1 = two copier warps in every CTA pull the remote shards, 0 = whole CTAs are set aside for it (COPY_CTAS), -1 = by team size", OptType::INT},
+            {"COPY_MODE", "-1", "allgather->GEMM: 1 = two copier warps in every CTA pull the remote shards, 0 = whole CTAs are set aside for it (COPY_CTAS), -1 = by team size (1 up to two ranks)", OptType::INT},
             {"COPY_CTAS", "0", "Copy mode 0: CTAs that pull the remote shards (0: 16)", OptType::UINT},
             {"RS_DEBUG_LOCAL", "n", "Diagnostic, wrong results: GEMM->reduce-scatter stores every partial tile into local memory and waits for nobody, to time the kernel without its NVLink traffic", OptType::BOOL},
             {"RS_FUSED", "y", "GEMM->reduce-scatter: add the peers' partial tiles in the epilogue of the local tiles instead of a reduce phase after the last tile", OptType::BOOL},

@@ -149,11 +149,14 @@ xccl_status_t xccl_tp_ws_create(const xccl_oob_collectives_t *oob, int emu_ranks
             }
         }
     }
-    // Copy mode 0 (whole copy CTAs): one SM pulls only 16-20 GB/s over NVLink (measured on 8 GPUs: 4 copy CTAs 1.52 ms,
-    // 8: 0.92 ms, 16: 0.76 ms for the 8192 x 7168 x 8192 projection whose MMAs take 0.68 ms), so 16 of them are needed
-    // to stay ahead of the tile walk, and each costs tensor throughput. Copy mode 1 spreads the copy over all SMs.
+    // Copy mode 0 (whole copy CTAs, bulk copies through shared memory): one SM pulls only 16-20 GB/s over NVLink
+    // (measured on 8 GPUs: 4 copy CTAs 1.52 ms, 8: 0.92 ms, 16: 0.76 ms for the 8192 x 7168 x 8192 projection whose MMAs
+    // take 0.68 ms), so 16 of them are needed to stay ahead of the tile walk, and each costs tensor throughput.
+    // Copy mode 1 (two copier warps in every CTA, plain loads) costs no tensor throughput but moves only about
+    // 120 GB/s per GPU however many loads it keeps in flight (8 GPUs: 1.12 ms), enough for two ranks (67 MB in 2.5 ms:
+    // 4.16 ms per block step against 4.41 ms with copy CTAs), not for eight.
     if (w->copy_ctas <= 0) w->copy_ctas = 16;
-    if (w->copy_mode < 0) w->copy_mode = w->tp >= 8 ? 0 : 1;
+    if (w->copy_mode < 0) w->copy_mode = w->tp <= 2 ? 1 : 0;
     int tiles_m = (M + kBM - 1) / kBM;
     if (st == XCCL_OK && (M % kBM != 0 || tiles_m % w->tp != 0)) st = XCCL_ERR_INVALID_PARAM;
     for (int l = 0; l < w->n_local && st == XCCL_OK; l++) {
