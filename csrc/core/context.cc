@@ -49,7 +49,7 @@ xccl_status_t xccl_context_create(xccl_lib_h lib, const xccl_context_params_t *p
         ctx->params.thread_mode = XCCL_THREAD_MODE_SINGLE;
     }
     uint64_t want = (params->field_mask & XCCL_CONTEXT_PARAM_FIELD_TLS) ? params->tls : (uint64_t)XCCL_TL_ALL;
-    ctx->pq       = ProgressQueue::create(ctx->params.thread_mode);
+    ctx->pq       = ProgressQueue::create(ctx->params.thread_mode, (int)global_state().opts.num("LF_TASKS_QUEUE_SIZE"));
 
     for (size_t i = 0; i < lib->tls.size(); i++) {
         TeamLib *tl = lib->tls[i];

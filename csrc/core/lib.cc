@@ -21,7 +21,7 @@ static const std::vector<OptField> kGlobalFields = {
     {"LOG_LEVEL", "warn", "Verbosity: fatal, error, warn, info, debug, trace", OptType::LOG_LEVEL},
     {"TEAM_LIB_PATH", "", "Directory searched for extra team-library plugins (xccl_team_lib_*.so)", OptType::STRING},
     {"MEM_COMPONENT_CACHE_SIZE", "4096", "Bytes of scratch kept cached per memory type", OptType::MEMUNITS},
-    {"LF_TASKS_QUEUE_SIZE", "8", "Slots per pool of the multi-thread progress queue (fixed at 8)", OptType::UINT},
+    {"LF_TASKS_QUEUE_SIZE", "8", "Slots per pool of the multi-thread progress queue; tasks beyond twice this go to a locked overflow list", OptType::UINT},
     {"OOB_TIMEOUT", "120", "Seconds a blocking out-of-band exchange may take before it fails", OptType::DOUBLE},
     {"WAIT_TIMEOUT", "600", "Seconds xccl_collective_wait may spin before it returns XCCL_ERR_TIMED_OUT", OptType::DOUBLE},
     {"NVTX", "n", "Wrap xccl_collective_post and xccl_collective_wait in NVTX ranges named after the collective", OptType::BOOL},

@@ -112,19 +112,20 @@ private:
 };
 
 // ------------------------------------------------------------------ multi-thread queue
-// Two pools of kSlots atomic slots. Producers CAS a task into the pool that is currently
+// Two pools of `slots` atomic slots (XCCL_LF_TASKS_QUEUE_SIZE, 8 by default: the reference reads the
+// same option but keeps its line at 8). Producers CAS a task into the pool that is currently
 // "open"; when both the open pool is full the task goes to an overflow list under a spin
 // lock. A consumer pops ONE task per call, progresses it outside any lock and re-inserts it
 // when it has not finished, so any number of threads may call progress() concurrently.
 
 class LockFreeQueue final : public ProgressQueue {
-    static constexpr int kSlots = 8;
-
 public:
-    LockFreeQueue()
+    explicit LockFreeQueue(int slots)
     {
-        for (auto &pool : pools_)
+        for (auto &pool : pools_) {
+            pool = std::vector<std::atomic<Task *>>((size_t)std::max(1, slots));
             for (auto &s : pool) s.store(nullptr);
+        }
     }
 
     void enqueue(Task *t) override
@@ -202,18 +203,18 @@ private:
         return t;
     }
 
-    std::array<std::array<std::atomic<Task *>, kSlots>, 2> pools_;
-    std::atomic<int>                                       open_pool_{0};
-    std::atomic_flag                                       lock_ = ATOMIC_FLAG_INIT;
-    std::deque<Task *>                                     overflow_;
+    std::array<std::vector<std::atomic<Task *>>, 2> pools_;
+    std::atomic<int>                                open_pool_{0};
+    std::atomic_flag                                lock_ = ATOMIC_FLAG_INIT;
+    std::deque<Task *>                              overflow_;
 };
 
 }  // namespace
 
-std::unique_ptr<ProgressQueue> ProgressQueue::create(unsigned thread_mode)
+std::unique_ptr<ProgressQueue> ProgressQueue::create(unsigned thread_mode, int lf_slots)
 {
     if (thread_mode == XCCL_THREAD_MODE_MULTIPLE) {
-        return std::make_unique<LockFreeQueue>();
+        return std::make_unique<LockFreeQueue>(lf_slots);
     }
     return std::make_unique<ListQueue>();
 }

@@ -73,7 +73,8 @@ public:
     virtual ~ProgressQueue() = default;
     virtual void          enqueue(Task *t) = 0;
     virtual xccl_status_t progress()       = 0;
-    static std::unique_ptr<ProgressQueue> create(unsigned thread_mode);
+    // lf_slots: slots per pool of the multi-thread flavour
+    static std::unique_ptr<ProgressQueue> create(unsigned thread_mode, int lf_slots = 8);
 };
 
 }  // namespace xccl

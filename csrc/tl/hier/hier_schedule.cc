@@ -114,35 +114,23 @@ xccl_status_t build_barrier(HierTeam &t, const xccl_coll_op_args_t &a, std::vect
     return up_and_down(t, a, XCCL_MEMORY_TYPE_HOST, XCCL_FANIN, XCCL_BARRIER, XCCL_FANOUT, s);
 }
 
-xccl_status_t build_bcast(HierTeam &t, const xccl_coll_op_args_t &a, xccl_memory_type_t mem, std::vector<Step> *out,
-                          int *first_dependency)
+PairId shmseg_pair(SbgpType s)
 {
-    const Layout &L    = t.layout;
-    const int     root = a.root;
-    if (root < 0 || root >= t.size) return XCCL_ERR_INVALID_PARAM;
+    return s == SBGP_SOCKET ? PAIR_SOCKET_SHMSEG : s == SBGP_SOCKET_LEADERS ? PAIR_SOCKET_LEADERS_SHMSEG : PAIR_NODE_SHMSEG;
+}
+
+PairId host_pair(SbgpType s)
+{
+    return s == SBGP_SOCKET ? PAIR_SOCKET_HOST : s == SBGP_SOCKET_LEADERS ? PAIR_SOCKET_LEADERS_HOST : PAIR_NODE_HOST;
+}
+
+std::vector<BcastLevel> bcast_local_levels(const HierTeam &t, int root)
+{
+    const Layout &L = t.layout;
+    std::vector<BcastLevel> lv;
     const bool root_on_node   = L.node_of[(size_t)root] == L.node_id;
     const bool root_on_socket = root_on_node && t.procs[(size_t)root].socket_id == t.procs[(size_t)t.rank].socket_id;
-    xccl_coll_op_args_t base  = a;
-    base.alg.set_by_user      = 0;
-    // the data ends up in dst on every rank; the root's src is read only in the level it roots
-    int dep = -1;
-    auto add = [&](SbgpType sb, PairId pair, int level_root) -> xccl_status_t {
-        if (!member(t, sb)) return XCCL_OK;
-        if (!t.pair_ok(pair)) return XCCL_ERR_NO_RESOURCE;
-        Step s{pair, base};
-        s.args.root = level_root;
-        if (t.rank != root) s.args.buffer_info.src_buffer = a.buffer_info.dst_buffer;
-        if (level_root != L.sbgp[sb].group_rank) dep = (int)out->size();
-        out->push_back(s);
-        return XCCL_OK;
-    };
-    xccl_status_t st = XCCL_OK;
-    if (exists(t, SBGP_NODE_LEADERS)) {
-        PairId p = PAIR_NODE_LEADERS_HOST;
-        st       = add(SBGP_NODE_LEADERS, p, L.node_of[(size_t)root]);
-        if (st != XCCL_OK) return st;
-    }
-    const bool sockets = L.sockets_usable && exists(t, SBGP_SOCKET_LEADERS);
+    const bool sockets        = L.sockets_usable && exists(t, SBGP_SOCKET_LEADERS);
     if (sockets) {
         int r = 0;
         if (root_on_node) {
@@ -151,20 +139,79 @@ xccl_status_t build_bcast(HierTeam &t, const xccl_coll_op_args_t &a, xccl_memory
                 if (t.procs[(size_t)ranks[i]].socket_id == t.procs[(size_t)root].socket_id) r = (int)i;
             }
         }
-        st = add(SBGP_SOCKET_LEADERS, PAIR_SOCKET_LEADERS_HOST, r);
-        if (st != XCCL_OK) return st;
+        if (member(t, SBGP_SOCKET_LEADERS)) lv.push_back({SBGP_SOCKET_LEADERS, r});
         r = root_on_socket ? std::max(0, index_in(L.sbgp[SBGP_SOCKET].ranks, root)) : 0;
-        st = add(SBGP_SOCKET, PAIR_SOCKET_HOST, r);
-        if (st != XCCL_OK) return st;
+        if (member(t, SBGP_SOCKET)) lv.push_back({SBGP_SOCKET, r});
     } else {
         int r = root_on_node ? std::max(0, index_in(L.sbgp[SBGP_NODE].ranks, root)) : 0;
-        st    = add(SBGP_NODE, node_pair(t, mem), r);
+        if (member(t, SBGP_NODE)) lv.push_back({SBGP_NODE, r});
+    }
+    return lv;
+}
+
+// Reference shape: src/team_lib/hier/xccl_hier_schedule_bcast.c:172-311; the FANOUT_GET variant with its closing
+// FANIN: the same file, :313-485 (there the regions are mapped by the schedule's first progress step, here by the
+// request before it builds its fragments).
+xccl_status_t build_bcast(HierTeam &t, const xccl_coll_op_args_t &a, xccl_memory_type_t mem, std::vector<Step> *out,
+                          int *first_dependency, const SmGet *sm)
+{
+    const Layout &L    = t.layout;
+    const int     root = a.root;
+    if (root < 0 || root >= t.size) return XCCL_ERR_INVALID_PARAM;
+    xccl_coll_op_args_t base  = a;
+    base.alg.set_by_user      = 0;
+    // the data ends up in dst on every rank; the root's src is read only in the level it roots
+    int              dep = -1;      // the step in which this rank receives
+    std::vector<int> mains;         // the data-moving step of each level
+    std::vector<std::pair<int, int>> fanins;  // (step, its level's data-moving step)
+    auto add = [&](SbgpType sb, PairId pair, int level_root) -> xccl_status_t {
+        if (!member(t, sb)) return XCCL_OK;
+        const bool get = sm != nullptr && sm->memh[sb] != nullptr;
+        if (get) pair = shmseg_pair(sb);
+        if (!t.pair_ok(pair)) return XCCL_ERR_NO_RESOURCE;
+        Step s{pair, base};
+        s.args.root = level_root;
+        if (t.rank != root) s.args.buffer_info.src_buffer = a.buffer_info.dst_buffer;
+        if (get) {
+            s.args.coll_type             = XCCL_FANOUT_GET;
+            s.args.field_mask            = 0;
+            s.args.get_info.memh         = sm->memh[sb];
+            s.args.get_info.offset       = (ptrdiff_t)sm->offset;
+            s.args.get_info.len          = a.buffer_info.len;
+            s.args.get_info.local_buffer = a.buffer_info.dst_buffer;
+        }
+        if (level_root != L.sbgp[sb].group_rank) dep = (int)out->size();
+        mains.push_back((int)out->size());
+        out->push_back(s);
+        if (get) {
+            // the level root learns that every reader has copied: its buffer and the window may be reused
+            if (!t.pair_ok(host_pair(sb))) return XCCL_ERR_NO_RESOURCE;
+            Step f{host_pair(sb), xccl_coll_op_args_t{}};
+            f.args.coll_type = XCCL_FANIN;
+            f.args.root      = level_root;
+            fanins.push_back({(int)out->size(), mains.back()});
+            out->push_back(f);
+        }
+        return XCCL_OK;
+    };
+    xccl_status_t st = XCCL_OK;
+    if (exists(t, SBGP_NODE_LEADERS)) {
+        PairId p = PAIR_NODE_LEADERS_HOST;
+        st       = add(SBGP_NODE_LEADERS, p, L.node_of[(size_t)root]);
+        if (st != XCCL_OK) return st;
+    }
+    for (const BcastLevel &lv : bcast_local_levels(t, root)) {
+        st = add(lv.sbgp, lv.sbgp == SBGP_NODE ? node_pair(t, mem) : host_pair(lv.sbgp), lv.root);
         if (st != XCCL_OK) return st;
     }
     if (out->empty()) return XCCL_ERR_UNSUPPORTED;
     // Where the root is not the leader of its group, the leader RECEIVES in the lower level and
     // roots the upper one, so "the level where I am not the root" is the one to run first.
     *first_dependency = dep >= 0 ? dep : 0;
+    if (sm != nullptr) {
+        for (int m : mains) (*out)[(size_t)m].after = (m == *first_dependency) ? Step::kDepNone : *first_dependency;
+        for (auto &f : fanins) (*out)[(size_t)f.first].after = f.second;
+    }
     return XCCL_OK;
 }
 

@@ -185,6 +185,9 @@ xccl_status_t HierTeam::init()
         {PAIR_NODE_LEADERS_HOST, SBGP_NODE_LEADERS, XCCL_TL_UCX},
         {PAIR_NODE_LEADERS_SHARP, SBGP_NODE_LEADERS, XCCL_TL_SHARP},
         {PAIR_FLAT_HOST, SBGP_FLAT, XCCL_TL_UCX},
+        {PAIR_NODE_SHMSEG, SBGP_NODE, XCCL_TL_SHMSEG},
+        {PAIR_SOCKET_SHMSEG, SBGP_SOCKET, XCCL_TL_SHMSEG},
+        {PAIR_SOCKET_LEADERS_SHMSEG, SBGP_SOCKET_LEADERS, XCCL_TL_SHMSEG},
     };
     for (const Plan &pl : plan) {
         st = create_pair(pl.id, pl.sbgp, pl.tl);
@@ -226,7 +229,49 @@ public:
 class HierReq final : public xccl_coll_req {
 public:
     HierReq(HierTeam *t) : team_(t) {}
-    ~HierReq() override = default;
+    ~HierReq() override
+    {
+        tasks_.clear();  // the FANOUT_GET requests go before the regions they read
+        for (xccl_mem_h m : sm_.memh) {
+            if (m != nullptr) xccl_global_mem_unmap(m);
+        }
+    }
+
+    // Host broadcasts with BCAST_SM_GET: the node-local levels read the level root's buffer through a region of the
+    // shared-segment team (FANOUT_GET). The regions are mapped here, once per request, by all members of each group.
+    xccl_status_t map_regions(const xccl_coll_op_args_t &args, xccl_memory_type_t mem)
+    {
+        const HierCfg &cfg = team_->hctx->cfg;
+        const size_t   len = args.buffer_info.len;
+        if (args.coll_type != XCCL_BCAST || mem != XCCL_MEMORY_TYPE_HOST || !cfg.bcast_sm_get || len == 0 ||
+            len < cfg.bcast_sm_get_thresh || args.root < 0 || args.root >= team_->size) {
+            return XCCL_OK;
+        }
+        const double limit = global_state().opts.real("OOB_TIMEOUT");
+        for (const BcastLevel &lv : bcast_local_levels(*team_, args.root)) {
+            const Pair &p = team_->pairs[shmseg_pair(lv.sbgp)];
+            if (p.team == nullptr || !team_->pair_ok(host_pair(lv.sbgp))) continue;
+            const void *src = args.buffer_info.src_buffer;
+            const bool  own = team_->rank == args.root && src != nullptr && src != XCCL_IN_PLACE;
+            xccl_mem_map_params_t mp{};
+            mp.field_mask = XCCL_MEM_MAP_PARAM_FIELD_ADDRESS | XCCL_MEM_MAP_PARAM_FIELD_LENGTH | XCCL_MEM_MAP_PARAM_FIELD_ROOT;
+            mp.address    = own ? const_cast<void *>(src) : args.buffer_info.dst_buffer;
+            mp.length     = len;
+            mp.root       = lv.root;
+            xccl_status_t st = xccl_global_mem_map_start(p.team, mp, &sm_.memh[lv.sbgp]);
+            if (st != XCCL_OK) return st;
+            auto t0 = std::chrono::steady_clock::now();
+            while ((st = xccl_global_mem_map_test(sm_.memh[lv.sbgp])) == XCCL_INPROGRESS) {
+                xccl_context_progress(p.ctx);
+                if (limit > 0 && std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() > limit) {
+                    return XCCL_ERR_TIMED_OUT;
+                }
+            }
+            if (st != XCCL_OK) return st;
+            use_sm_ = true;
+        }
+        return XCCL_OK;
+    }
 
     // Large broadcasts are cut into fragments of BCAST_PIPELINE_THRESH bytes; each fragment is a
     // complete schedule of its own and BCAST_PIPELINE_DEPTH of them are in flight at a time
@@ -234,6 +279,8 @@ public:
     xccl_status_t build(const xccl_coll_op_args_t &args, xccl_memory_type_t mem)
     {
         const HierCfg &cfg   = team_->hctx->cfg;
+        xccl_status_t  mst   = map_regions(args, mem);
+        if (mst != XCCL_OK) return mst;
         size_t         nfrag = 1, frag_bytes = args.buffer_info.len;
         if (args.coll_type == XCCL_BCAST && cfg.bcast_pipeline_thresh > 0 &&
             args.buffer_info.len > cfg.bcast_pipeline_thresh) {
@@ -253,6 +300,7 @@ public:
                 a.buffer_info.dst_buffer = (char *)args.buffer_info.dst_buffer + off;
             }
             auto frag = std::make_unique<Schedule>();
+            sm_.offset = nfrag > 1 ? f * frag_bytes : 0;
             xccl_status_t st = build_fragment(a, mem, frag.get());
             if (st != XCCL_OK) return st;
             auto kick = [](Task *self, Task *) { static_cast<Schedule *>(self)->start(); };
@@ -278,7 +326,7 @@ public:
         switch (args.coll_type) {
         case XCCL_ALLREDUCE: st = build_allreduce(*team_, args, mem, &steps); break;
         case XCCL_BARRIER: st = build_barrier(*team_, args, &steps); break;
-        case XCCL_BCAST: st = build_bcast(*team_, args, mem, &steps, &first_dep); break;
+        case XCCL_BCAST: st = build_bcast(*team_, args, mem, &steps, &first_dep, use_sm_ ? &sm_ : nullptr); break;
         case XCCL_ALLTOALL: st = build_alltoall(*team_, args, mem, &steps, &parallel, &keep_); break;
         default: return XCCL_ERR_UNSUPPORTED;
         }
@@ -318,7 +366,13 @@ public:
         for (size_t i = 0; i < steps.size(); i++) {
             Task *cur = tasks_[base + i].get();
             frag->add(cur);
-            if (parallel) {
+            if (steps[i].after != Step::kDepDefault) {
+                if (steps[i].after == Step::kDepNone) {
+                    frag->subscribe(EVENT_SCHEDULE_STARTED, cur);
+                } else {
+                    tasks_[base + (size_t)steps[i].after]->subscribe(EVENT_COMPLETED, cur);
+                }
+            } else if (parallel) {
                 frag->subscribe(EVENT_SCHEDULE_STARTED, cur);
             } else if (first_dep >= 0) {
                 if ((int)i == first_dep) {
@@ -363,6 +417,8 @@ private:
     std::vector<std::unique_ptr<StepTask>> tasks_;
     std::vector<std::unique_ptr<Schedule>> frags_;
     std::vector<std::vector<uint32_t>>     keep_;  // count / displacement arrays of alltoallv steps
+    SmGet                                  sm_;     // regions of a FANOUT_GET broadcast, by sub-group
+    bool                                   use_sm_ = false;
 };
 
 }  // namespace
@@ -401,8 +457,8 @@ public:
             {"ENABLE_NVLINK", "yes", "Use the NVLink team for CUDA buffers inside a node", OptType::BOOL},
             {"BCAST_PIPELINE_THRESH", "inf", "Broadcasts above this size are cut into fragments", OptType::MEMUNITS},
             {"BCAST_PIPELINE_DEPTH", "1", "Fragments in flight", OptType::UINT},
-            {"BCAST_SM_GET", "0", "Accepted for compatibility (needs the shared-segment team)", OptType::BOOL},
-            {"BCAST_SM_GET_THRESH", "inf", "Accepted for compatibility", OptType::MEMUNITS},
+            {"BCAST_SM_GET", "0", "Host broadcasts inside a node read the level root's buffer through FANOUT_GET on the shared-segment team (needs ENABLE_SHMSEG)", OptType::BOOL},
+            {"BCAST_SM_GET_THRESH", "0", "Smallest broadcast that takes the FANOUT_GET path", OptType::MEMUNITS},
             {"NODE_LEADER_RANK_ID", "0", "Local index of the rank that leads its node", OptType::UINT},
         };
     }
@@ -418,6 +474,8 @@ public:
         c.bcast_pipeline_thresh = (size_t)cfg.num("BCAST_PIPELINE_THRESH");
         c.bcast_pipeline_depth  = (int)cfg.num("BCAST_PIPELINE_DEPTH");
         c.node_leader_rank_id   = (int)cfg.num("NODE_LEADER_RANK_ID");
+        c.bcast_sm_get          = cfg.flag("BCAST_SM_GET") && c.enable_shmseg;
+        c.bcast_sm_get_thresh   = (size_t)cfg.num("BCAST_SM_GET_THRESH");
         auto         *h  = new HierContext(params, c);
         h->tl            = this;
         xccl_status_t st = h->init();

@@ -50,6 +50,9 @@ enum PairId {
     PAIR_NODE_LEADERS_HOST,
     PAIR_NODE_LEADERS_SHARP, // in-fabric reduction among node leaders when enabled
     PAIR_FLAT_HOST,
+    PAIR_NODE_SHMSEG,            // shared-segment teams: FANOUT_GET broadcasts inside a node
+    PAIR_SOCKET_SHMSEG,
+    PAIR_SOCKET_LEADERS_SHMSEG,
     PAIR_LAST
 };
 
@@ -66,6 +69,8 @@ struct HierCfg {
     size_t bcast_pipeline_thresh = (size_t)-1;
     int    bcast_pipeline_depth  = 1;
     int    node_leader_rank_id   = 0;
+    bool   bcast_sm_get          = false;  // host broadcasts inside a node through FANOUT_GET on the shared-segment team
+    size_t bcast_sm_get_thresh   = 0;      // ... from this size on
 };
 
 class HierContext;
@@ -116,14 +121,36 @@ public:
 struct Step {
     PairId              pair;
     xccl_coll_op_args_t args;
+    // which step of the same fragment has to complete first: kDepDefault = the schedule's own rule (a chain, or the
+    // broadcast rule), kDepNone = starts with the schedule
+    int                 after = kDepDefault;
+    static constexpr int kDepDefault = -2, kDepNone = -1;
 };
+
+// Regions of a broadcast that runs its node-local levels through FANOUT_GET: one per sub-group this rank is in
+// (mapped by the request before the steps are built). `offset` is where the fragment starts in the message.
+struct SmGet {
+    xccl_mem_h memh[SBGP_LAST] = {};
+    size_t     offset          = 0;
+};
+// The shared-segment and host pairs that serve a node-local level.
+PairId shmseg_pair(SbgpType s);
+PairId host_pair(SbgpType s);
 
 // Builders return the ordered steps THIS rank takes part in. `parallel` marks schedules whose
 // steps have no dependency on each other (the two alltoallv halves).
 xccl_status_t build_allreduce(HierTeam &t, const xccl_coll_op_args_t &a, xccl_memory_type_t mem, std::vector<Step> *s);
 xccl_status_t build_barrier(HierTeam &t, const xccl_coll_op_args_t &a, std::vector<Step> *s);
+// sm != nullptr: levels with a region in `sm` become FANOUT_GET + FANIN (the root may reuse its buffer once every
+// reader has copied); every step then names its dependency itself.
 xccl_status_t build_bcast(HierTeam &t, const xccl_coll_op_args_t &a, xccl_memory_type_t mem, std::vector<Step> *s,
-                          int *first_dependency);
+                          int *first_dependency, const SmGet *sm = nullptr);
+// The node-local levels of a broadcast this rank takes part in, with the level root's index in the group.
+struct BcastLevel {
+    SbgpType sbgp;
+    int      root;
+};
+std::vector<BcastLevel> bcast_local_levels(const HierTeam &t, int root);
 xccl_status_t build_alltoall(HierTeam &t, const xccl_coll_op_args_t &a, xccl_memory_type_t mem, std::vector<Step> *s,
                              bool *parallel, std::vector<std::vector<uint32_t>> *keep);
 

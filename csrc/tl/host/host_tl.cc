@@ -99,12 +99,23 @@ void HostReq::progress()
     team->tr.progress();
 }
 
+// Polls the transport up to NUM_TO_PROBE times (reference: the probe count of xccl_ucx_req_test,
+// src/team_lib/ucx/xccl_ucx_sendrecv.h:200-216) before the caller's test returns "in progress".
 bool HostReq::all_done()
 {
-    progress();
-    for (const P2pReq &q : p2p_) {
-        if (!q.done) return false;
+    const int probes = std::max(1, team->cfg.num_to_probe);
+    bool      done   = false;
+    for (int k = 0; k < probes && !done; k++) {
+        progress();
+        done = true;
+        for (const P2pReq &q : p2p_) {
+            if (!q.done) {
+                done = false;
+                break;
+            }
+        }
     }
+    if (!done) return false;
     for (const P2pReq &q : p2p_) {
         if (q.status != XCCL_OK && last_ == XCCL_OK) last_ = q.status;
     }
@@ -409,7 +420,7 @@ public:
             {"ALLREDUCE_ALG", "auto", "auto, knomial or sra", OptType::STRING},
             {"ALLREDUCE_KN_RADIX", "4", "Radix of both allreduce algorithms", OptType::UINT},
             {"ALLREDUCE_SRA_THRESH", "4096", "auto: messages of at least this many bytes use sra", OptType::MEMUNITS},
-            {"NUM_TO_PROBE", "10", "Accepted for compatibility; progress drains every ring once", OptType::UINT},
+            {"NUM_TO_PROBE", "10", "Transport polls per test call before it reports that the collective is still in progress", OptType::UINT},
             {"ALLTOALL_PAIRWISE_CHUNK", "1", "Exchange steps in flight; 0 = all of them", OptType::UINT},
             {"ALLTOALL_PAIRWISE_REVERSE", "0", "Walk peers in the opposite direction", OptType::BOOL},
             {"ALLTOALL_PAIRWISE_BARRIER", "0", "Insert a barrier every N steps; 0 = never", OptType::UINT},
@@ -434,6 +445,7 @@ public:
         c.a2a_reverse     = cfg.flag("ALLTOALL_PAIRWISE_REVERSE");
         c.a2a_barrier     = (int)cfg.num("ALLTOALL_PAIRWISE_BARRIER");
         c.ring_bytes      = (size_t)cfg.num("RING_SIZE");
+        c.num_to_probe    = (int)cfg.num("NUM_TO_PROBE");
         *ctx              = new HostContext(params, c);
         return XCCL_OK;
     }

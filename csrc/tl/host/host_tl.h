@@ -20,6 +20,7 @@ struct HostCfg {
     bool        a2a_reverse = false, block_stream = false;
     size_t      ring_bytes = 1 << 20;
     size_t      sra_threshold = 4096;
+    int         num_to_probe  = 10;  // transport polls per test call before it reports "in progress"
 };
 
 class HostTeam;

@@ -60,8 +60,20 @@ Transport::~Transport()
     }
     if (mine_.base != nullptr) {
         munmap(mine_.base, mine_.bytes);
-        shm_unlink(my_name_.c_str());
+        if (!unlinked_) shm_unlink(my_name_.c_str());
     }
+}
+
+// The name of a segment is needed only until every peer has mapped it. Dropping it then means that a process which
+// exits without destroying its team (or is killed) leaves nothing behind under /dev/shm.
+void Transport::unlink_when_attached()
+{
+    if (unlinked_ || mine_.base == nullptr) return;
+    for (int p = 0; p < size_; p++) {
+        if (p != rank_ && ctl_of(mine_, p)->attached.load(std::memory_order_acquire) == 0) return;
+    }
+    shm_unlink(my_name_.c_str());
+    unlinked_ = true;
 }
 
 RingCtl *Transport::ctl_of(const Segment &s, int src) const
@@ -78,6 +90,11 @@ xccl_status_t Transport::create_local(PeerInfo *mine)
     my_name_    = name;
     mine_.bytes = (size_t)size_ * (sizeof(RingCtl) + ring_bytes_);
     int fd      = shm_open(name, O_CREAT | O_EXCL | O_RDWR, 0600);
+    if (fd < 0 && errno == EEXIST) {
+        // the name carries this process's id and a counter it has not used yet: a leftover of a dead process
+        shm_unlink(name);
+        fd = shm_open(name, O_CREAT | O_EXCL | O_RDWR, 0600);
+    }
     if (fd < 0) {
         xccl_error("shm_open(%s): %s", name, std::strerror(errno));
         return XCCL_ERR_NO_RESOURCE;
@@ -130,7 +147,9 @@ xccl_status_t Transport::connect(const PeerInfo *all)
         close(fd);
         if (s.base == MAP_FAILED) return XCCL_ERR_NO_MEMORY;
         peers_[(size_t)p] = s;
+        ctl_of(s, rank_)->attached.store(1, std::memory_order_release);
     }
+    unlink_when_attached();
     return XCCL_OK;
 }
 
@@ -314,6 +333,7 @@ void Transport::pull(int peer)
 
 void Transport::progress()
 {
+    if (!unlinked_) unlink_when_attached();
     for (int p = 0; p < size_; p++) {
         if (!outq_[(size_t)p].empty()) push(p);
         pull(p);

@@ -30,8 +30,10 @@ struct alignas(64) RingCtl {
     std::atomic<uint64_t> head;  // bytes consumed (receiver writes)
     char                  pad0[56];
     std::atomic<uint64_t> tail;  // bytes produced (sender writes)
-    char                  pad1[56];
+    std::atomic<uint32_t> attached;  // the sender has mapped this segment (sender writes, once)
+    char                  pad1[52];
 };
+static_assert(sizeof(RingCtl) == 128, "two cache lines");
 
 struct PeerInfo {  // what members exchange out of band
     char     seg_name[64];
@@ -100,6 +102,8 @@ private:
     int                          rank_, size_;
     size_t                       ring_bytes_;
     std::string                  my_name_;
+    bool                         unlinked_ = false;  // the segment's name is gone: every peer has it mapped
+    void                         unlink_when_attached();
     Segment                      mine_;
     std::vector<Segment>         peers_;     // peers_[p] = p's segment (mine for p == rank)
     std::vector<std::deque<SendOp>> outq_;   // per destination

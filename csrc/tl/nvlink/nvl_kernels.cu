@@ -363,7 +363,9 @@ __global__ void __launch_bounds__(512) allreduce_two_shot_kernel(World w, Call c
 
 // ------------------------------------------------------------------ reduce (to root), reduce-scatter
 
-template <typename T, typename O, bool kSum, bool kScatter>
+// kNvls: the reducing rank reads each pack once through the multicast mapping (multimem.ld_reduce): the switch fetches
+// and adds the N workspaces' copies, so a root takes in S bytes instead of (N - 1) x S.
+template <typename T, typename O, bool kSum, bool kScatter, bool kNvls>
 __global__ void __launch_bounds__(512) reduce_kernel(World w, Call c)
 {
     using A           = typename Traits<T>::acc;
@@ -397,7 +399,18 @@ __global__ void __launch_bounds__(512) reduce_kernel(World w, Call c)
         }
         block_barrier(w, s);
         if (s.failed) break;
-        if (i_reduce) {
+        if (i_reduce && kNvls) {
+            const char *mc = w.mc_ws + hoff + (size_t)my_seg * stride * 16;
+            stream_packs<8>(
+                r.lo, r.hi, [&](size_t i) { return XCCL_DBG_MC_LOAD_OK(mc + i * 16) ? nvls_reduce<T>(mc + i * 16) : make_uint4(0, 0, 0, 0); },
+                [&](size_t i, uint4 v) {
+                    auto x = from_raw<T>(v);
+                    A    acc[E];
+#pragma unroll
+                    for (int e = 0; e < E; e++) acc[e] = dev::scaled(Traits<T>::up(x.v[e]), c.scale, c.do_scale != 0);
+                    store_out<O, E>(dst + e_off, i, cnt, dst_al, acc);
+                });
+        } else if (i_reduce) {
             const size_t seg_off = hoff + (size_t)my_seg * stride * 16;
             reduce_packs<T, kSum, 2>([&](int q) { return (const char *)w.ws[q] + seg_off; }, w.size, r.lo, r.hi, c.op, [&](size_t i, A(&acc)[E]) {
 #pragma unroll
@@ -971,12 +984,16 @@ xccl_status_t allreduce_typed(const World &w, const Call &c, Alg alg, const Laun
 }
 
 template <typename T, typename O, bool kScatter>
-xccl_status_t reduce_typed(const World &w, const Call &c, const LaunchCfg &cfg, cudaStream_t stream)
+xccl_status_t reduce_typed(const World &w, const Call &c, const LaunchCfg &cfg, cudaStream_t stream, bool nvls)
 {
-    constexpr int E      = Epp<T>::value;
-    const size_t  npacks = (c.count + E - 1) / E;
-    const bool    sum    = (c.op == XCCL_OP_SUM);
-    auto          k      = sum ? reduce_kernel<T, O, true, kScatter> : reduce_kernel<T, O, false, kScatter>;
+    constexpr int  E      = Epp<T>::value;
+    constexpr bool can    = std::is_same<T, float>::value || std::is_same<T, __half>::value ||
+                            std::is_same<T, __nv_bfloat16>::value;
+    const size_t   npacks = (c.count + E - 1) / E;
+    const bool     sum    = (c.op == XCCL_OP_SUM);
+    if (nvls && (!can || !sum || w.mc_ws == nullptr)) return XCCL_ERR_UNSUPPORTED;
+    auto k = nvls ? reduce_kernel<T, O, true, kScatter, can>
+                  : sum ? reduce_kernel<T, O, true, kScatter, false> : reduce_kernel<T, O, false, kScatter, false>;
     int           blocks = pick_blocks(k, w, cfg, npacks * (kScatter ? w.size : 1), 2);
     return launch(k, dim3((unsigned)blocks, (unsigned)w.n_local), dim3((unsigned)cfg.threads), cfg.cooperative, stream,
                   w, c);
@@ -1097,19 +1114,19 @@ xccl_status_t launch_allreduce(const World &w, const Call &c, xccl_dt_t dt, xccl
 }
 
 xccl_status_t launch_reduce(const World &w, const Call &c, xccl_dt_t dt, xccl_dt_t out_dt, const LaunchCfg &cfg,
-                            cudaStream_t stream)
+                            cudaStream_t stream, bool nvls)
 {
     if (!reduce_op_ok(dt, (xccl_op_t)c.op)) return XCCL_ERR_UNSUPPORTED;
     if (c.count == 0) return XCCL_OK;
-    return XCCL_DISPATCH_IO(dt, out_dt, return (reduce_typed<T, O, false>(w, c, cfg, stream)););
+    return XCCL_DISPATCH_IO(dt, out_dt, return (reduce_typed<T, O, false>(w, c, cfg, stream, nvls)););
 }
 
 xccl_status_t launch_reduce_scatter(const World &w, const Call &c, xccl_dt_t dt, xccl_dt_t out_dt,
-                                    const LaunchCfg &cfg, cudaStream_t stream)
+                                    const LaunchCfg &cfg, cudaStream_t stream, bool nvls)
 {
     if (!reduce_op_ok(dt, (xccl_op_t)c.op)) return XCCL_ERR_UNSUPPORTED;
     if (c.count == 0) return XCCL_OK;
-    return XCCL_DISPATCH_IO(dt, out_dt, return (reduce_typed<T, O, true>(w, c, cfg, stream)););
+    return XCCL_DISPATCH_IO(dt, out_dt, return (reduce_typed<T, O, true>(w, c, cfg, stream, nvls)););
 }
 
 bool push_fits(const World &w, int coll, size_t len)

@@ -47,10 +47,12 @@ size_t one_shot_limit(const World &w);
 
 xccl_status_t launch_allreduce(const World &w, const Call &c, xccl_dt_t dt, xccl_dt_t out_dt, Alg alg,
                                const LaunchCfg &cfg, cudaStream_t stream);
+// nvls = true: the reducing ranks read through the multicast mapping (multimem.ld_reduce; needs w.mc_ws, a sum of
+// fp32 / fp16 / bf16)
 xccl_status_t launch_reduce(const World &w, const Call &c, xccl_dt_t dt, xccl_dt_t out_dt, const LaunchCfg &cfg,
-                            cudaStream_t stream);
+                            cudaStream_t stream, bool nvls = false);
 xccl_status_t launch_reduce_scatter(const World &w, const Call &c, xccl_dt_t dt, xccl_dt_t out_dt,
-                                    const LaunchCfg &cfg, cudaStream_t stream);
+                                    const LaunchCfg &cfg, cudaStream_t stream, bool nvls = false);
 // multicast = true: root writes once through the NVSwitch multicast mapping (needs w.mc_ws)
 xccl_status_t launch_bcast(const World &w, const Call &c, const LaunchCfg &cfg, cudaStream_t stream,
                            bool multicast = false);

@@ -24,12 +24,15 @@ namespace nvl {
 
 namespace {
 
+constexpr size_t kNever = ~(size_t)0;  // a threshold no message reaches
+
 struct NvlCfg {
     size_t ws_bytes      = 128u << 20;
     bool   nvls          = true;
     size_t one_shot_max  = 128u << 10;
     size_t nvls_min      = 256u << 10;
     size_t bcast_mc_min  = 0;
+    size_t bcast_mc_max  = 0;           // 0: by team size
     size_t bcast_mc_chunk = 0;          // 0: one workspace half per step
     size_t direct_min    = ~(size_t)0;  // messages from this size register their buffers and skip the workspace
     bool   direct_min_set = false;      // given explicitly: a tuning file does not override it
@@ -177,8 +180,12 @@ public:
                         size, cfg.tuning_file.c_str(), a, b, c);
             }
         }
-        if (cfg.one_shot_max == 0) cfg.one_shot_max = size >= 8 ? (256u << 10) : (1u << 20);
-        if (cfg.nvls_min == 0) cfg.nvls_min = size >= 8 ? (1u << 20) : (128u << 10);
+        // Two ranks: a multimem load or store sends the local half through the switch as well, so the in-switch
+        // paths move twice the bytes of a plain peer access and lose at every size measured; the one-shot kernel
+        // (one flag round trip) wins up to 4 MiB, and from a few MiB a broadcast is faster pulled by its one reader.
+        if (cfg.one_shot_max == 0) cfg.one_shot_max = size >= 8 ? (256u << 10) : size == 2 ? (4u << 20) : (1u << 20);
+        if (cfg.nvls_min == 0) cfg.nvls_min = size >= 8 ? (1u << 20) : size == 2 ? kNever : (128u << 10);
+        if (cfg.bcast_mc_max == 0) cfg.bcast_mc_max = size == 2 ? (1u << 20) : kNever;
         world.wait_budget_ns = (unsigned long long)(cfg.wait_timeout_ms * 1e6);
         for (int p = 0; p < size; p++) {
             world.pad[p] = (uint32_t *)region->base[(size_t)p];
@@ -515,7 +522,9 @@ xccl_status_t NvlReq::post()
         if (user) {
             take = args_.alg.id == ALG_SYMMETRIC || (args_.alg.id == ALG_NVLS && bytes >= team_->cfg.symmetric_min);
         } else {
-            take = bytes >= team_->cfg.symmetric_min && (args_.coll_type == XCCL_BCAST || bytes > team_->cfg.one_shot_max);
+            take = bytes >= team_->cfg.symmetric_min &&
+                   (args_.coll_type == XCCL_BCAST ? bytes <= team_->cfg.bcast_mc_max
+                                                  : bytes > team_->cfg.one_shot_max && team_->cfg.nvls_min != kNever);
         }
         if (take) {
             c.mc_src[0] = mc_src_;
@@ -569,17 +578,25 @@ xccl_status_t NvlReq::post()
         team_->phase += (alg == ALG_ONE_SHOT) ? 1 : chunks_used(w, XCCL_ALLREDUCE, c.count, c.len, dt);
         break;
     }
-    case XCCL_REDUCE:
-        st = launch_reduce(w, c, dt, out_dt, cfg, s);
+    case XCCL_REDUCE: {
+        // in-switch reduction at the root: asked for by name, or from the size where NVLS wins for allreduce
+        const bool can  = w.mc_ws != nullptr && nvls_supported(dt, (xccl_op_t)c.op);
+        const bool nvls = can && (args_.alg.set_by_user ? args_.alg.id == ALG_NVLS
+                                                        : c.count * xccl_dt_size(dt) >= team_->cfg.nvls_min);
+        st = launch_reduce(w, c, dt, out_dt, cfg, s, nvls);
+        if (nvls) team_->stats.nvls++;
         team_->phase += chunks_used(w, XCCL_REDUCE, c.count, c.len, dt);
         break;
+    }
     case XCCL_REDUCE_SCATTER:
         if (c.count == 0 && c.len != 0) c.count = c.len / xccl_dt_size(dt) / (size_t)team_->size;
-        st = launch_reduce_scatter(w, c, dt, out_dt, cfg, s);
+        st = launch_reduce_scatter(w, c, dt, out_dt, cfg, s,
+                                   args_.alg.set_by_user && args_.alg.id == ALG_NVLS && w.mc_ws != nullptr &&
+                                       nvls_supported(dt, (xccl_op_t)c.op));
         team_->phase += chunks_used(w, XCCL_REDUCE_SCATTER, c.count, c.len, dt);
         break;
     case XCCL_BCAST: {
-        bool mc = w.mc_ws != nullptr && c.len >= team_->cfg.bcast_mc_min;
+        bool mc = w.mc_ws != nullptr && c.len >= team_->cfg.bcast_mc_min && c.len <= team_->cfg.bcast_mc_max;
         if (args_.alg.set_by_user) mc = (args_.alg.id == ALG_NVLS);
         st = launch_bcast(w, c, cfg, s, mc);
         team_->phase += chunks_used(w, XCCL_BCAST, c.count, c.len, dt, mc);
@@ -697,10 +714,11 @@ public:
         return {
             {"WORKSPACE_SIZE", "128m", "Bytes of symmetric workspace per rank (two alternating halves)", OptType::MEMUNITS},
             {"NVLS", "try", "Bind the workspace to an NVSwitch multicast object and use multimem kernels", OptType::TERNARY},
-            {"ONE_SHOT_MAX", "0", "Allreduce messages up to this size use the one-shot kernel (0: by team size, 256k from 8 ranks, else 1m)", OptType::MEMUNITS},
-            {"NVLS_MIN", "0", "Allreduce messages from this size use NVLS when available (0: by team size, 1m from 8 ranks, else 128k)", OptType::MEMUNITS},
+            {"ONE_SHOT_MAX", "0", "Allreduce messages up to this size use the one-shot kernel (0: by team size, 256k from 8 ranks, 4m with 2, else 1m)", OptType::MEMUNITS},
+            {"NVLS_MIN", "0", "Allreduce messages from this size use NVLS when available (0: by team size, 1m from 8 ranks, never with 2, else 128k)", OptType::MEMUNITS},
             {"BCAST_MC_CHUNK", "0", "Multicast broadcasts move this many bytes per step, copy-out overlapping the next push (0: a workspace half)", OptType::MEMUNITS},
             {"BCAST_MC_MIN", "0", "Broadcasts from this size go through the NVSwitch multicast mapping when available", OptType::MEMUNITS},
+            {"BCAST_MC_MAX", "0", "Broadcasts above this size are pulled from the root's workspace instead (0: by team size, 1m with 2 ranks, else no limit)", OptType::MEMUNITS},
             {"DIRECT", "y", "Register the buffers of large messages with the peers (CUDA IPC) and run zero-copy kernels on them", OptType::BOOL},
             {"DIRECT_MIN", "0", "Messages from this size register their buffers and use the direct (zero-copy) kernels (0: from the tuning file, else only on request; measured crossover 32m-256m)", OptType::MEMUNITS},
             {"PUSH_MAX", "1m", "Allgather / alltoall messages up to this size (bytes per rank) store into the destinations' workspaces instead of being pulled", OptType::MEMUNITS},
@@ -738,6 +756,7 @@ public:
         c.one_shot_max    = (size_t)cfg.num("ONE_SHOT_MAX");
         c.nvls_min        = (size_t)cfg.num("NVLS_MIN");
         c.bcast_mc_min    = (size_t)cfg.num("BCAST_MC_MIN");
+        c.bcast_mc_max    = (size_t)cfg.num("BCAST_MC_MAX");
         c.bcast_mc_chunk  = (size_t)cfg.num("BCAST_MC_CHUNK");
         c.direct_min      = (size_t)cfg.num("DIRECT_MIN");
         c.direct_min_set  = c.direct_min != 0;

@@ -6,10 +6,13 @@
 //   mem_map_start(address, length, root)  the root creates a POSIX shared-memory window of
 //       `length` bytes and announces it out of band; everybody maps it
 //   FANOUT_GET(memh, offset, local_buffer, len)  the root publishes bytes [offset, offset+len) of
-//       its region into the window and raises a sequence flag; every other rank waits for the
+//       its region into the window and raises the request's flag; every other rank waits for the
 //       flag (bounded by XCCL_WAIT_TIMEOUT) and copies the bytes out. The root returns at once:
 //       it is a fan-out, completion on the root says nothing about the readers (callers that
 //       reuse the region follow it with a FANIN, as the reference's bcast schedule does).
+//   Requests on one region are numbered in the order they are created (the same on every rank, as
+//   for every collective) and each owns one of kSlots flags, so they may be POSTED in any order:
+//   the fragments of a pipelined broadcast complete their upper levels in no fixed order.
 // Host memory only.
 #include <atomic>
 #include <cerrno>
@@ -26,9 +29,11 @@ namespace shmseg {
 
 namespace {
 
+constexpr int kSlots = 256;  // flags per region: requests in use at the same time must be fewer than this apart in creation order
+
 struct WindowHdr {
-    std::atomic<uint64_t> published;  // number of FANOUT_GETs the root has published
-    char                  pad[56];
+    // flag of request k: slot k % kSlots holds (k << 24 | number of posts) of the newest publication
+    std::atomic<uint64_t> published[kSlots];
 };
 
 struct Announce {
@@ -67,7 +72,7 @@ public:
     void                 *base  = nullptr;
     size_t                bytes = 0;
     bool                  owner = false, ready = false;
-    uint64_t              gets  = 0;  // FANOUT_GETs issued on this handle by this rank
+    uint64_t              n_reqs = 0;  // FANOUT_GET requests created on this handle by this rank
     WindowHdr            *hdr() const { return (WindowHdr *)base; }
     char                 *data() const { return (char *)base + sizeof(WindowHdr); }
 };
@@ -103,6 +108,10 @@ xccl_status_t SegMem::start()
     if (team->rank == params.root) {
         std::snprintf(name, sizeof(name), "/xccl-seg-%d-%d", (int)getpid(), g_counter.fetch_add(1));
         int fd = shm_open(name, O_CREAT | O_EXCL | O_RDWR, 0600);
+        if (fd < 0 && errno == EEXIST) {  // this process's id and a counter it has not used: left by a dead process
+            shm_unlink(name);
+            fd = shm_open(name, O_CREAT | O_EXCL | O_RDWR, 0600);
+        }
         if (fd < 0) return XCCL_ERR_NO_RESOURCE;
         if (ftruncate(fd, (off_t)bytes) != 0) {
             close(fd);
@@ -148,19 +157,23 @@ xccl_status_t SegMem::test()
 
 class GetReq final : public xccl_coll_req {
 public:
-    GetReq(SegTeam *t, SegMem *m, const xccl_coll_get_info_t &g) : team_(t), mem_(m), get_(g) {}
+    GetReq(SegTeam *t, SegMem *m, const xccl_coll_get_info_t &g) : team_(t), mem_(m), get_(g), id_(m->n_reqs++) {}
     xccl_status_t post() override
     {
         if (!mem_->ready) return XCCL_ERR_NO_RESOURCE;
         if ((size_t)get_.offset + get_.len > mem_->params.length) return XCCL_ERR_INVALID_PARAM;
-        seq_  = ++mem_->gets;
+        seq_  = (id_ << 24) | (++posts_ & 0xffffffu);
         done_ = false;
         t0_   = std::chrono::steady_clock::now();
         if (team_->rank == mem_->params.root) {
             const char *src = (const char *)mem_->params.address + get_.offset;
             std::memcpy(mem_->data() + get_.offset, src, get_.len);
             if (get_.local_buffer != nullptr && get_.local_buffer != src) std::memcpy(get_.local_buffer, src, get_.len);
-            mem_->hdr()->published.store(seq_, std::memory_order_release);
+            // never lowered: a slot is shared by requests kSlots apart, the newer one has the larger value
+            auto    &flag = mem_->hdr()->published[id_ % kSlots];
+            uint64_t cur  = flag.load(std::memory_order_relaxed);
+            while (cur < seq_ && !flag.compare_exchange_weak(cur, seq_, std::memory_order_release, std::memory_order_relaxed)) {
+            }
             done_ = true;
         }
         return XCCL_OK;
@@ -168,7 +181,7 @@ public:
     xccl_status_t test() override
     {
         if (done_) return XCCL_OK;
-        if (mem_->hdr()->published.load(std::memory_order_acquire) >= seq_) {
+        if (mem_->hdr()->published[id_ % kSlots].load(std::memory_order_acquire) >= seq_) {
             std::memcpy(get_.local_buffer, mem_->data() + get_.offset, get_.len);
             done_ = true;
             return XCCL_OK;
@@ -186,6 +199,8 @@ private:
     SegTeam                              *team_;
     SegMem                               *mem_;
     xccl_coll_get_info_t                  get_;
+    uint64_t                              id_;         // creation index on the region, the same on every rank
+    uint64_t                              posts_ = 0;
     uint64_t                              seq_  = 0;
     bool                                  done_ = true;
     std::chrono::steady_clock::time_point t0_;

@@ -142,3 +142,40 @@ def _pipelined_bcast_rank(rank, size, job):
 
 def test_hier_bcast_fragmented_pipeline():
     run_ranks(_pipelined_bcast_rank, 4, timeout=120)
+
+
+def _sm_get_bcast_rank(rank, size, job, node_of, sock_of, check_window):
+    import glob
+    os.environ["XCCL_HIER_FAKE_NODE_ID"] = str(node_of[rank])
+    os.environ["XCCL_FAKE_SOCKET_ID"] = str(sock_of[rank])
+    oob = ShmOob(job, rank, size)
+    lib = Lib()
+    ctx = Context(lib, oob, tls=K.TL_HIER | K.TL_UCX,
+                  config={K.TL_HIER: {"ENABLE_SHMSEG": "y", "BCAST_SM_GET": "1", "BCAST_SM_GET_THRESH": "1k",
+                                      "BCAST_PIPELINE_THRESH": "16k", "BCAST_PIPELINE_DEPTH": "3",
+                                      "ENABLE_NVLINK": "no"}})
+    team = Team(ctx)
+    mine = "/dev/shm/xccl-seg-%d-*" % os.getpid()
+    for n, windows in ((100, False), (777, True), (50001, True)):   # 400 B: below the threshold; 200 KB: 13 fragments
+        for root in range(size):
+            buf = np.zeros(n, np.float32)
+            req = team.bcast(buf, root)
+            if check_window and rank == root:
+                # the root of a node-local level owns one window per region while the request lives
+                assert bool(glob.glob(mine)) == windows, (n, root, glob.glob(mine))
+            for it in range(3):  # persistent: the same regions and flags serve every post
+                buf[:] = _data(root, n, np.float32, seed=10 + it) if rank == root else 0
+                req.post().wait(timeout=60)
+                np.testing.assert_array_equal(buf, _data(root, n, np.float32, seed=10 + it))
+            req.finalize()
+            assert not glob.glob(mine)
+    team.close(); ctx.close(); lib.close(); oob.close()
+    return True
+
+
+@pytest.mark.parametrize("name", ["one_node_unbound", "two_nodes_two_sockets", "uneven_nodes_leader1"])
+def test_hier_bcast_through_fanout_get(name):
+    """Host broadcasts whose node-local levels are FANOUT_GETs on the shared-segment team, closed by a FANIN
+    (reference: src/team_lib/hier/xccl_hier_schedule_bcast.c:313-485, unreachable there for want of that team)."""
+    node_of, sock_of, _ = LAYOUTS[name]
+    run_ranks(_sm_get_bcast_rank, len(node_of), node_of, sock_of, name != "uneven_nodes_leader1", timeout=180)

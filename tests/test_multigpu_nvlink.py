@@ -194,6 +194,24 @@ def _rank_main(rank, size, job, tls, nvls):
             assert torch.all(dst[rd[s_]:rd[s_] + rcnt[s_]] == float(100 * s_ + rank)), ("alltoallv", s_)
         out["big_alltoallv"] = "ok"
     if (tls & K.TL_NVLINK) and out.get("nvls") == "ok":
+        # reduce to a root and reduce-scatter with the in-switch reduction (multimem.ld_reduce by the reducing rank);
+        # counts that are no multiple of a pack and that span several workspace chunks
+        for dtype in (torch.float32, torch.bfloat16):
+            for count in (5, 70001, (5 << 20) + 3):
+                src = _vals(rank, count, dtype, seed=60).to(dev)
+                dst = torch.zeros(count, dtype=dtype, device=dev)
+                root = count % size
+                team.reduce(src, dst, root=root, stream=stream, alg=K.NVLINK_ALG_NVLS, scale=0.5).run().finalize()
+                if rank == root:
+                    want = (torch.stack([_vals(r, count, dtype, seed=60).double() for r in range(size)]).sum(0) * 0.5).to(dtype)
+                    assert torch.equal(dst.cpu(), want), ("nvls reduce", dtype, count)
+            per = 40003
+            src = _vals(rank, per * size, dtype, seed=61).to(dev)
+            dst = torch.zeros(per, dtype=dtype, device=dev)
+            team.reduce_scatter(src, dst, stream=stream, alg=K.NVLINK_ALG_NVLS).run().finalize()
+            full = torch.stack([_vals(r, per * size, dtype, seed=61).double() for r in range(size)]).sum(0).to(dtype)
+            assert torch.equal(dst.cpu(), full[rank * per:(rank + 1) * per]), ("nvls reduce_scatter", dtype)
+        out["nvls_reduce"] = "ok"
         # symmetric memory: in-switch reduction and multicast straight on the caller's buffers
         nbytes = 8 << 20
         mem = team.mem_alloc(2 * nbytes)
