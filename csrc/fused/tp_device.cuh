@@ -36,11 +36,37 @@ struct Tile {
 //  COMM_ALLGATHER_A     row shard by row shard, starting with the local one (its A is already here)
 //  COMM_REDUCE_SCATTER  row shard by row shard, starting with the next rank's and ending with the
 //                       local one, so remote partial tiles leave early and local ones need no wire
+// Position t in a band of `mbs` row blocks x tiles_n column blocks that is walked in groups of row blocks (all column
+// blocks of a group before the next group) whose heights ramp up 1, 1, 2, 4, ... to `gr`. Used while the band's rows
+// are still arriving from the host: the first wave of tiles then needs the first rows only, and later groups are
+// reached after their rows have landed (the copy delivers rows faster than the tiles consume them).
+__host__ __device__ __forceinline__ void ramp_pos(int t, int mbs, int tiles_n, int gr, int *mb, int *nb)
+{
+    int start = 0, h = 1, i = 0;
+    for (;;) {
+        const int gm  = min(min(h, gr), mbs - start);
+        const int cnt = gm * tiles_n;
+        if (t < cnt || start + gm >= mbs) {
+            *mb = start + t % gm;
+            *nb = t / gm;
+            return;
+        }
+        t -= cnt;
+        start += gm;
+        h = (i++ == 0) ? 1 : min(h * 2, gr);  // capped: heights stay at gr once they reach it
+    }
+}
+
 __host__ __device__ __forceinline__ Tile tile_of(const GemmParams &p, int rank, int t, int tiles_m, int tiles_n)
 {
     Tile tl;
     if (p.comm == COMM_NONE) {
         const int gr    = p.group_rows > 0 ? p.group_rows : 16;
+        if (p.group_ramp) {
+            ramp_pos(t, tiles_m, tiles_n, gr, &tl.mb, &tl.nb);
+            tl.shard = 0;
+            return tl;
+        }
         const int group = gr * tiles_n;
         const int g = t / group, within = t % group;
         const int gm = min(gr, tiles_m - g * gr);
@@ -56,6 +82,11 @@ __host__ __device__ __forceinline__ Tile tile_of(const GemmParams &p, int rank, 
     tl.shard = (rank + first + idx) % p.tp_size;
     // inside a shard: sub-groups of group_rows row blocks x all column blocks
     const int gr  = (p.group_rows > 0 && p.group_rows < mbs) ? p.group_rows : mbs;
+    if (p.group_ramp && idx == 0 && p.comm == COMM_ALLGATHER_A) {  // the local shard, whose rows may still be arriving
+        ramp_pos(within, mbs, tiles_n, gr, &tl.mb, &tl.nb);
+        tl.mb += tl.shard * mbs;
+        return tl;
+    }
     const int sub = within / (gr * tiles_n), rem = within % (gr * tiles_n);
     const int gm  = min(gr, mbs - sub * gr);
     tl.mb = tl.shard * mbs + sub * gr + rem % gm;

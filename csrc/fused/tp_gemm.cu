@@ -714,6 +714,7 @@ const OptTable &tp_options()
             {"RS_DEBUG_LOCAL", "n", "Diagnostic, wrong results: GEMM->reduce-scatter stores every partial tile into local memory and waits for nobody, to time the kernel without its NVLink traffic", OptType::BOOL},
             {"RS_FUSED", "y", "GEMM->reduce-scatter: add the peers' partial tiles in the epilogue of the local tiles instead of a reduce phase after the last tile", OptType::BOOL},
             {"H2D_CHUNK_ROWS", "256", "Rows per chunk of the overlapped host->device input copy", OptType::UINT},
+            {"H2D_RAMP", "y", "While the input rows arrive from the host, walk the local rows in groups of 1, 1, 2, 4, ... row blocks instead of full groups", OptType::BOOL},
         });
         o.read(nullptr, nullptr);
         return o;
@@ -966,13 +967,24 @@ xccl_status_t xccl_gemm_swiglu_bf16(const void *A, const void *Wg, const void *W
 
 // Host-side view of the tile order (tests): writes (row block, column block, shard) of tile t = 0 .. tiles-1 as
 // rank `rank` walks them and returns the number of tiles, or -1 when `max` is too small.
+int xccl_tp_tile_order_ramp(int tiles_m, int tiles_n, int tp, int rank, int comm, int group_rows, int ramp, int *mb,
+                            int *nb, int *shard, int max);
+
 int xccl_tp_tile_order(int tiles_m, int tiles_n, int tp, int rank, int comm, int group_rows, int *mb, int *nb, int *shard,
                        int max)
+{
+    return xccl_tp_tile_order_ramp(tiles_m, tiles_n, tp, rank, comm, group_rows, 0, mb, nb, shard, max);
+}
+
+// ramp = 1: the order used while the local rows are still arriving from the host (GemmParams::group_ramp)
+int xccl_tp_tile_order_ramp(int tiles_m, int tiles_n, int tp, int rank, int comm, int group_rows, int ramp, int *mb,
+                            int *nb, int *shard, int max)
 {
     GemmParams p{};
     p.comm       = comm;
     p.tp_size    = tp;
     p.group_rows = group_rows;
+    p.group_ramp = ramp;
     const int total = tiles_m * tiles_n;
     if (total > max) return -1;
     for (int t = 0; t < total; t++) {

@@ -41,6 +41,7 @@ struct TpWorkspace {
     uint32_t   *in_flags[kMaxTpRanks] = {nullptr};  // per LOCAL rank: one word per chunk of in_rows rows
     uint32_t    in_seq = 0;
     bool        in_active = false;
+    bool        in_ramp   = false;  // walk the local rows in growing groups: the kernel starts before the rows are there
     int         in_rows = 256;
     cudaEvent_t in_consumed = nullptr;
 
@@ -275,6 +276,7 @@ xccl_status_t xccl_tp_ag_gemm_swiglu(xccl_tp_ws_h w, const void *const *Wg, cons
     if (w->in_active) {
         p.in_target        = w->in_seq;
         p.in_rows_per_flag = w->in_rows;
+        p.group_ramp       = w->in_ramp ? 1 : 0;
     }
     xccl_status_t lst = launch_gemm(p, l, (cudaStream_t)stream);
     if (w->in_active && lst == XCCL_OK) {
@@ -286,13 +288,29 @@ xccl_status_t xccl_tp_ag_gemm_swiglu(xccl_tp_ws_h w, const void *const *Wg, cons
     return lst;
 }
 
-xccl_status_t xccl_tp_h2d_begin(xccl_tp_ws_h w, const void *const *host_x, void *copy_stream)
+// The overlapped input copy in two halves, so that the caller can launch the consuming kernel BETWEEN them: the kernel
+// then starts at once and waits for rows, and the host time of issuing the chunks (two driver calls per chunk) is spent
+// while the GPU already works. `expect` fixes the sequence number the next allgather->GEMM waits for and orders the copy
+// stream after the kernel that read the shard last; `issue` enqueues the chunks and their flag writes. ramp != 0: the
+// kernel walks the local rows in groups of 1, 1, 2, 4, ... row blocks, so its first wave needs the first chunk only
+// (for a step that starts with an idle GPU; a pipelined caller, whose copy runs under the previous step's second
+// kernel, passes 0 and keeps the full groups).
+xccl_status_t xccl_tp_h2d_expect(xccl_tp_ws_h w, void *copy_stream, int ramp)
+{
+    if (w == nullptr) return XCCL_ERR_INVALID_PARAM;
+    if (w->in_active) return XCCL_ERR_NO_RESOURCE;  // one copy per allgather->GEMM
+    if (w->in_consumed != nullptr) XCCL_CUDA_CHECK(cudaStreamWaitEvent((cudaStream_t)copy_stream, w->in_consumed, 0));
+    w->in_seq++;
+    w->in_active = true;
+    w->in_ramp   = ramp != 0 && tp_options().flag("H2D_RAMP");
+    return XCCL_OK;
+}
+
+xccl_status_t xccl_tp_h2d_issue(xccl_tp_ws_h w, const void *const *host_x, void *copy_stream)
 {
     if (w == nullptr || host_x == nullptr) return XCCL_ERR_INVALID_PARAM;
     XCCL_DRIVER_FN(cuStreamWriteValue32);
     cudaStream_t cs = (cudaStream_t)copy_stream;
-    if (w->in_consumed != nullptr) XCCL_CUDA_CHECK(cudaStreamWaitEvent(cs, w->in_consumed, 0));
-    w->in_seq++;
     const size_t rows = (size_t)w->M / w->tp, row_bytes = (size_t)w->K * 2;
     for (int i = 0; i < w->n_local; i++) {
         char       *dst = (char *)xccl_tp_ws_x_shard(w, i);
@@ -304,8 +322,13 @@ xccl_status_t xccl_tp_h2d_begin(xccl_tp_ws_h w, const void *const *host_x, void 
             XCCL_CU_CHECK(cuStreamWriteValue32((CUstream)cs, (CUdeviceptr)(w->in_flags[i] + c), w->in_seq, 0));
         }
     }
-    w->in_active = true;
     return XCCL_OK;
+}
+
+xccl_status_t xccl_tp_h2d_begin(xccl_tp_ws_h w, const void *const *host_x, void *copy_stream)
+{
+    xccl_status_t st = xccl_tp_h2d_expect(w, copy_stream, 1);
+    return st != XCCL_OK ? st : xccl_tp_h2d_issue(w, host_x, copy_stream);
 }
 
 xccl_status_t xccl_tp_gemm_rs(xccl_tp_ws_h w, const void *const *Hin, const void *const *Wd, void *const *Yout,

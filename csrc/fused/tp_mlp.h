@@ -41,6 +41,12 @@ xccl_status_t xccl_tp_gemm_rs(xccl_tp_ws_h ws, const void *const *Hin, const voi
 // call (on its own stream, no event between the two) starts at once and consumes the rows as their chunks land, so
 // the copy hides behind the first tiles instead of preceding the kernel.
 xccl_status_t xccl_tp_h2d_begin(xccl_tp_ws_h ws, const void *const *host_x, void *copy_stream);
+/* The same copy in two calls with the launch of xccl_tp_ag_gemm_swiglu between them (expect, launch, issue): the kernel
+ * starts at once and the chunks are enqueued while it already runs. Every `expect` must be followed by the launch and
+ * the `issue`: the kernel's waits for the rows are bounded. ramp != 0: the local rows are walked in groups of 1, 1, 2,
+ * 4, ... row blocks, so that the first tiles need the first chunk only (a step that starts on an idle GPU). */
+xccl_status_t xccl_tp_h2d_expect(xccl_tp_ws_h ws, void *copy_stream, int ramp);
+xccl_status_t xccl_tp_h2d_issue(xccl_tp_ws_h ws, const void *const *host_x, void *copy_stream);
 
 // ---- block-scaled fp8 variants (e4m3 activations with 1 x 128 scales, e4m3 weights with 128 x 128 scales)
 // The fp8 rows and their scales live in the same gathered buffer as the bf16 rows ([M, K] bytes followed by

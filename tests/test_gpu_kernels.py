@@ -573,6 +573,28 @@ def test_tp_mlp_input_arriving_from_host_overlaps_first_kernel(dev, tp, monkeypa
         mlp.close()
 
 
+def test_tp_mlp_full_output_read_back_is_pipelined_and_exact(dev):
+    """forward_from_host_full: input from pinned memory (kernels launched first, rows follow), the whole output shard
+    copied back on a copy stream while the next step runs; every step's host copy must hold that step's output."""
+    from xccl_b200.models.tp_mlp import TpMlp, reference_forward_fp32
+    tokens, hidden, ffn = 1024, 512, 1024
+    mlp = TpMlp(tokens, hidden, ffn, tp=1)
+    try:
+        y_pinned = [[torch.empty(tokens, hidden, dtype=torch.bfloat16).pin_memory()] for _ in range(2)]
+        xs = [torch.randn(tokens, hidden, generator=torch.Generator().manual_seed(40 + it)).to(torch.bfloat16) for it in range(4)]
+        pinned = [[x.pin_memory()] for x in xs]
+        wants = [reference_forward_fp32(x.to(dev), *_full_weights(mlp)) for x in xs]
+        for it in range(4):   # no host wait between the steps
+            mlp.forward_from_host_full(pinned[it], y_pinned)
+        mlp.wait_outputs()
+        mlp.check_error()
+        # the two host buffers hold the outputs of the last two steps (parity 0: step 2, parity 1: step 3)
+        torch.testing.assert_close(y_pinned[0][0].float().to(dev), wants[2], rtol=3e-2, atol=3e-2)
+        torch.testing.assert_close(y_pinned[1][0].float().to(dev), wants[3], rtol=3e-2, atol=3e-2)
+    finally:
+        mlp.close()
+
+
 # ----------------------------------------------------------------------------- fused MoE all-to-all
 @pytest.mark.parametrize("ranks", [1, 2, 4])
 def test_moe_dispatch_combine_matches_reference(dev, ranks):

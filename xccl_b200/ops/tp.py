@@ -23,6 +23,8 @@ K.optional("xccl_tp_ws_error", C.c_uint32, C.c_void_p)
 K.optional("xccl_tp_ag_gemm_swiglu", C.c_int, C.c_void_p, _pp, _pp, _pp, C.c_int, C.c_void_p)
 K.optional("xccl_tp_gemm_rs", C.c_int, C.c_void_p, _pp, _pp, _pp, C.c_int, C.c_void_p)
 K.optional("xccl_tp_h2d_begin", C.c_int, C.c_void_p, _pp, C.c_void_p)
+K.optional("xccl_tp_h2d_expect", C.c_int, C.c_void_p, C.c_void_p, C.c_int)
+K.optional("xccl_tp_h2d_issue", C.c_int, C.c_void_p, _pp, C.c_void_p)
 K.optional("xccl_tp_quantize_rows", C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p)
 K.optional("xccl_tp_ws_x8_shard", C.c_void_p, C.c_void_p, C.c_int)
 K.optional("xccl_tp_ws_sx_shard", C.c_void_p, C.c_void_p, C.c_int)
@@ -129,6 +131,26 @@ class TpWorkspace:
         st = K.load().xccl_tp_h2d_begin(self.h, arr, copy_stream.cuda_stream)
         if st != K.OK:
             raise XcclError(st, "xccl_tp_h2d_begin")
+
+    def h2d_expect(self, copy_stream: "torch.cuda.Stream", ramp: bool = True) -> None:
+        """First half of ``h2d_begin``: the next ``ag_gemm_swiglu`` will wait for the rows of a copy that
+        ``h2d_issue`` enqueues AFTER the kernel has been launched, so the host time of issuing the chunks is spent
+        while the kernel already runs. Must be followed by the launch and by ``h2d_issue``. ``ramp``: the kernel
+        walks the local rows in groups of 1, 1, 2, 4, ... row blocks so that its first tiles need the first chunk only;
+        a pipelined caller, whose copy runs under the previous step's kernels, passes False."""
+        st = K.load().xccl_tp_h2d_expect(self.h, copy_stream.cuda_stream, 1 if ramp else 0)
+        if st != K.OK:
+            raise XcclError(st, "xccl_tp_h2d_expect")
+
+    def h2d_issue(self, x_pinned: Sequence[torch.Tensor], copy_stream: "torch.cuda.Stream") -> None:
+        arr = (C.c_void_p * len(x_pinned))()
+        for i, t in enumerate(x_pinned):
+            if t.dtype != torch.bfloat16 or not t.is_contiguous() or not t.is_pinned():
+                raise ValueError("expected contiguous pinned bf16 host tensors")
+            arr[i] = t.data_ptr()
+        st = K.load().xccl_tp_h2d_issue(self.h, arr, copy_stream.cuda_stream)
+        if st != K.OK:
+            raise XcclError(st, "xccl_tp_h2d_issue")
 
     # ---- block-scaled fp8 (the same buffers hold [M, K] e4m3 rows followed by [M, K/128] fp32 scales)
     def x8_shard(self, local_rank: int = 0) -> torch.Tensor:
