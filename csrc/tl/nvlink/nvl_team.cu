@@ -37,6 +37,7 @@ struct NvlCfg {
     size_t direct_min    = ~(size_t)0;  // messages from this size register their buffers and skip the workspace
     bool   direct_min_set = false;      // given explicitly: a tuning file does not override it
     bool   direct        = true;
+    bool   direct_cache  = true;        // keep peer mappings of registered buffers until the team goes
     bool   symmetric     = true;        // zero-copy NVLS on buffers from xccl_team_mem_alloc
     size_t symmetric_min = 32u << 10;
     size_t push_max      = 1u << 20;  // allgather / alltoall up to this many bytes per rank use the push form
@@ -104,6 +105,7 @@ private:
     // direct algorithms: every rank's buffers of this request, mapped here at init
     xccl_status_t       register_buffers(void *src, void *dst, size_t src_bytes, size_t dst_bytes);
     bool                direct_ = false;
+    std::vector<std::string> mappings_;  // peer mappings this request holds a count on
     const void         *peer_src_[kMaxRanks] = {nullptr};
     void               *peer_dst_[kMaxRanks] = {nullptr};
     // symmetric algorithms: the buffers lie in memory of xccl_team_mem_alloc; their multicast addresses
@@ -125,26 +127,38 @@ public:
         tl_info(tl_, "nvlink team rank %d: allreduce posts one-shot %llu, two-shot %llu, NVLS %llu, direct %llu; other "
                 "collectives %llu (direct %llu); on symmetric memory %llu", rank, stats.one_shot, stats.two_shot, stats.nvls,
                 stats.direct_allreduce, stats.other, stats.direct_other, stats.symmetric);
-        for (auto &kv : ipc_cache) cudaIpcCloseMemHandle(kv.second);
+        for (auto &kv : ipc_cache) cudaIpcCloseMemHandle(kv.second.ptr);
         for (SymmetricRegion *r : sym_regions) delete r;
         delete region;
         if (status_host != nullptr) cudaFreeHost(status_host);
     }
 
-    // Mapping of a peer's allocation (legacy CUDA IPC), opened once per allocation and kept until the team goes.
-    void *open_peer(const cudaIpcMemHandle_t &h)
+    // Mapping of a peer's allocation (legacy CUDA IPC), opened once per allocation and counted per request that uses
+    // it. With DIRECT_CACHE (default) it is kept until the team goes; without, release_peer closes it with its last user.
+    void *open_peer(const cudaIpcMemHandle_t &h, std::vector<std::string> *used)
     {
         std::string key((const char *)&h, sizeof(h));
         auto        it = ipc_cache.find(key);
-        if (it != ipc_cache.end()) return it->second;
-        void *p = nullptr;
-        if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
-            (void)cudaGetLastError();
-            return nullptr;
+        if (it == ipc_cache.end()) {
+            void *p = nullptr;
+            if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+                (void)cudaGetLastError();
+                return nullptr;
+            }
+            it = ipc_cache.emplace(key, PeerMapping{p, 0}).first;
         }
-        ipc_cache[key] = p;
-        return p;
+        it->second.refs++;
+        used->push_back(key);
+        return it->second.ptr;
     }
+    void release_peer(const std::string &key)
+    {
+        auto it = ipc_cache.find(key);
+        if (it == ipc_cache.end() || --it->second.refs > 0 || cfg.direct_cache) return;
+        cudaIpcCloseMemHandle(it->second.ptr);
+        ipc_cache.erase(it);
+    }
+    size_t peer_mappings() const { return ipc_cache.size(); }
 
     xccl_status_t init(const OobGroup &g)
     {
@@ -255,7 +269,11 @@ public:
     TeamLib         *tl_;
     NvlCfg           cfg;
     OobGroup         oob;
-    std::map<std::string, void *> ipc_cache;
+    struct PeerMapping {
+        void *ptr;
+        int   refs;
+    };
+    std::map<std::string, PeerMapping> ipc_cache;
     std::vector<SymmetricRegion *> sym_regions;
     struct {
         unsigned long long one_shot = 0, two_shot = 0, nvls = 0, direct_allreduce = 0, other = 0, direct_other = 0, symmetric = 0;
@@ -295,6 +313,8 @@ NvlReq::~NvlReq()
     if (done_ != nullptr) cudaEventDestroy(done_);
     if (start_ != nullptr) cudaEventDestroy(start_);
     if (vmeta_ != nullptr) cudaFree(vmeta_);
+    // a finalized request has no kernel in flight: its count on the peers' mappings can go
+    for (const std::string &k : mappings_) team_->release_peer(k);
 }
 
 xccl_status_t NvlReq::prepare()
@@ -436,14 +456,14 @@ xccl_status_t NvlReq::register_buffers(void *src, void *dst, size_t src_bytes, s
             peer_dst_[p] = dst;
             continue;
         }
-        char *ms = (char *)team_->open_peer(all[(size_t)p].src_h);
+        char *ms = (char *)team_->open_peer(all[(size_t)p].src_h, &mappings_);
         if (ms == nullptr) {
             ok = 0;
             break;
         }
         peer_src_[p] = ms + all[(size_t)p].src_off;
         if (dst_bytes != 0) {
-            char *md = (char *)team_->open_peer(all[(size_t)p].dst_h);
+            char *md = (char *)team_->open_peer(all[(size_t)p].dst_h, &mappings_);
             if (md == nullptr) {
                 ok = 0;
                 break;
@@ -720,6 +740,7 @@ public:
             {"BCAST_MC_MIN", "0", "Broadcasts from this size go through the NVSwitch multicast mapping when available", OptType::MEMUNITS},
             {"BCAST_MC_MAX", "0", "Broadcasts above this size are pulled from the root's workspace instead (0: by team size, 1m with 2 ranks, else no limit)", OptType::MEMUNITS},
             {"DIRECT", "y", "Register the buffers of large messages with the peers (CUDA IPC) and run zero-copy kernels on them", OptType::BOOL},
+            {"DIRECT_CACHE", "y", "Keep the peers' mappings of registered buffers until the team is destroyed (a registration cache); n: a mapping is closed when the last request that uses it is finalized, after which its owner may free the buffer", OptType::BOOL},
             {"DIRECT_MIN", "0", "Messages from this size register their buffers and use the direct (zero-copy) kernels (0: from the tuning file, else only on request; measured crossover 32m-256m)", OptType::MEMUNITS},
             {"PUSH_MAX", "1m", "Allgather / alltoall messages up to this size (bytes per rank) store into the destinations' workspaces instead of being pulled", OptType::MEMUNITS},
             {"SYMMETRIC", "y", "Run collectives whose buffers come from xccl_team_mem_alloc zero-copy through the multicast mapping", OptType::BOOL},
@@ -766,6 +787,7 @@ public:
         if (!c.direct_min_set) c.direct_min = ~(size_t)0;
         c.tuning_file     = cfg.str("TUNING_FILE");
         c.direct          = cfg.flag("DIRECT");
+        c.direct_cache    = cfg.flag("DIRECT_CACHE");
         c.push_max        = (size_t)cfg.num("PUSH_MAX");
         c.symmetric       = cfg.flag("SYMMETRIC");
         c.symmetric_min   = (size_t)cfg.num("SYMMETRIC_MIN");
@@ -782,6 +804,18 @@ NvlLib           g_nvl_lib;
 TeamLibRegistrar g_nvl_reg(&g_nvl_lib);
 
 }  // namespace
+
+// Peer mappings (registered buffers of other ranks, one per allocation) that the NVLink part of `team` holds right
+// now; -1 when the team has none. With DIRECT_CACHE=n it falls back to 0 once the requests that registered buffers
+// have been finalized.
+extern "C" int xccl_nvlink_peer_mappings(xccl_team_h team)
+{
+    if (team == nullptr) return -1;
+    for (auto &t : team->tl_teams) {
+        if (auto *n = dynamic_cast<NvlTeam *>(t.get())) return (int)n->peer_mappings();
+    }
+    return -1;
+}
 
 }  // namespace nvl
 }  // namespace xccl

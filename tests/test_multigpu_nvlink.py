@@ -307,6 +307,49 @@ def test_tp_mlp_fused_across_gpus(size):
     print("tp mlp max abs err per rank:", res)
 
 
+def _registration_release_main(rank, size, job):
+    """DIRECT_CACHE=n: the peers' mappings of registered buffers live as long as the requests that use them."""
+    import ctypes as C
+    from xccl_b200.api import Context, Lib, ShmOob, Team
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    oob = ShmOob(job, rank, size)
+    lib = Lib()
+    ctx = Context(lib, oob, tls=K.TL_NVLINK | K.TL_UCX, config={K.TL_NVLINK: {"DIRECT_CACHE": "n", "WORKSPACE_SIZE": "32m"}})
+    team = Team(ctx)
+    count_fn = K.load().xccl_nvlink_peer_mappings
+    count_fn.restype, count_fn.argtypes = C.c_int, [C.c_void_p]
+    stream = torch.cuda.current_stream().cuda_stream
+    assert count_fn(team.h) == 0
+    for it in range(3):   # fresh buffers every round: each is registered, used, released; its memory may then be freed
+        n = (1 << 20) + 16 * it
+        src = _vals(rank, n, torch.float32, seed=70 + it).to(dev)
+        dst = torch.zeros_like(src)
+        r1 = team.allreduce(src, dst, stream=stream, alg=K.NVLINK_ALG_DIRECT)
+        r2 = team.allreduce(src, dst, stream=stream, alg=K.NVLINK_ALG_DIRECT)   # the same allocations: counted twice
+        held = count_fn(team.h)
+        assert 1 <= held <= 2 * (size - 1), held
+        r1.run()
+        want = torch.stack([_vals(r, n, torch.float32, seed=70 + it) for r in range(size)]).sum(0)
+        assert torch.equal(dst.cpu(), want)
+        r1.finalize()
+        assert count_fn(team.h) == held          # r2 still holds them
+        r2.run()
+        assert torch.equal(dst.cpu(), want)
+        r2.finalize()
+        assert count_fn(team.h) == 0
+        team.barrier().run().finalize()         # every peer has closed its mapping of my buffers
+        del src, dst
+    team.close(); ctx.close(); lib.close(); oob.close()
+    return True
+
+
+def test_registered_buffers_are_released_with_their_requests():
+    if _ngpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    run_ranks(_registration_release_main, 2, timeout=300, start_method="spawn")
+
+
 def _host_team_cuda_main(rank, size, job):
     """The host team serving CUDA buffers (the reference's CUDA tests run its UCX team on device memory,
     test/test_mpi_cuda_allreduce.c, test_mpi_cuda_reduce.c): staged through pinned memory, started in
