@@ -1,7 +1,11 @@
 #include "schedule.h"
 
+#include <algorithm>
 #include <array>
+#include <chrono>
 #include <deque>
+#include <thread>
+#include <vector>
 
 #include "log.h"
 
@@ -220,3 +224,52 @@ std::unique_ptr<ProgressQueue> ProgressQueue::create(unsigned thread_mode, int l
 }
 
 }  // namespace xccl
+
+// Self-test of a progress queue (tests): `producers` threads enqueue `tasks_per_thread` tasks each, every task needs
+// `polls` progress calls to complete, and all threads call progress() until everything has completed or `timeout_s`
+// has passed. Returns the number of completed tasks (every task exactly once: a task that is progressed after its
+// completion, or twice at the same time, counts as -1000000).
+extern "C" long xccl_progress_queue_selftest(unsigned thread_mode, int lf_slots, int producers, int tasks_per_thread,
+                                             int polls, double timeout_s)
+{
+    using namespace xccl;
+    struct Counted final : Task {
+        std::atomic<int> left{0};
+        std::atomic<int> busy{0};
+    };
+    auto                  queue = ProgressQueue::create(thread_mode, lf_slots);
+    const int             total = producers * tasks_per_thread;
+    std::vector<Counted>  tasks((size_t)total);
+    std::atomic<long>     completed{0}, errors{0};
+    for (auto &t : tasks) {
+        t.left.store(polls);
+        t.progress = [&completed, &errors](Task *self) -> xccl_status_t {
+            auto *c = static_cast<Counted *>(self);
+            if (c->busy.fetch_add(1) != 0) errors.fetch_add(1);  // two threads in one task at once
+            const int left = c->left.fetch_sub(1) - 1;
+            if (left < 0) errors.fetch_add(1);                   // progressed after completion
+            c->busy.fetch_sub(1);
+            if (left == 0) {
+                c->complete(XCCL_OK);
+                completed.fetch_add(1);
+            }
+            return XCCL_OK;
+        };
+    }
+    const auto t0 = std::chrono::steady_clock::now();
+    auto expired  = [&] { return std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() > timeout_s; };
+    std::vector<std::thread> threads;
+    const int                n_threads = thread_mode == XCCL_THREAD_MODE_MULTIPLE ? producers : 1;
+    for (int p = 0; p < n_threads; p++) {
+        threads.emplace_back([&, p] {
+            const int mine = thread_mode == XCCL_THREAD_MODE_MULTIPLE ? tasks_per_thread : total;
+            for (int i = 0; i < mine; i++) {
+                queue->enqueue(&tasks[(size_t)(p * tasks_per_thread + i)]);
+                queue->progress();
+            }
+            while (completed.load() < total && !expired()) queue->progress();
+        });
+    }
+    for (auto &t : threads) t.join();
+    return errors.load() != 0 ? -1000000 : completed.load();
+}
