@@ -78,6 +78,15 @@ __host__ __device__ __forceinline__ Tile tile_of(const GemmParams &p, int rank, 
     const int mbs   = tiles_m / p.tp_size;
     const int per   = mbs * tiles_n;
     const int idx   = t / per, within = t % per;
+    if (p.comm == COMM_ALLGATHER_A && p.group_ramp == 2) {
+        // every rank's rows are still arriving: row block c of every shard, local shard first, all column blocks
+        const int per_phase = tiles_n * p.tp_size;
+        const int c = t / per_phase, rem = t % per_phase;
+        tl.nb    = rem / p.tp_size;
+        tl.shard = (rank + rem % p.tp_size) % p.tp_size;
+        tl.mb    = tl.shard * mbs + c;
+        return tl;
+    }
     const int first = (p.comm == COMM_ALLGATHER_A) ? 0 : 1;
     tl.shard = (rank + first + idx) % p.tp_size;
     // inside a shard: sub-groups of group_rows row blocks x all column blocks
@@ -138,6 +147,7 @@ __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x));
 // chunk i (peer memory -> slot) is issued kCopyAhead chunks before its store (slot -> local buffer),
 // so every copy CTA keeps kCopyAhead * kCopyChunk bytes in flight on the wire without holding them
 // in registers.
+constexpr int      kProgressSlot = 1200;  // pad counter words [1200, 1200 + ranks): blocks of each rank's shard that have landed
 constexpr int      kCopySlots = 12;
 constexpr int      kCopyAhead = 8;
 constexpr int      kCopyLag   = 2;       // a block is announced once the stores of 2 later chunks were issued
@@ -166,14 +176,43 @@ __device__ void copy_cta_loop(const GemmParams &p, int rank, int local, int copy
         for (int s = 0; s < kCopySlots; s++) mbar_init(bars + 8u * s, 1);
         mbar_fence_init();
     }
-    // my own shard may still be arriving from the host: the peers are told to read it only when all of it is here
-    if (p.in_ready[local] != nullptr && threadIdx.x == 0) {
-        const int chunks = (p.M / p.tp_size + p.in_rows_per_flag - 1) / p.in_rows_per_flag;
-        for (int c = 0; c < chunks; c++) {
-            if (!wait_counter(p.in_ready[local] + c, p.in_target, true, ab, 9)) break;
+    // Two ways of telling the peers that this rank's shard may be read.
+    //  whole (default): the shard is complete before this CTA joins the opening barrier below; where it is still
+    //    arriving from the host, thread 0 waits for all of its chunks first.
+    //  by block (group_ramp == 2, the same on every rank of the launch): a word per source rank in every reader's
+    //    pad holds (sequence number of this launch << 8) | 128-row blocks that have landed. A shard that was
+    //    complete when the kernel started is reported whole at once; one that is still arriving is reported block by
+    //    block as its chunks land. Written by one thread of copy CTA 0 (beside thread 0's copy ring), read by every
+    //    copy CTA before it pulls a block.
+    const bool     by_block  = p.group_ramp == 2;
+    const uint32_t prog_base = p.seq << 8;
+    if (!by_block) {
+        if (p.in_ready[local] != nullptr && threadIdx.x == 0) {
+            const int chunks = (p.M / p.tp_size + p.in_rows_per_flag - 1) / p.in_rows_per_flag;
+            for (int c = 0; c < chunks; c++) {
+                if (!wait_counter(p.in_ready[local] + c, p.in_target, true, ab, 9)) break;
+            }
+        }
+    } else if (copy_idx == 0 && threadIdx.x == 32) {
+        auto publish = [&](uint32_t blocks) {
+            for (int q = 0; q < p.tp_size; q++) {
+                if (q != rank) nvl::st_release_sys(p.pad[q] + nvl::kPadCounterOff + kProgressSlot + rank, prog_base | blocks);
+            }
+        };
+        if (p.in_ready[local] == nullptr) {
+            publish((uint32_t)mbs);
+        } else {
+            const int rows   = p.M / p.tp_size;
+            const int chunks = (rows + p.in_rows_per_flag - 1) / p.in_rows_per_flag;
+            uint32_t  told   = 0;
+            for (int c = 0; c < chunks; c++) {
+                if (!wait_counter(p.in_ready[local] + c, p.in_target, true, ab, 9)) break;
+                const uint32_t landed = (uint32_t)(min(rows, (c + 1) * p.in_rows_per_flag) / kBM);
+                if (landed > told) publish(told = landed);
+            }
         }
     }
-    // peers must have published their shards before we read them: barrier among the copy CTAs
+    // every peer has entered this launch (its gathered buffer is no longer read by its previous kernels' tiles)
     uint32_t *epoch_slot = p.pad[rank] + nvl::kPadEpochOff + copy_idx;
     uint32_t  epoch      = *epoch_slot + 1;
     __syncthreads();
@@ -193,8 +232,24 @@ __device__ void copy_cta_loop(const GemmParams &p, int rank, int local, int copy
     if (threadIdx.x == 0) {
         const int n_blocks = (p.tp_size - 1) * mbs;
         auto block_of = [&](int b) {  // b-th remote row block in the order this rank pulls them
+            if (by_block) {           // row block c of every remote shard, then c + 1: the order of the tile walk
+                const int c = b / (p.tp_size - 1), shard = (rank + 1 + b % (p.tp_size - 1)) % p.tp_size;
+                return shard * mbs + c;
+            }
             const int shard = (rank + 1 + b / mbs) % p.tp_size;
             return shard * mbs + b % mbs;
+        };
+        // blocks of each shard known to have landed at their owner
+        uint32_t        landed[kMaxTpRanks] = {0};
+        const uint32_t *progress = p.pad[rank] + nvl::kPadCounterOff + kProgressSlot;
+        auto wait_landed = [&](int blk) {
+            if (!by_block) return true;  // the opening barrier has said it for the whole shard
+            const int      shard = blk / mbs;
+            const uint32_t need  = (uint32_t)(blk % mbs) + 1u;
+            if (landed[shard] >= need) return true;
+            if (!wait_counter(progress + shard, prog_base | need, true, ab, 10)) return false;
+            landed[shard] = nvl::ld_acquire_sys(progress + shard) - prog_base;  // at least `need`; a later launch's value is larger still
+            return true;
         };
         auto announce = [&](int b) {
             asm volatile("fence.proxy.async.global;" ::: "memory");
@@ -202,7 +257,10 @@ __device__ void copy_cta_loop(const GemmParams &p, int rank, int local, int copy
             red_release_gpu_add(p.ready[local] + block_of(b), 1u);
         };
         if (cpb == 0) {
-            for (int b = 0; b < n_blocks; b++) announce(b);
+            for (int b = 0; b < n_blocks; b++) {
+                if (!wait_landed(block_of(b))) break;
+                announce(b);
+            }
         } else {
             const int total = n_blocks * cpb;
             // chunk g of this CTA: where it comes from in rank `shard`'s buffers and where it goes in mine
@@ -227,6 +285,10 @@ __device__ void copy_cta_loop(const GemmParams &p, int rank, int local, int copy
             int  loads_issued = 0, stores_issued = 0;
             for (int i = 0; i < total + kCopyAhead && ok; i++) {
                 if (i < total) {
+                    if (i % cpb == 0 && !wait_landed(block_of(i / cpb))) {  // first chunk of a block: its rows are at the owner
+                        ok = false;
+                        break;
+                    }
                     // the slot's previous store (chunk i - kCopySlots) must have left shared memory
                     if (i >= kCopySlots) bulk_wait_read<kCopySlots - 1 - kCopyAhead>();
                     const char *src;

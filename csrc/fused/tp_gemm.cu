@@ -714,6 +714,7 @@ const OptTable &tp_options()
             {"RS_DEBUG_LOCAL", "n", "Diagnostic, wrong results: GEMM->reduce-scatter stores every partial tile into local memory and waits for nobody, to time the kernel without its NVLink traffic", OptType::BOOL},
             {"RS_FUSED", "y", "GEMM->reduce-scatter: add the peers' partial tiles in the epilogue of the local tiles instead of a reduce phase after the last tile", OptType::BOOL},
             {"H2D_CHUNK_ROWS", "256", "Rows per chunk of the overlapped host->device input copy", OptType::UINT},
+            {"H2D_PHASES", "n", "Allgather with copy CTAs while every rank's input arrives from the host: ranks report their rows block by block and the tiles are walked row block by row block over all shards (set it on every rank alike). Measured on 4 GPUs: no gain over the default (3.07 against 2.94 ms per end-to-end step)", OptType::BOOL},
             {"H2D_RAMP", "y", "While the input rows arrive from the host, walk the local rows in groups of 1, 1, 2, 4, ... row blocks instead of full groups", OptType::BOOL},
         });
         o.read(nullptr, nullptr);

@@ -40,8 +40,13 @@ struct GemmParams {
     int n_gemm_ctas;      // CTAs (per rank) that run MMA tiles; the rest copy (allgather mode, copy_mode 0)
     int copy_mode;        // allgather mode: 0 = whole CTAs set aside for the copy, 1 = two copier warps in every CTA
     int group_rows;       // row blocks of tiles walked together before moving along N (0 = chosen from the shape)
-    int group_ramp;       // 1: the first groups of the rows that arrive from the host are 1, 1, 2, 4, ... row blocks high,
-                          // so the first wave of tiles needs the first chunk of the copy only
+    int group_ramp;       // order of the tile walk while input rows are still arriving from the host.
+                          // 1: the groups of the local rows are 1, 1, 2, 4, ... row blocks high, so the first wave of
+                          //    tiles needs the first chunk of the copy only;
+                          // 2 (allgather mode with copy CTAs): phase c = row block c of EVERY rank's shard (local one
+                          //    first) x all column blocks; the copy CTAs pull in the same order, block by block as the
+                          //    owners report them landed, so remote tiles start after the first chunks, not after
+                          //    the peers' whole shards
     int l2_hint;          // operand loads: 0 no hint, 1 A and B evict_last, 2 A evict_last / B evict_first, 3 the reverse
     int st_stream;        // 1: output stores are marked streaming (evict first)
     // Soft lockstep of the tile walkers: before a tile (and every sync_kblocks K blocks inside it) a walker

@@ -41,7 +41,7 @@ struct TpWorkspace {
     uint32_t   *in_flags[kMaxTpRanks] = {nullptr};  // per LOCAL rank: one word per chunk of in_rows rows
     uint32_t    in_seq = 0;
     bool        in_active = false;
-    bool        in_ramp   = false;  // walk the local rows in growing groups: the kernel starts before the rows are there
+    int         in_ramp   = 0;      // 1: walk the local rows in growing groups (the kernel starts before the rows are there); 2: phases over all shards
     int         in_rows = 256;
     cudaEvent_t in_consumed = nullptr;
 
@@ -276,7 +276,11 @@ xccl_status_t xccl_tp_ag_gemm_swiglu(xccl_tp_ws_h w, const void *const *Wg, cons
     if (w->in_active) {
         p.in_target        = w->in_seq;
         p.in_rows_per_flag = w->in_rows;
-        p.group_ramp       = w->in_ramp ? 1 : 0;
+        // H2D_PHASES (with copy CTAs; every rank of the team must run with the same setting): every rank reports its
+        // rows block by block and the walk takes row block c of every shard before c + 1. Otherwise the peers' shards
+        // are read whole and only the local rows ramp.
+        const bool phases  = w->tp > 1 && w->copy_mode == 0 && w->in_ramp == 2;
+        p.group_ramp       = w->in_ramp == 0 ? 0 : phases ? 2 : 1;
     }
     xccl_status_t lst = launch_gemm(p, l, (cudaStream_t)stream);
     if (w->in_active && lst == XCCL_OK) {
@@ -294,7 +298,8 @@ xccl_status_t xccl_tp_ag_gemm_swiglu(xccl_tp_ws_h w, const void *const *Wg, cons
 // stream after the kernel that read the shard last; `issue` enqueues the chunks and their flag writes. ramp != 0: the
 // kernel walks the local rows in groups of 1, 1, 2, 4, ... row blocks, so its first wave needs the first chunk only
 // (for a step that starts with an idle GPU; a pipelined caller, whose copy runs under the previous step's second
-// kernel, passes 0 and keeps the full groups).
+// kernel, passes 0 and keeps the full groups). ramp == 2 (or the option H2D_PHASES): with copy CTAs, phases over all
+// shards as described at GemmParams::group_ramp; every rank of the team must ask for the same.
 xccl_status_t xccl_tp_h2d_expect(xccl_tp_ws_h w, void *copy_stream, int ramp)
 {
     if (w == nullptr) return XCCL_ERR_INVALID_PARAM;
@@ -302,7 +307,7 @@ xccl_status_t xccl_tp_h2d_expect(xccl_tp_ws_h w, void *copy_stream, int ramp)
     if (w->in_consumed != nullptr) XCCL_CUDA_CHECK(cudaStreamWaitEvent((cudaStream_t)copy_stream, w->in_consumed, 0));
     w->in_seq++;
     w->in_active = true;
-    w->in_ramp   = ramp != 0 && tp_options().flag("H2D_RAMP");
+    w->in_ramp   = (ramp == 0 || !tp_options().flag("H2D_RAMP")) ? 0 : (ramp == 2 || tp_options().flag("H2D_PHASES")) ? 2 : 1;
     return XCCL_OK;
 }
 

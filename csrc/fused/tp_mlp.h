@@ -44,7 +44,9 @@ xccl_status_t xccl_tp_h2d_begin(xccl_tp_ws_h ws, const void *const *host_x, void
 /* The same copy in two calls with the launch of xccl_tp_ag_gemm_swiglu between them (expect, launch, issue): the kernel
  * starts at once and the chunks are enqueued while it already runs. Every `expect` must be followed by the launch and
  * the `issue`: the kernel's waits for the rows are bounded. ramp != 0: the local rows are walked in groups of 1, 1, 2,
- * 4, ... row blocks, so that the first tiles need the first chunk only (a step that starts on an idle GPU). */
+ * 4, ... row blocks, so that the first tiles need the first chunk only (a step that starts on an idle GPU); ramp == 2:
+ * with copy CTAs, every rank reports its rows block by block and the tiles are walked row block by row block over all
+ * shards (every rank of the team must ask for the same). */
 xccl_status_t xccl_tp_h2d_expect(xccl_tp_ws_h ws, void *copy_stream, int ramp);
 xccl_status_t xccl_tp_h2d_issue(xccl_tp_ws_h ws, const void *const *host_x, void *copy_stream);
 

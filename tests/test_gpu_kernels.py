@@ -552,13 +552,15 @@ def test_tp_mlp_end_to_end_from_pinned_host(dev):
         mlp.close()
 
 
-@pytest.mark.parametrize("tp", [1, 2])
-def test_tp_mlp_input_arriving_from_host_overlaps_first_kernel(dev, tp, monkeypatch):
+@pytest.mark.parametrize("tp,phases", [(1, False), (2, False), (4, False), (4, True), (8, False), (8, True)])
+def test_tp_mlp_input_arriving_from_host_overlaps_first_kernel(dev, tp, phases, monkeypatch):
     """The chunked host->device copy with stream-ordered flags: the kernel starts before the rows are there and
-    must produce the same output as the plain copy-then-launch path, step after step."""
+    must produce the same output as the plain copy-then-launch path, step after step. With copy CTAs (4 and 8
+    ranks) and H2D_PHASES every rank reports its rows block by block and the tiles are walked in phases over all shards."""
     from xccl_b200.models.tp_mlp import TpMlp, reference_forward_fp32
     monkeypatch.setenv("XCCL_TP_H2D_OVERLAP", "1")
-    tokens, hidden, ffn = 1024, 512, 1024
+    monkeypatch.setenv("XCCL_TP_H2D_PHASES", "y" if phases else "n")
+    tokens, hidden, ffn = (1024, 512, 1024) if tp <= 2 else (4096, 512, 1024)
     mlp = TpMlp(tokens, hidden, ffn, tp=tp, emulate=(tp > 1))
     try:
         assert mlp.overlap_h2d

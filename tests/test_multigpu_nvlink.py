@@ -293,6 +293,16 @@ def _tp_rank_main(rank, size, job):
             mlp.check_error()
             errs.append(float((y.float() - want).abs().max()))
             torch.testing.assert_close(y.float(), want, rtol=3e-2, atol=3e-2)
+        # the same block with the input arriving from pinned host memory while the kernel already runs (every rank
+        # reports its rows as they land; remote tiles start after the first chunks), a new input every step
+        for it in range(3):
+            x2 = torch.randn(tokens, hidden, generator=torch.Generator().manual_seed(100 + it)).to(torch.bfloat16)
+            mine = x2.chunk(size, 0)[rank].contiguous().pin_memory()
+            metric = mlp.forward_from_host([mine])
+            mlp.check_error()
+            want2 = reference_forward_fp32(x2.to(dev), w_gate, w_up, w_down).chunk(size, 0)[rank]
+            torch.testing.assert_close(mlp.y[0].float(), want2, rtol=3e-2, atol=3e-2)
+            assert torch.isfinite(metric)
         return max(errs)
     finally:
         mlp.close()

@@ -96,3 +96,24 @@ def test_ramped_order_for_rows_arriving_from_the_host(tiles_m, tiles_n, tp, grou
         if tp > 1:
             plain = _order(tiles_m, tiles_n, tp, rank, comm, group_rows)
             assert order[mbs * tiles_n:] == plain[mbs * tiles_n:]
+
+
+@pytest.mark.parametrize("tp,mbs,tiles_n", [(4, 8, 28), (8, 4, 28), (8, 2, 5), (2, 3, 7)])
+def test_phase_order_of_the_allgather_while_every_shard_is_arriving(tp, mbs, tiles_n):
+    """group_ramp = 2: row block c of every shard (local first) x all column blocks, then c + 1."""
+    L = K.load()
+    fn = L.xccl_tp_tile_order_ramp
+    fn.restype = C.c_int
+    fn.argtypes = [C.c_int] * 7 + [C.POINTER(C.c_int)] * 3 + [C.c_int]
+    tiles_m = tp * mbs
+    n = tiles_m * tiles_n
+    for rank in range(tp):
+        mb, nb, sh = (C.c_int * n)(), (C.c_int * n)(), (C.c_int * n)()
+        assert fn(tiles_m, tiles_n, tp, rank, COMM_AG, 0, 2, mb, nb, sh, n) == n
+        order = list(zip(mb, nb, sh))
+        assert sorted((m, c) for m, c, _ in order) == sorted(itertools.product(range(tiles_m), range(tiles_n)))
+        for t, (m, c, s) in enumerate(order):
+            assert m // mbs == s
+            assert m % mbs == t // (tiles_n * tp)            # the phase
+            assert s == (rank + t % tp) % tp                  # shards rotate fastest, the local one first
+            assert c == (t % (tiles_n * tp)) // tp

@@ -54,6 +54,8 @@ class TpMlp:
         # 8192 x 8192 x 28672 block on one GPU: 10.2 ms per end-to-end step with copy-then-launch, 9.1 ms with the
         # overlapped copy, 8.8 ms with the growing groups; kernels alone 8.6 ms). XCCL_TP_H2D_OVERLAP=0 turns it off.
         self.overlap_h2d = os.environ.get("XCCL_TP_H2D_OVERLAP") != "0"
+        # phases over all shards while every rank's input arrives (copy CTAs, 4 ranks and more); off: no gain measured
+        self.h2d_phases = os.environ.get("XCCL_TP_H2D_PHASES", "n").lower() in ("y", "yes", "1", "on", "true")
         self._copy_stream = None
         self._y_alt = None
         self._d2h_stream = None
@@ -80,7 +82,7 @@ class TpMlp:
             return self.forward()
         if self._copy_stream is None:
             self._copy_stream = torch.cuda.Stream()
-        self.ws.h2d_expect(self._copy_stream, ramp)
+        self.ws.h2d_expect(self._copy_stream, (2 if self.h2d_phases else 1) if ramp else 0)
         try:
             y = self.forward()
         finally:

@@ -132,13 +132,14 @@ class TpWorkspace:
         if st != K.OK:
             raise XcclError(st, "xccl_tp_h2d_begin")
 
-    def h2d_expect(self, copy_stream: "torch.cuda.Stream", ramp: bool = True) -> None:
+    def h2d_expect(self, copy_stream: "torch.cuda.Stream", ramp: int = 1) -> None:
         """First half of ``h2d_begin``: the next ``ag_gemm_swiglu`` will wait for the rows of a copy that
         ``h2d_issue`` enqueues AFTER the kernel has been launched, so the host time of issuing the chunks is spent
         while the kernel already runs. Must be followed by the launch and by ``h2d_issue``. ``ramp``: the kernel
         walks the local rows in groups of 1, 1, 2, 4, ... row blocks so that its first tiles need the first chunk only;
-        a pipelined caller, whose copy runs under the previous step's kernels, passes False."""
-        st = K.load().xccl_tp_h2d_expect(self.h, copy_stream.cuda_stream, 1 if ramp else 0)
+        a pipelined caller, whose copy runs under the previous step's kernels, passes 0. 2: phases over all shards
+        (copy CTAs; every rank reports its rows block by block; all ranks must ask for the same)."""
+        st = K.load().xccl_tp_h2d_expect(self.h, copy_stream.cuda_stream, int(ramp))
         if st != K.OK:
             raise XcclError(st, "xccl_tp_h2d_expect")
 
