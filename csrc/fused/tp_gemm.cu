@@ -1,6 +1,6 @@
 // Tensor-parallel GEMM kernels for sm_100a (see tp_gemm.cuh for the operations).
 //
-// Default layout: CTA pairs. A cluster of two CTAs (192 threads each, one CTA per SM, persistent) owns an output tile
+// Default layout: CTA pairs. A cluster of two CTAs (256 threads each, 384 in fp8; one CTA per SM, persistent) owns an output tile
 // of 256 x 256: tcgen05.mma.cta_group::2 (M256 N256 K16) is issued by CTA 0 of the pair and accumulates fp32 in the
 // tensor memory of both CTAs. Each CTA stages its own 128 rows of A and HALF of the B tile per K block of 64, so a
 // stage is 32 KB and the ring has six. When the shape or the device cannot place pairs, the same kernel runs as
@@ -14,6 +14,7 @@
 //   warps 2-5  read their 32 TMEM lanes with tcgen05.ld, apply the epilogue (bf16 cast, silu(gate)*up, or the sum
 //            with the peers' partial tiles in reduce-scatter mode), transpose through shared memory and write
 //            128-byte row segments to local or peer memory
+//   last two warps  allgather mode with copier warps: pull this CTA's share of the remote row blocks (idle otherwise)
 // Tiles are walked in a shape-dependent order and the walkers are kept in soft lockstep so that CTAs sharing rows of A
 // or B hit them in L2 together. No TMA load uses cluster multicast and no TMA load reads another GPU's memory:
 // remote operands are first copied into local memory by the copy CTAs of this same kernel.
