@@ -54,7 +54,12 @@ xccl_status_t xccl_coll_req::wait()
         }
         if ((++spins & 0x3ff) == 0 && limit > 0) {
             double dt = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
-            if (dt > limit) return XCCL_ERR_TIMED_OUT;
+            if (dt > limit) {
+                // the collective is still in flight inside its team library and cannot be matched with the peers'
+                // any more: every later collective of that team fails at once instead of waiting again
+                if (tl_team != nullptr) tl_team->poisoned = true;
+                return XCCL_ERR_TIMED_OUT;
+            }
         }
     }
     return st;
@@ -295,6 +300,7 @@ xccl_status_t xccl_collective_init(xccl_coll_op_args_t *args, xccl_coll_req_h *r
         if (st != XCCL_OK) return st;
         req->core_team = team;
         req->coll_type = (int)args->coll_type;
+        req->tl_team   = tt;
         *request       = req;
         return XCCL_OK;
     }

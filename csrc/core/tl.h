@@ -19,6 +19,10 @@ struct xccl_context;
 struct xccl_team;
 
 // The public request handle IS the TL's request object.
+namespace xccl {
+class TlTeam;
+}
+
 struct xccl_coll_req {
     virtual ~xccl_coll_req() = default;
     virtual xccl_status_t post()     = 0;
@@ -28,6 +32,7 @@ struct xccl_coll_req {
     virtual double        elapsed_us() { return -1.0; }
     xccl_team *core_team = nullptr;
     int        coll_type = -1;   // xccl_collective_type_t, set by xccl_collective_init (tracing)
+    xccl::TlTeam *tl_team = nullptr;  // the team-library team that serves the request (poisoned when a wait runs out)
 };
 
 struct xccl_mem_handle {

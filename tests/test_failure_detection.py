@@ -102,3 +102,46 @@ def _leaves_between_steps(rank, size, job):
 def test_rank_leaving_between_collectives_is_detected():
     res = run_ranks(_leaves_between_steps, 3, timeout=60, env={"XCCL_WAIT_TIMEOUT": "1"})
     assert res == ["detected", "detected", "left"]
+
+
+def _shrinks_after_a_failure(rank, size, job):
+    """Four ranks; rank 2 leaves after the first allreduce. The others get the deadline error from the next one, drop
+    the poisoned team and carry on with a new team over the survivors on the SAME context (an endpoint map): no
+    rendezvous with the lost rank is needed, because team creation gathers over the members of the new team only."""
+    oob = ShmOob(job, rank, size)
+    lib = Lib()
+    ctx = Context(lib, oob, tls=K.TL_UCX)
+    team = Team(ctx)
+    src = np.arange(1000, dtype=np.int32) + rank
+    dst = np.zeros_like(src)
+    team.allreduce(src, dst).run().finalize()
+    if rank == 2:
+        return "left"
+    req = team.allreduce(src, dst)
+    req.post()
+    try:
+        req.wait()
+        return "completed"
+    except XcclError as e:
+        assert e.status == K.ERR_TIMED_OUT
+    # every later collective of the poisoned team fails at once instead of waiting again
+    t0 = time.monotonic()
+    with pytest.raises(XcclError):
+        team.allreduce(src, dst).run()
+    assert time.monotonic() - t0 < 0.5
+    survivors = [0, 1, 3]          # known to the survivors from outside (a store, a heartbeat)
+    small = Team(ctx, ranks=survivors, timeout=20.0)
+    assert small.size == 3 and small.rank == survivors.index(rank)
+    for it in range(3):
+        dst[:] = 0
+        small.allreduce(src + it, dst).run().finalize()
+        want = sum(np.arange(1000, dtype=np.int64) + r + it for r in survivors).astype(np.int32)
+        assert np.array_equal(dst, want)
+    small.barrier().run().finalize()
+    small.close()
+    return "recovered"
+
+
+def test_survivors_continue_on_a_smaller_team_of_the_same_context():
+    res = run_ranks(_shrinks_after_a_failure, 4, timeout=90, env={"XCCL_WAIT_TIMEOUT": "1"})
+    assert res == ["recovered", "recovered", "left", "recovered"]
