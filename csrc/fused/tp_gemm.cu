@@ -894,9 +894,15 @@ xccl_status_t launch_gemm_impl(const GemmParams &p_in, const GemmLaunch &l, cuda
         cfg.numAttrs             = 2;
         cfg.gridDim              = dim3((unsigned)pctas, (unsigned)l.n_local);
         // every CTA of the grid must be resident at once: roles wait for one another
-        int         max_clusters = 0;
-        cudaError_t oe           = fp8 ? cudaOccupancyMaxActiveClusters(&max_clusters, tp_gemm_kernel<true, true>, &cfg)
-                                       : cudaOccupancyMaxActiveClusters(&max_clusters, tp_gemm_kernel<true, false>, &cfg);
+        // (a property of the device, the kernel and its launch shape, none of which changes: asked once per device)
+        static int  clusters_fit[64][2] = {};
+        int         max_clusters        = clusters_fit[dev][fp8 ? 1 : 0];
+        cudaError_t oe                  = cudaSuccess;
+        if (max_clusters == 0) {
+            oe = fp8 ? cudaOccupancyMaxActiveClusters(&max_clusters, tp_gemm_kernel<true, true>, &cfg)
+                     : cudaOccupancyMaxActiveClusters(&max_clusters, tp_gemm_kernel<true, false>, &cfg);
+            if (oe == cudaSuccess) clusters_fit[dev][fp8 ? 1 : 0] = max_clusters;
+        }
         if (oe == cudaSuccess && pp.n_gemm_ctas >= 2 && max_clusters * 2 >= pctas * l.n_local) {
             cudaError_t le = fp8 ? cudaLaunchKernelEx(&cfg, tp_gemm_kernel<true, true>, pp, l)
                                  : cudaLaunchKernelEx(&cfg, tp_gemm_kernel<true, false>, pp, l);
