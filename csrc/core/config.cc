@@ -84,10 +84,11 @@ bool OptTable::valid(const OptField &f, const std::string &v) const
     switch (f.type) {
     case OptType::STRING: return true;
     case OptType::INT:
-    case OptType::UINT:
-    case OptType::MEMUNITS:
         parse_memunits(v, &ok);
         return ok;
+    case OptType::UINT:
+    case OptType::MEMUNITS:
+        return parse_memunits(v, &ok) >= 0 && ok;  // counts and sizes: a negative value is a mistake, not a huge number
     case OptType::BOOL: return parse_bool(v, &b);
     case OptType::TERNARY: return parse_bool(v, &b) || lower(v) == "try";
     case OptType::LOG_LEVEL: return parse_log_level(v, -1) >= 0;

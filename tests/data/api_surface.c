@@ -152,6 +152,14 @@ int main(void)
         CHECK(xccl_context_config_modify(&one, cc, "ALLREDUCE_KN_RADIX", "many") != XCCL_OK);
         one = XCCL_TL_HIER;
         CHECK(xccl_context_config_modify(&one, cc, "BCAST_PIPELINE_THRESH", "64k") == XCCL_OK);
+        CHECK(xccl_context_config_modify(&one, cc, "BCAST_PIPELINE_THRESH", "inf") == XCCL_OK);
+        CHECK(xccl_context_config_modify(&one, cc, "BCAST_PIPELINE_THRESH", "12 parsecs") != XCCL_OK);
+        CHECK(xccl_context_config_modify(&one, cc, "ENABLE_SHMSEG", "y") == XCCL_OK);
+        CHECK(xccl_context_config_modify(&one, cc, "ENABLE_SHMSEG", "off") == XCCL_OK);
+        CHECK(xccl_context_config_modify(&one, cc, "ENABLE_SHMSEG", "perhaps") != XCCL_OK);
+        CHECK(xccl_context_config_modify(&one, cc, "BCAST_PIPELINE_DEPTH", "-3") != XCCL_OK);   /* unsigned */
+        one = XCCL_TL_MPOD;   /* no such team library in this config when it was filtered out, or no such option */
+        CHECK(xccl_context_config_modify(&one, cc, "NO_SUCH_OPTION", "1") != XCCL_OK);
         xccl_context_config_release(cc);
         unsetenv("XCCL_TEAM_UCX_ALLREDUCE_KN_RADIX");
         xccl_lib_cleanup(lib);
