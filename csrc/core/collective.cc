@@ -252,6 +252,54 @@ xccl_status_t xccl_collective_init(xccl_coll_op_args_t *args, xccl_coll_req_h *r
     if (args == nullptr || request == nullptr || team == nullptr) return XCCL_ERR_INVALID_PARAM;
     if (!team->created) return XCCL_ERR_NO_RESOURCE;
     if ((int)args->coll_type < 0 || args->coll_type >= XCCL_COLL_LAST) return XCCL_ERR_INVALID_PARAM;
+    // a root is a team rank: checked here once, so that no team library indexes its peers with it unchecked
+    if (args->coll_type == XCCL_BCAST || args->coll_type == XCCL_REDUCE || args->coll_type == XCCL_FANIN ||
+        args->coll_type == XCCL_FANOUT) {
+        const xccl_team_params_t &tp = team->params;
+        const int team_size = (tp.field_mask & XCCL_TEAM_PARAM_FIELD_OOB) ? tp.oob.size
+                              : ((tp.field_mask & XCCL_TEAM_PARAM_FIELD_EP_RANGE) && tp.range.type != XCCL_EP_RANGE_UNDEFINED)
+                                  ? tp.range.ep_num
+                                  : team->ctx->params.oob.size;
+        if (args->root < 0 || args->root >= team_size) {
+            xccl_debug("root %d outside a team of %d ranks", args->root, team_size);
+            return XCCL_ERR_INVALID_PARAM;
+        }
+    }
+
+    // buffers and count arrays a collective cannot do without (an empty message may come without buffers)
+    {
+        const xccl_coll_buffer_info_t &bi = args->buffer_info;
+        const bool empty = bi.len == 0 && args->reduce_info.count == 0;
+        switch (args->coll_type) {
+        case XCCL_ALLREDUCE:
+        case XCCL_REDUCE_SCATTER:
+        case XCCL_ALLTOALL:
+            if (!empty && bi.dst_buffer == nullptr) return XCCL_ERR_INVALID_PARAM;
+            break;
+        case XCCL_ALLGATHER: {
+            const xccl_team_params_t &tp = team->params;
+            const int n = (tp.field_mask & XCCL_TEAM_PARAM_FIELD_OOB) ? tp.oob.size
+                          : ((tp.field_mask & XCCL_TEAM_PARAM_FIELD_EP_RANGE) && tp.range.type != XCCL_EP_RANGE_UNDEFINED)
+                              ? tp.range.ep_num
+                              : team->ctx->params.oob.size;
+            if (!empty && bi.dst_buffer == nullptr) return XCCL_ERR_INVALID_PARAM;
+            if (n > 0 && bi.len % (size_t)n != 0) return XCCL_ERR_INVALID_PARAM;  // len is the gathered size
+            break;
+        }
+        case XCCL_ALLTOALLV:
+            if (bi.dst_buffer == nullptr || bi.src_counts == nullptr || bi.dst_counts == nullptr ||
+                bi.src_displacements == nullptr || bi.dst_displacements == nullptr) {
+                return XCCL_ERR_INVALID_PARAM;
+            }
+            break;
+        case XCCL_BCAST:
+            if (!empty && bi.dst_buffer == nullptr && (bi.src_buffer == nullptr || bi.src_buffer == XCCL_IN_PLACE)) {
+                return XCCL_ERR_INVALID_PARAM;
+            }
+            break;
+        default: break;
+        }
+    }
 
     // Synchronisation-only collectives carry no buffer and count as host memory.
     xccl_memory_type_t mem = XCCL_MEMORY_TYPE_HOST;
