@@ -220,6 +220,7 @@ xccl_status_t build_alltoall(HierTeam &t, const xccl_coll_op_args_t &a, xccl_mem
 {
     const Layout &L = t.layout;
     *parallel       = false;
+    if (t.size == 1) return XCCL_ERR_UNSUPPORTED;  // nothing to schedule: the next team library copies the block
     if (a.buffer_info.src_buffer == XCCL_IN_PLACE || a.buffer_info.src_buffer == a.buffer_info.dst_buffer) {
         return XCCL_ERR_UNSUPPORTED;
     }

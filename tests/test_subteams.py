@@ -64,3 +64,37 @@ def _rank_main(rank, size, job):
 def test_split_team_created_without_blocking_while_the_world_team_works():
     res = run_ranks(_rank_main, 5, timeout=120)
     assert res == [3, 2, 3, 2, 3]
+
+
+def _small_teams(rank, size, job):
+    """Teams of one rank and of every second rank on a context whose first team library is the hierarchy layer: what
+    that layer cannot schedule (nothing to exchange) falls through to the host team, the rest runs on the sub-group."""
+    oob = ShmOob(job, rank, size)
+    lib = Lib()
+    ctx = Context(lib, oob, tls=K.TL_UCX | K.TL_HIER, config={K.TL_HIER: {"ENABLE_NVLINK": "no"}})
+    solo = Team(ctx, ranks=[rank])
+    assert (solo.rank, solo.size) == (0, 1)
+    x = np.arange(10, dtype=np.int32) + rank
+    y = np.zeros_like(x)
+    solo.allreduce(x, y).run().finalize()
+    assert np.array_equal(x, y)
+    y[:] = 0
+    solo.alltoall(x, y).run().finalize()
+    assert np.array_equal(x, y)
+    solo.bcast(x, 0).run().finalize()
+    solo.barrier().run().finalize()
+    solo.close()
+    if rank % 2 == 1:
+        members = [r for r in range(size) if r % 2 == 1]
+        odd = Team(ctx, ranks=members)
+        v = np.full(5, rank, np.int32)
+        w = np.zeros_like(v)
+        odd.allreduce(v, w).run().finalize()
+        assert np.all(w == sum(members))
+        odd.close()
+    ctx.close(); lib.close(); oob.close()
+    return True
+
+
+def test_teams_of_one_and_of_every_second_rank():
+    run_ranks(_small_teams, 5, timeout=120)
