@@ -30,6 +30,15 @@ struct xccl_lib_config {
 struct xccl_lib {
     std::vector<xccl::TeamLib *> tls;   // TLs that passed the params filter
     xccl_lib_params_t            params{};
+    // whether team library `id` opened on this machine and passed the filter (composite team libraries ask before
+    // they try an optional level, so that a level that cannot exist here is left out without an error message)
+    bool has(xccl_tl_id_t id) const
+    {
+        for (const xccl::TeamLib *t : tls) {
+            if (t->id == id) return true;
+        }
+        return false;
+    }
 };
 
 struct xccl_context_config {

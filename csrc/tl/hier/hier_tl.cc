@@ -38,18 +38,8 @@ xccl_status_t HierContext::init()
     if (cfg.enable_hmc) want.push_back(XCCL_TL_HMC);
     if (cfg.enable_shmseg) want.push_back(XCCL_TL_SHMSEG);
     // optional levels whose team library did not open here (no CUDA device, no NCCL) are left out quietly
-    std::vector<xccl_tl_id_t> have;
-    {
-        xccl_tl_id_t *ids = nullptr;
-        unsigned      n   = 0;
-        if (xccl_get_tl_list(lib, &ids, &n) == XCCL_OK && ids != nullptr) {
-            have.assign(ids, ids + n);
-            xccl_free_tl_list(ids);
-        }
-    }
-    auto opened = [&](xccl_tl_id_t id) { return std::find(have.begin(), have.end(), id) != have.end(); };
     for (xccl_tl_id_t id : want) {
-        if (id != XCCL_TL_UCX && !opened(id)) continue;
+        if (id != XCCL_TL_UCX && !lib->has(id)) continue;
         xccl_context_params_t cp = params;
         cp.field_mask |= XCCL_CONTEXT_PARAM_FIELD_TLS;
         cp.tls = (uint64_t)id;

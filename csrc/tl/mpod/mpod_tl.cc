@@ -94,9 +94,10 @@ public:
         };
         st = make(XCCL_TL_UCX, "MPOD_ucx", &host);
         if (st != XCCL_OK) return st;
-        if (make(XCCL_TL_NVLINK, "MPOD_nvlink", &dev) != XCCL_OK) {
+        // the device level is optional: NVLink team first, NCCL team second, neither on a machine without GPUs
+        if (!lib->has(XCCL_TL_NVLINK) || make(XCCL_TL_NVLINK, "MPOD_nvlink", &dev) != XCCL_OK) {
             dev = nullptr;
-            if (make(XCCL_TL_NCCL, "MPOD_nccl", &dev) != XCCL_OK) dev = nullptr;
+            if (!lib->has(XCCL_TL_NCCL) || make(XCCL_TL_NCCL, "MPOD_nccl", &dev) != XCCL_OK) dev = nullptr;
         }
         return XCCL_OK;
     }
