@@ -89,6 +89,22 @@ def _rank(rank, size, job):
     assert init_raw(ragged_allgather) == K.ERR_INVALID_PARAM
     out["raw"] = "ok"
 
+    # the Python layer sees the arrays, not just their addresses: a strided view or a buffer that is too short is
+    # refused before anything is sent
+    big = np.arange(100, dtype=np.int32)
+    small = np.zeros(50, np.int32)
+    with pytest.raises(ValueError, match="not contiguous"):
+        team.allreduce(big[::2], small)
+    with pytest.raises(ValueError, match="dst holds 200 bytes"):
+        team.allreduce(big, small)
+    with pytest.raises(ValueError, match="src holds"):
+        team.allgather(small[:3], np.zeros(4 * size, np.int32))
+    with pytest.raises(ValueError, match="dst holds"):
+        team.alltoallv(big, [10] * size, [10 * i for i in range(size)], small, [30] * size, [30 * i for i in range(size)])
+    with pytest.raises(ValueError, match="one count"):
+        team.alltoallv(big, [1], [0], small, [1], [0])
+    out["python_checks"] = "ok"
+
     # the request life cycle: a second post while in flight is refused or ordered, finalize refuses a request in
     # flight, a completed request can be posted again
     x = np.arange(50000, dtype=np.int64) + rank
@@ -116,4 +132,4 @@ def _rank(rank, size, job):
 def test_wrong_arguments_end_in_status_codes():
     res = run_ranks(_rank, 3, timeout=120)
     for r in res:
-        assert r == {"zero_count": "ok", "bad_root": "ok", "float_band": "ok", "raw": "ok", "lifecycle": "ok"}
+        assert r == {"zero_count": "ok", "bad_root": "ok", "float_band": "ok", "raw": "ok", "python_checks": "ok", "lifecycle": "ok"}

@@ -59,6 +59,25 @@ def numel_of(buf: Any) -> int:
     return int(buf.size) if hasattr(buf, "ctypes") else int(buf.numel())
 
 
+def _is_array(buf: Any) -> bool:
+    return buf is not None and not isinstance(buf, (int, str)) and (hasattr(buf, "data_ptr") or hasattr(buf, "ctypes"))
+
+
+def _require(buf: Any, nbytes: int, what: str) -> None:
+    """A buffer handed to a collective is one contiguous block of at least `nbytes` bytes: the library sees only its
+    address, so a strided view or a short buffer would be read or written past what the caller meant."""
+    if not _is_array(buf):
+        return  # a raw address or the in-place marker: the caller vouches for it
+    if hasattr(buf, "is_contiguous"):
+        contiguous = bool(buf.is_contiguous())
+    else:
+        contiguous = bool(buf.flags["C_CONTIGUOUS"])
+    if not contiguous:
+        raise ValueError(f"{what} is not contiguous")
+    if nbytes_of(buf) < nbytes:
+        raise ValueError(f"{what} holds {nbytes_of(buf)} bytes, the collective needs {nbytes}")
+
+
 class ShmOob:
     """Shared-memory out-of-band provider for ranks of one host (``xccl_oob_shm_create``)."""
 
@@ -313,6 +332,8 @@ class Team:
         keep: list = []
         dt = dtype_of(dst if isinstance(src, str) else src) if dt is None else dt
         count = numel_of(dst if isinstance(src, str) else src) if count is None else count
+        _require(src, count * K.DT_SIZE[dt], "src")
+        _require(dst, count * K.DT_SIZE[dt if out_dt is None or out_dt == K.DT_UNSUPPORTED else out_dt], "dst")
         a = self._args(K.ALLREDUCE, src, dst, count * K.DT_SIZE[dt], alg, stream, keep)
         a.reduce_info.dt, a.reduce_info.op, a.reduce_info.count = dt, op, count
         self._epilogue(a, scale, out_dt)
@@ -331,6 +352,9 @@ class Team:
         keep: list = []
         dt = dtype_of(src) if dt is None else dt
         count = numel_of(src) if count is None else count
+        _require(src, count * K.DT_SIZE[dt], "src")
+        if self.rank == root:
+            _require(dst, count * K.DT_SIZE[dt if out_dt is None or out_dt == K.DT_UNSUPPORTED else out_dt], "dst")
         a = self._args(K.REDUCE, src, dst, count * K.DT_SIZE[dt], alg, stream, keep)
         a.reduce_info.dt, a.reduce_info.op, a.reduce_info.count = dt, op, count
         a.root = root
@@ -342,6 +366,8 @@ class Team:
                        scale: Optional[float] = None, out_dt: Optional[int] = None) -> Request:
         keep: list = []
         dt = dtype_of(src) if dt is None else dt
+        _require(src, 0, "src")
+        _require(dst, numel_of(src) // self.size * K.DT_SIZE[dt if out_dt is None or out_dt == K.DT_UNSUPPORTED else out_dt], "dst")
         a = self._args(K.REDUCE_SCATTER, src, dst, nbytes_of(src), alg, stream, keep)
         a.reduce_info.dt, a.reduce_info.op = dt, op
         a.reduce_info.count = numel_of(src) // self.size
@@ -351,12 +377,15 @@ class Team:
     def bcast(self, buf: Any, root: int, nbytes: Optional[int] = None, alg: Optional[int] = None,
               stream: Any = None) -> Request:
         keep: list = []
+        _require(buf, 0 if nbytes is None else nbytes, "buf")
         a = self._args(K.BCAST, buf, buf, nbytes_of(buf) if nbytes is None else nbytes, alg, stream, keep)
         a.root = root
         return Request(self, a, tuple(keep))
 
     def allgather(self, src: Any, dst: Any, stream: Any = None, alg: Optional[int] = None) -> Request:
         keep: list = []
+        _require(dst, 0, "dst")
+        _require(src, nbytes_of(dst) // self.size, "src")
         a = self._args(K.ALLGATHER, src, dst, nbytes_of(dst), alg, stream, keep)
         return Request(self, a, tuple(keep))
 
@@ -364,6 +393,8 @@ class Team:
                  stream: Any = None) -> Request:
         keep: list = []
         per = nbytes_of(dst) // self.size if bytes_per_peer is None else bytes_per_peer
+        _require(src, per * self.size, "src")
+        _require(dst, per * self.size, "dst")
         a = self._args(K.ALLTOALL, src, dst, per, alg, stream, keep)
         return Request(self, a, tuple(keep))
 
@@ -372,6 +403,12 @@ class Team:
                   stream: Any = None) -> Request:
         keep: list = []
         dt = dtype_of(src) if dt is None else dt
+        if len(src_counts) != self.size or len(src_displs) != self.size or len(dst_counts) != self.size or \
+                len(dst_displs) != self.size:
+            raise ValueError("alltoallv takes one count and one displacement per team rank")
+        es = K.DT_SIZE[dt]
+        _require(src, max((int(d) + int(c)) for c, d in zip(src_counts, src_displs)) * es, "src")
+        _require(dst, max((int(d) + int(c)) for c, d in zip(dst_counts, dst_displs)) * es, "dst")
         a = self._args(K.ALLTOALLV, src, dst, 0, None, stream, keep)
         arrs = [(C.c_uint32 * self.size)(*map(int, v)) for v in (src_counts, src_displs, dst_counts, dst_displs)]
         keep.extend(arrs)
