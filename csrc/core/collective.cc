@@ -15,9 +15,8 @@ namespace {
 // collective a kernel or a host wait belongs to. Read once.
 bool nvtx_on()
 {
-    static int on = -1;
-    if (on < 0) on = global_state().opts.flag("NVTX") ? 1 : 0;
-    return on == 1;
+    static const bool on = global_state().opts.flag("NVTX");  // initialised once, also with several posting threads
+    return on;
 }
 const char *coll_name(int t)
 {

@@ -13,10 +13,10 @@ from xccl_b200.utils.launch import run_ranks
 N_THREADS, ITERS = 4, 40
 
 
-def _rank_main(rank, size, job):
+def _rank_main(rank, size, job, tls=K.TL_UCX):
     oob = ShmOob(job, rank, size)
     lib = Lib(thread_mode=K.THREAD_MULTIPLE)
-    ctx = Context(lib, oob, tls=K.TL_UCX, thread_mode=K.THREAD_MULTIPLE)
+    ctx = Context(lib, oob, tls=tls, thread_mode=K.THREAD_MULTIPLE, config={K.TL_HIER: {"ENABLE_NVLINK": "no"}})
     errors, done = [], []
 
     def worker(tid: int) -> None:
@@ -58,4 +58,11 @@ def _rank_main(rank, size, job):
 
 def test_threads_drive_their_own_teams_concurrently():
     res = run_ranks(_rank_main, 3, timeout=240)
+    assert res == [list(range(N_THREADS))] * 3
+
+
+def test_threads_drive_hierarchy_teams_concurrently():
+    """The same with the hierarchy layer on top: its schedules run as tasks of the context's lock-free progress queue,
+    which any of the threads may pop and progress."""
+    res = run_ranks(_rank_main, 3, K.TL_HIER | K.TL_UCX, timeout=240)
     assert res == [list(range(N_THREADS))] * 3
